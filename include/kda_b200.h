@@ -1,0 +1,116 @@
+/* C ABI of libkda_b200.so -- the KDA (Kimi Delta Attention) chunked forward, chunk
+ * size 16, K = V = 128, hand-written CUDA for sm_100a (B200).
+ *
+ * The library is the drop-in for the device side of the reference project's
+ * forward path.  Reference interfaces each entry point replaces (paths inside
+ * the reference project):
+ *
+ *   kda_fwd            <- the two Triton launches of `_run`
+ *                         (src/kda_bt16/kernels.py:581-602) and the Ascend stage
+ *                         sequence of `_kda_fwd_impl`
+ *                         (python/kda_ascendc_v1/api.py:890-1191), which reach the
+ *                         device through `launch_argsarray_engine`
+ *                         (aclab/launcher/launcher.cpp:271-294).
+ *   kda_fwd_k1         <- `kda_bt16_kernel_k1` (src/kda_bt16/kernels.py:53-184)
+ *   kda_fwd_k2         <- `kda_bt16_kernel_k2` (src/kda_bt16/kernels.py:187-302)
+ *   kda_fwd_workspace_bytes
+ *                      <- the per-call `torch.empty` intermediates of `_run`
+ *                         (src/kda_bt16/kernels.py:572-579)
+ *   kda_last_error     <- the launcher's exception text
+ *                         (aclab/launcher/launcher.cpp:35-39)
+ *
+ * Conventions: the library allocates nothing; the caller owns every buffer and
+ * passes raw device pointers (NULL = tensor absent).  All launches are
+ * asynchronous on the given stream (a cudaStream_t passed as void*), exactly as
+ * the reference launches on the caller's current stream.  Functions return 0 on
+ * success and a negative KDA_ERR_* code otherwise; kda_last_error() returns the
+ * thread-local message of the last failure.
+ */
+#ifndef KDA_B200_H_
+#define KDA_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define KDA_OK 0
+#define KDA_ERR_INVALID_ARG (-1)
+#define KDA_ERR_CUDA (-2)
+#define KDA_ERR_DEVICE_STATUS (-3)
+
+#define KDA_G_FP32 0
+#define KDA_G_BF16 1
+
+/* flags (all three set = the reference's production bucket) */
+#define KDA_FLAG_GATE_IN_KERNEL 1u    /* g is the raw gate; apply A_log/dt_bias/sigmoid/cumsum */
+#define KDA_FLAG_QK_L2NORM 2u         /* l2-normalise q and k (eps 1e-6) */
+#define KDA_FLAG_BETA_SIGMOID 4u      /* beta holds logits */
+
+typedef struct KdaFwdArgs {
+  /* inputs: [B, T, H, 128], innermost dimension contiguous; strides in ELEMENTS.
+   * A head-shard or sequence-segment view of a larger tensor is passed by strides,
+   * without a copy.  Every row start must be 16-byte aligned. */
+  const void* q;        /* bf16 */
+  const void* k;        /* bf16 */
+  const void* v;        /* bf16 */
+  const void* g;        /* raw gate (or, without KDA_FLAG_GATE_IN_KERNEL, the chunk-local
+                           log2 cumsum); fp32 or bf16 per g_dtype */
+  const float* beta;    /* [B, T, H] fp32 */
+  const float* A_log;   /* [H] fp32; required with KDA_FLAG_GATE_IN_KERNEL */
+  const float* dt_bias; /* [H*128] fp32 or NULL */
+  const float* h0;      /* initial state [B, H, V=128, K=128] fp32 contiguous, or NULL (zeros) */
+  void* o;              /* out: bf16 [B, T, H, 128] */
+  float* ht;            /* out: final state [B, H, 128, 128] fp32 contiguous, or NULL */
+  void* workspace;      /* kda_fwd_workspace_bytes(B, T, H) bytes, 256-byte aligned */
+  float* g_out;         /* optional debug out: log2 cumsum, fp32 [B, T, H, 128] contiguous */
+  float* ainv_out;      /* optional debug out: (I+Akk)^-1, fp32 [B, T, H, 16] contiguous */
+  int32_t B, T, H;
+  int32_t g_dtype;      /* KDA_G_FP32 / KDA_G_BF16 */
+  int64_t q_stride[3];  /* batch, token, head strides of q (elements) */
+  int64_t k_stride[3];
+  int64_t v_stride[3];
+  int64_t g_stride[3];
+  int64_t o_stride[3];
+  int64_t beta_stride[3];
+  float scale;
+  float lower_bound;
+  uint32_t flags;
+  int32_t k2_vsplit;    /* 0 = choose; else number of V slices per (batch, head): 1, 2, 4 or 8 */
+} KdaFwdArgs;
+
+/* Bytes of K1 -> K2 scratch for a (B, T, H) problem: a 256-byte status block
+ * followed by one 25,600-byte record per (batch, head, chunk). */
+size_t kda_fwd_workspace_bytes(int32_t B, int32_t T, int32_t H);
+
+/* Whole forward: clears the status block, launches K1 then K2 on `stream`. */
+int kda_fwd(const KdaFwdArgs* args, void* stream);
+
+/* Stage launches (per-stage timing / profiling, and the sequence-parallel path,
+ * which runs K2 more than once on the records of one K1 pass). */
+int kda_fwd_k1(const KdaFwdArgs* args, void* stream);
+int kda_fwd_k2(const KdaFwdArgs* args, void* stream);
+
+/* State-only K2 pass for the sequence-parallel split: walks the records and
+ * returns only the final state.  With zero_u != 0 the u term is dropped, so that
+ * feeding h0 = I yields the segment's transition matrix. */
+int kda_fwd_k2_state(const KdaFwdArgs* args, int zero_u, void* stream);
+
+/* Synchronising read of the device status word of a workspace (0 = every bounded
+ * wait inside the kernels completed). */
+int kda_fwd_status(const void* workspace, void* stream, int32_t* status_out);
+
+/* Number of kernels the last kda_fwd* call on this thread launched. */
+int kda_last_launch_count(void);
+
+const char* kda_last_error(void);
+
+/* "major.minor" of the library and the SM architecture it was built for. */
+const char* kda_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* KDA_B200_H_ */

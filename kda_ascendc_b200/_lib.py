@@ -1,0 +1,67 @@
+"""ctypes binding of libkda_b200.so (declarations: include/kda_b200.h).
+
+There is no fallback: if the shared library is missing, importing the kernels
+raises, and every entry point refuses tensors that are not on a CUDA device.
+"""
+from __future__ import annotations
+
+import ctypes
+from pathlib import Path
+
+LIB_PATH = Path(__file__).resolve().parent / "libkda_b200.so"
+
+KDA_G_FP32, KDA_G_BF16 = 0, 1
+FLAG_GATE, FLAG_L2NORM, FLAG_BETA_SIGMOID = 1, 2, 4
+
+EXPORTS = (
+    "kda_fwd_workspace_bytes", "kda_fwd", "kda_fwd_k1", "kda_fwd_k2", "kda_fwd_k2_state",
+    "kda_fwd_status", "kda_last_launch_count", "kda_last_error", "kda_version",
+)
+
+
+class KdaFwdArgs(ctypes.Structure):
+    _fields_ = [
+        ("q", ctypes.c_void_p), ("k", ctypes.c_void_p), ("v", ctypes.c_void_p), ("g", ctypes.c_void_p),
+        ("beta", ctypes.c_void_p), ("A_log", ctypes.c_void_p), ("dt_bias", ctypes.c_void_p),
+        ("h0", ctypes.c_void_p), ("o", ctypes.c_void_p), ("ht", ctypes.c_void_p),
+        ("workspace", ctypes.c_void_p), ("g_out", ctypes.c_void_p), ("ainv_out", ctypes.c_void_p),
+        ("B", ctypes.c_int32), ("T", ctypes.c_int32), ("H", ctypes.c_int32), ("g_dtype", ctypes.c_int32),
+        ("q_stride", ctypes.c_int64 * 3), ("k_stride", ctypes.c_int64 * 3), ("v_stride", ctypes.c_int64 * 3),
+        ("g_stride", ctypes.c_int64 * 3), ("o_stride", ctypes.c_int64 * 3), ("beta_stride", ctypes.c_int64 * 3),
+        ("scale", ctypes.c_float), ("lower_bound", ctypes.c_float), ("flags", ctypes.c_uint32),
+        ("k2_vsplit", ctypes.c_int32),
+    ]
+
+
+_lib = None
+
+
+def load() -> ctypes.CDLL:
+    """Load the library once; raise if it has not been built."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not LIB_PATH.exists():
+        raise RuntimeError(
+            "%s is missing: build it with `python -m kda_ascendc_b200.build` "
+            "(there is no CPU or PyTorch fallback for the KDA kernels)" % LIB_PATH)
+    lib = ctypes.CDLL(str(LIB_PATH))
+    lib.kda_fwd_workspace_bytes.restype = ctypes.c_size_t
+    lib.kda_fwd_workspace_bytes.argtypes = [ctypes.c_int32] * 3
+    for name in ("kda_fwd", "kda_fwd_k1", "kda_fwd_k2"):
+        fn = getattr(lib, name)
+        fn.restype = ctypes.c_int
+        fn.argtypes = [ctypes.POINTER(KdaFwdArgs), ctypes.c_void_p]
+    lib.kda_fwd_k2_state.restype = ctypes.c_int
+    lib.kda_fwd_k2_state.argtypes = [ctypes.POINTER(KdaFwdArgs), ctypes.c_int, ctypes.c_void_p]
+    lib.kda_fwd_status.restype = ctypes.c_int
+    lib.kda_fwd_status.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.POINTER(ctypes.c_int32)]
+    lib.kda_last_launch_count.restype = ctypes.c_int
+    lib.kda_last_error.restype = ctypes.c_char_p
+    lib.kda_version.restype = ctypes.c_char_p
+    _lib = lib
+    return lib
+
+
+def last_error() -> str:
+    return load().kda_last_error().decode("utf-8", "replace")

@@ -1,0 +1,187 @@
+// C-ABI layer of libkda_b200.so: argument checks, workspace arithmetic, stage launches.
+// Interface and the reference entry points it stands in for: include/kda_b200.h.
+#include <cstdio>
+#include <cstring>
+
+#include "../../include/kda_b200.h"
+#include "kda_common.cuh"
+#include "kda_kernels.h"
+
+namespace {
+
+thread_local char g_err[512] = "";
+thread_local int g_launches = 0;
+
+int fail(int code, const char* fmt, const char* a = "", long long x = 0, long long y = 0) {
+  snprintf(g_err, sizeof(g_err), fmt, a, x, y);
+  return code;
+}
+
+int check_common(const KdaFwdArgs* a) {
+  if (a == nullptr) return fail(KDA_ERR_INVALID_ARG, "kda: args is NULL%s", "");
+  if (a->B <= 0 || a->T <= 0 || a->H <= 0)
+    return fail(KDA_ERR_INVALID_ARG, "kda: B, T, H must be positive%s (T=%lld, H=%lld)", "", a->T, a->H);
+  if (a->workspace == nullptr) return fail(KDA_ERR_INVALID_ARG, "kda: workspace is NULL%s", "");
+  if (reinterpret_cast<uintptr_t>(a->workspace) % 256 != 0)
+    return fail(KDA_ERR_INVALID_ARG, "kda: workspace must be 256-byte aligned%s", "");
+  return KDA_OK;
+}
+
+bool row_aligned(const void* p, const int64_t s[3], int elem_bytes) {
+  if (reinterpret_cast<uintptr_t>(p) % 16 != 0) return false;
+  for (int i = 0; i < 3; ++i)
+    if ((s[i] * elem_bytes) % 16 != 0) return false;
+  return true;
+}
+
+int check_k1(const KdaFwdArgs* a) {
+  if (int rc = check_common(a)) return rc;
+  if (!a->q || !a->k || !a->v || !a->g || !a->beta)
+    return fail(KDA_ERR_INVALID_ARG, "kda: q, k, v, g and beta are required%s", "");
+  if (a->g_dtype != KDA_G_FP32 && a->g_dtype != KDA_G_BF16)
+    return fail(KDA_ERR_INVALID_ARG, "kda: g_dtype must be KDA_G_FP32 or KDA_G_BF16%s (got %lld)", "", a->g_dtype);
+  if ((a->flags & KDA_FLAG_GATE_IN_KERNEL) && a->A_log == nullptr)
+    return fail(KDA_ERR_INVALID_ARG, "kda: the in-kernel gate requires A_log%s", "");
+  if ((a->flags & KDA_FLAG_GATE_IN_KERNEL) && !(a->lower_bound > -11.0f && a->lower_bound < 0.0f))
+    return fail(KDA_ERR_INVALID_ARG, "kda: lower_bound must be in (-11, 0)%s", "");
+  if (!row_aligned(a->q, a->q_stride, 2) || !row_aligned(a->k, a->k_stride, 2) || !row_aligned(a->v, a->v_stride, 2) ||
+      !row_aligned(a->g, a->g_stride, a->g_dtype == KDA_G_BF16 ? 2 : 4))
+    return fail(KDA_ERR_INVALID_ARG, "kda: q/k/v/g rows must start on 16-byte boundaries%s", "");
+  return KDA_OK;
+}
+
+int check_k2(const KdaFwdArgs* a, bool state_only) {
+  if (int rc = check_common(a)) return rc;
+  if (!state_only && a->o == nullptr) return fail(KDA_ERR_INVALID_ARG, "kda: o is NULL%s", "");
+  if (a->k2_vsplit != 0 && a->k2_vsplit != 1 && a->k2_vsplit != 2 && a->k2_vsplit != 4 && a->k2_vsplit != 8)
+    return fail(KDA_ERR_INVALID_ARG, "kda: k2_vsplit must be 0, 1, 2, 4 or 8%s (got %lld)", "", a->k2_vsplit);
+  return KDA_OK;
+}
+
+int pick_vsplit(const KdaFwdArgs* a) {
+  if (a->k2_vsplit != 0) return a->k2_vsplit;
+  int dev = 0, sms = 148;
+  if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  const long long bh = static_cast<long long>(a->B) * a->H;
+  // as many state slices as still give every CTA an SM of its own
+  if (bh * 8 <= sms) return 8;
+  if (bh * 4 <= sms) return 4;
+  if (bh * 2 <= sms + sms / 2) return 2;
+  return 1;
+}
+
+int* status_ptr(const KdaFwdArgs* a) { return static_cast<int*>(a->workspace); }
+uint8_t* rec_ptr(const KdaFwdArgs* a) { return static_cast<uint8_t*>(a->workspace) + kda::WS_HEADER_BYTES; }
+
+int do_k1(const KdaFwdArgs* a, cudaStream_t st) {
+  kda::K1Params p;
+  memset(&p, 0, sizeof(p));
+  p.q = static_cast<const __nv_bfloat16*>(a->q);
+  p.k = static_cast<const __nv_bfloat16*>(a->k);
+  p.v = static_cast<const __nv_bfloat16*>(a->v);
+  p.g = a->g;
+  p.beta = a->beta;
+  p.A_log = a->A_log;
+  p.dt_bias = a->dt_bias;
+  p.rec = rec_ptr(a);
+  p.status = status_ptr(a);
+  p.g_out = a->g_out;
+  p.ainv_out = a->ainv_out;
+  p.B = a->B; p.T = a->T; p.H = a->H; p.NT = (a->T + kda::BT - 1) / kda::BT;
+  for (int i = 0; i < 3; ++i) {
+    p.q_s[i] = a->q_stride[i]; p.k_s[i] = a->k_stride[i]; p.v_s[i] = a->v_stride[i];
+    p.g_s[i] = a->g_stride[i]; p.beta_s[i] = a->beta_stride[i];
+  }
+  p.scale = a->scale;
+  p.lower_bound = a->lower_bound;
+  p.flags = a->flags;
+  // 2^g may be factored as 2^(g-g_mid) * 2^(g_mid) only while no factor can underflow:
+  // 16 tokens * |lower_bound| * RCP_LN2 must stay inside the fp32 exponent range.
+  const bool fast_exp = (a->flags & KDA_FLAG_GATE_IN_KERNEL) && (16.0f * -a->lower_bound * kda::RCP_LN2 <= 120.0f);
+  cudaError_t e = kda::launch_k1(p, a->g_dtype == KDA_G_BF16, fast_exp, st);
+  if (e != cudaSuccess) return fail(KDA_ERR_CUDA, "kda: K1 launch failed: %s", cudaGetErrorString(e));
+  ++g_launches;
+  return KDA_OK;
+}
+
+int do_k2(const KdaFwdArgs* a, bool state_only, int zero_u, cudaStream_t st) {
+  kda::K2Params p;
+  memset(&p, 0, sizeof(p));
+  p.rec = rec_ptr(a);
+  p.h0 = a->h0;
+  p.o = static_cast<__nv_bfloat16*>(a->o);
+  p.ht = a->ht;
+  p.status = status_ptr(a);
+  p.B = a->B; p.T = a->T; p.H = a->H; p.NT = (a->T + kda::BT - 1) / kda::BT;
+  for (int i = 0; i < 3; ++i) p.o_s[i] = a->o_stride[i];
+  p.scale = a->scale;
+  p.zero_u = zero_u;
+  cudaError_t e = kda::launch_k2(p, pick_vsplit(a), state_only, st);
+  if (e != cudaSuccess) return fail(KDA_ERR_CUDA, "kda: K2 launch failed: %s", cudaGetErrorString(e));
+  ++g_launches;
+  return KDA_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+size_t kda_fwd_workspace_bytes(int32_t B, int32_t T, int32_t H) {
+  if (B <= 0 || T <= 0 || H <= 0) return 0;
+  const size_t nt = (static_cast<size_t>(T) + kda::BT - 1) / kda::BT;
+  return kda::WS_HEADER_BYTES + static_cast<size_t>(B) * H * nt * kda::REC_BYTES;
+}
+
+int kda_fwd(const KdaFwdArgs* a, void* stream) {
+  g_launches = 0;
+  if (int rc = check_k1(a)) return rc;
+  if (int rc = check_k2(a, false)) return rc;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  cudaError_t e = cudaMemsetAsync(a->workspace, 0, kda::WS_HEADER_BYTES, st);
+  if (e != cudaSuccess) return fail(KDA_ERR_CUDA, "kda: status clear failed: %s", cudaGetErrorString(e));
+  if (int rc = do_k1(a, st)) return rc;
+  return do_k2(a, false, 0, st);
+}
+
+int kda_fwd_k1(const KdaFwdArgs* a, void* stream) {
+  g_launches = 0;
+  if (int rc = check_k1(a)) return rc;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  cudaError_t e = cudaMemsetAsync(a->workspace, 0, kda::WS_HEADER_BYTES, st);
+  if (e != cudaSuccess) return fail(KDA_ERR_CUDA, "kda: status clear failed: %s", cudaGetErrorString(e));
+  return do_k1(a, st);
+}
+
+int kda_fwd_k2(const KdaFwdArgs* a, void* stream) {
+  g_launches = 0;
+  if (int rc = check_k2(a, false)) return rc;
+  return do_k2(a, false, 0, static_cast<cudaStream_t>(stream));
+}
+
+int kda_fwd_k2_state(const KdaFwdArgs* a, int zero_u, void* stream) {
+  g_launches = 0;
+  if (int rc = check_k2(a, true)) return rc;
+  if (a->ht == nullptr) return fail(KDA_ERR_INVALID_ARG, "kda: the state-only pass needs ht%s", "");
+  return do_k2(a, true, zero_u, static_cast<cudaStream_t>(stream));
+}
+
+int kda_fwd_status(const void* workspace, void* stream, int32_t* status_out) {
+  if (workspace == nullptr || status_out == nullptr)
+    return fail(KDA_ERR_INVALID_ARG, "kda: workspace and status_out are required%s", "");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  int32_t v = 0;
+  cudaError_t e = cudaMemcpyAsync(&v, workspace, sizeof(v), cudaMemcpyDeviceToHost, st);
+  if (e == cudaSuccess) e = cudaStreamSynchronize(st);
+  if (e != cudaSuccess) return fail(KDA_ERR_CUDA, "kda: status read failed: %s", cudaGetErrorString(e));
+  *status_out = v;
+  if (v != 0) return fail(KDA_ERR_DEVICE_STATUS, "kda: a bounded device-side wait gave up%s (status %lld)", "", v);
+  return KDA_OK;
+}
+
+int kda_last_launch_count(void) { return g_launches; }
+
+const char* kda_last_error(void) { return g_err; }
+
+const char* kda_version(void) { return "0.1 sm_100a"; }
+
+}  // extern "C"

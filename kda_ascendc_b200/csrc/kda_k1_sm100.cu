@@ -1,0 +1,413 @@
+// K1: intra-chunk stage of the KDA forward, one CTA (128 threads) per
+// (batch, head, chunk of 16 tokens).  sm_100a.
+//
+// Replaces kda_bt16_kernel_k1 of the reference (src/kda_bt16/kernels.py:53-184) and
+// follows the arithmetic and rounding points of the reference's torch chunk
+// implementation (tests/test_torch_reference.py:77-173):
+//   1. gate pre-pass: beta sigmoid, q/k l2-norm (eps 1e-6, result rounded to bf16),
+//      gate = lower_bound*sigmoid(exp(A_log)*(g+dt_bias))*RCP_LN2, chunk-local cumsum
+//   2. Aqk = scale*tril((qhat 2^gm)(khat 2^-gm)^T), Akk = tril_-1((khat 2^gm)(khat 2^-gm)^T)*beta_i
+//      with gm = g - g[mid]; tensor-core MMAs on hi/lo bf16 splits of the fp32 operands
+//      (three partial products, fp32 accumulate => ~2^-16 relative, "fp32-like")
+//   3. X = (I + Akk)^-1 by forward substitution, fp32, one lane per column of X
+//   4. w = X (khat beta 2^g)   (bf16 out),   u = X (v beta)   (fp32 out, split-bf16 MMAs)
+// and additionally pre-computes what the reference's Triton K2 re-derives every step
+// (src/kda_bt16/kernels.py:255-259,271,286-287): qg = bf16(qhat 2^g),
+// kg = khat 2^(g_last-g) as a hi/lo bf16 pair, dec = 2^g_last -- the arrangement of
+// the reference's Ascend pipeline (python/kda_ascendc_v1/api.py:890-897).
+//
+// Data movement: the four 16x128 input tiles arrive by per-row bulk (TMA) copies that
+// complete on one mbarrier (rows may be strided: head-shard views need no copy); the
+// 25,600-byte chunk record leaves by three bulk stores.  See kda_common.cuh for the
+// record layout.
+#include "kda_common.cuh"
+#include "kda_kernels.h"
+
+namespace kda {
+
+// shared-memory map (bytes)
+constexpr int S_QG = 0, S_KGH = 4096, S_KGL = 8192, S_AQK = 12288, S_DEC = 12800;  // -> record[4096, 17408)
+constexpr int S_GRAM = 13312;
+constexpr int S_QGH = S_GRAM, S_KQH = S_GRAM + 4096, S_KQL = S_GRAM + 8192, S_KNH = S_GRAM + 12288,
+              S_KNL = S_GRAM + 16384;
+constexpr int S_W = S_GRAM, S_UF = S_GRAM + 4096;  // reuse of the Gram tiles once the Grams are done
+constexpr int S_IN = S_GRAM + 20480;               // 33792
+constexpr int S_Q = S_IN, S_K = S_IN + 4096, S_V = S_IN + 8192, S_G = S_IN + 12288;
+constexpr int S_KBH = S_IN, S_VBH = S_IN + 4096, S_VBL = S_IN + 8192;  // reuse of q/k/v tiles after they are read
+
+template <bool G_BF16>
+struct K1Smem {
+  static constexpr int G_BYTES = G_BF16 ? 4096 : 8192;
+  static constexpr int SMALL = S_G + G_BYTES;
+  static constexpr int L = SMALL;             // fp32 [16][17]
+  static constexpr int XH = SMALL + 1088;     // bf16 [16][16]
+  static constexpr int XL = XH + 512;
+  static constexpr int RNQ = XL + 512;        // fp32 [16]
+  static constexpr int RNK = RNQ + 64;
+  static constexpr int BETA = RNK + 64;
+  static constexpr int MBAR = BETA + 64;      // 8 bytes
+  static constexpr int FLAG = MBAR + 8;
+  static constexpr int TOTAL = FLAG + 8;
+};
+
+template <bool G_BF16, bool FAST_EXP>
+__global__ void __launch_bounds__(128, 4) kda_k1_kernel(const K1Params p) {
+  extern __shared__ __align__(128) uint8_t smem[];
+  using SM = K1Smem<G_BF16>;
+  const int tid = threadIdx.x;
+  const int lane = tid & 31;
+  const int warp = tid >> 5;
+
+  // block -> (b, n, h) with h fastest: CTAs that run together read one contiguous span of tokens
+  const int h = blockIdx.x % p.H;
+  const int bn = blockIdx.x / p.H;
+  const int n_chunk = bn % p.NT;
+  const int b = bn / p.NT;
+  const int t0 = n_chunk * BT;
+  const int nvalid = min(BT, p.T - t0);
+  const size_t rec_idx = (static_cast<size_t>(b) * p.H + h) * p.NT + n_chunk;
+  uint8_t* rec = p.rec + rec_idx * REC_BYTES;
+
+  const uint32_t sbase = smem_u32(smem);
+  const uint32_t mbar = sbase + SM::MBAR;
+  float* sL = reinterpret_cast<float*>(smem + SM::L);
+  float* sRnq = reinterpret_cast<float*>(smem + SM::RNQ);
+  float* sRnk = reinterpret_cast<float*>(smem + SM::RNK);
+  float* sBeta = reinterpret_cast<float*>(smem + SM::BETA);
+  volatile int* sFlag = reinterpret_cast<volatile int*>(smem + SM::FLAG);
+
+  if (tid == 0) {
+    mbar_init(mbar, 1);
+    *sFlag = 0;
+    fence_mbar_init();
+  }
+  __syncthreads();
+
+  // ---- stage the inputs: one bulk copy per (tensor, row) -------------------
+  constexpr uint32_t ROW_BYTES = D * 2;
+  constexpr uint32_t G_ROW_BYTES = G_BF16 ? D * 2 : D * 4;
+  if (tid == 0) mbar_arrive_expect_tx(mbar, nvalid * (3 * ROW_BYTES + G_ROW_BYTES));
+  if (tid < 64) {
+    const int which = tid >> 4, r = tid & 15;
+    const int64_t tok = t0 + r;
+    if (r < nvalid) {
+      if (which == 0)
+        bulk_g2s(sbase + S_Q + r * ROW_BYTES, p.q + b * p.q_s[0] + tok * p.q_s[1] + h * p.q_s[2], ROW_BYTES, mbar);
+      else if (which == 1)
+        bulk_g2s(sbase + S_K + r * ROW_BYTES, p.k + b * p.k_s[0] + tok * p.k_s[1] + h * p.k_s[2], ROW_BYTES, mbar);
+      else if (which == 2)
+        bulk_g2s(sbase + S_V + r * ROW_BYTES, p.v + b * p.v_s[0] + tok * p.v_s[1] + h * p.v_s[2], ROW_BYTES, mbar);
+      else {
+        const int64_t eoff = b * p.g_s[0] + tok * p.g_s[1] + h * p.g_s[2];
+        const uint8_t* src = static_cast<const uint8_t*>(p.g) + eoff * (G_BF16 ? 2 : 4);
+        bulk_g2s(sbase + S_G + r * G_ROW_BYTES, src, G_ROW_BYTES, mbar);
+      }
+    } else {
+      // rows past the end of the sequence: zero operands (plain stores, untouched by the copies)
+      const int off = (which == 0 ? S_Q : which == 1 ? S_K : which == 2 ? S_V : S_G) +
+                      r * (which == 3 ? G_ROW_BYTES : ROW_BYTES);
+      const int nb = which == 3 ? G_ROW_BYTES : ROW_BYTES;
+      for (int i = 0; i < nb; i += 16) *reinterpret_cast<uint4*>(smem + off + i) = make_uint4(0, 0, 0, 0);
+    }
+  } else if (tid < 80) {
+    const int r = tid - 64;
+    float bv = 0.f;
+    if (r < nvalid) {
+      bv = p.beta[b * p.beta_s[0] + static_cast<int64_t>(t0 + r) * p.beta_s[1] + h * p.beta_s[2]];
+      if (p.flags & 4u) bv = 1.0f / (1.0f + __expf(-bv));
+    }
+    sBeta[r] = bv;
+  }
+  const bool use_gate = (p.flags & 1u) != 0;
+  const bool use_l2 = (p.flags & 2u) != 0;
+  float expA = 1.f, bias = 0.f;
+  if (use_gate) {
+    expA = expf(p.A_log[h]);
+    if (p.dt_bias != nullptr) bias = p.dt_bias[h * D + tid];
+  }
+
+  bool ok = true;
+  if (lane == 0) ok = mbar_wait_bounded(mbar, 0, sFlag);
+  if (!ok) *sFlag = 1;
+  __syncthreads();
+  if (*sFlag != 0) {
+    // a copy never completed: report, give in-flight copies one more bounded wait, leave
+    if (tid == 0) {
+      atomicExch(p.status, ST_K1_LOAD_TIMEOUT);
+      mbar_wait_bounded(mbar, 0, nullptr);
+    }
+    __syncthreads();
+    return;
+  }
+
+  // ---- phase A: row norms (8 threads per row) -------------------------------
+  {
+    const int r = tid >> 3, seg = tid & 7;
+    float rq = 1.f, rk = 1.f;
+    if (use_l2) {
+      float sq = 0.f, sk = 0.f;
+#pragma unroll
+      for (int hseg = 0; hseg < 2; ++hseg) {
+        const uint4 a = *reinterpret_cast<const uint4*>(smem + S_Q + r * 256 + seg * 32 + hseg * 16);
+        const uint4 c = *reinterpret_cast<const uint4*>(smem + S_K + r * 256 + seg * 32 + hseg * 16);
+        const uint32_t aw[4] = {a.x, a.y, a.z, a.w}, cw[4] = {c.x, c.y, c.z, c.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          float x0 = bf16_lo_to_f32(aw[i]), x1 = bf16_hi_to_f32(aw[i]);
+          float y0 = bf16_lo_to_f32(cw[i]), y1 = bf16_hi_to_f32(cw[i]);
+          sq = fmaf(x0, x0, sq); sq = fmaf(x1, x1, sq);
+          sk = fmaf(y0, y0, sk); sk = fmaf(y1, y1, sk);
+        }
+      }
+#pragma unroll
+      for (int m = 1; m < 8; m <<= 1) {
+        sq += __shfl_xor_sync(0xffffffffu, sq, m);
+        sk += __shfl_xor_sync(0xffffffffu, sk, m);
+      }
+      rq = 1.0f / sqrtf(sq + L2NORM_EPS);
+      rk = 1.0f / sqrtf(sk + L2NORM_EPS);
+    }
+    if (seg == 0) { sRnq[r] = rq; sRnk[r] = rk; }
+  }
+  __syncthreads();
+
+  // ---- phase B: one column per thread: gate, cumsum, gated operands ---------
+  const int c = tid;
+  float kb[BT], vb[BT];
+  {
+    float gv[BT];
+    if (use_gate) {
+      float run = 0.f;
+#pragma unroll
+      for (int r = 0; r < BT; ++r) {
+        float x;
+        if (G_BF16) x = __uint_as_float(static_cast<uint32_t>(*reinterpret_cast<const unsigned short*>(smem + S_G + (r * D + c) * 2)) << 16);
+        else x = *reinterpret_cast<const float*>(smem + S_G + (r * D + c) * 4);
+        const float z = expA * (x + bias);
+        const float s = 1.0f / (1.0f + __expf(-z));
+        float gate = (p.lower_bound * s) * RCP_LN2;
+        if (r >= nvalid) gate = 0.f;
+        run += gate;
+        gv[r] = run;
+      }
+    } else {
+      float last = 0.f;
+#pragma unroll
+      for (int r = 0; r < BT; ++r) {
+        float x;
+        if (G_BF16) x = __uint_as_float(static_cast<uint32_t>(*reinterpret_cast<const unsigned short*>(smem + S_G + (r * D + c) * 2)) << 16);
+        else x = *reinterpret_cast<const float*>(smem + S_G + (r * D + c) * 4);
+        if (r < nvalid) last = x;
+        gv[r] = last;
+      }
+    }
+    const int mid = min(BT / 2, nvalid - 1);
+    float gmid = gv[0];
+#pragma unroll
+    for (int r = 1; r <= BT / 2; ++r) gmid = (r == mid) ? gv[r] : gmid;
+    const float glast = gv[BT - 1];
+    const float c1 = ex2f(gmid), c2 = ex2f(glast - gmid);
+    *reinterpret_cast<float*>(smem + S_DEC + c * 4) = ex2f(glast);
+
+    if (p.g_out != nullptr) {
+#pragma unroll
+      for (int r = 0; r < BT; ++r)
+        if (r < nvalid) p.g_out[((static_cast<size_t>(b) * p.T + t0 + r) * p.H + h) * D + c] = gv[r];
+    }
+
+#pragma unroll
+    for (int r = 0; r < BT; ++r) {
+      const uint32_t off = swz_off(r, c);
+      const float qraw = __uint_as_float(static_cast<uint32_t>(*reinterpret_cast<const unsigned short*>(smem + S_Q + (r * D + c) * 2)) << 16);
+      const float kraw = __uint_as_float(static_cast<uint32_t>(*reinterpret_cast<const unsigned short*>(smem + S_K + (r * D + c) * 2)) << 16);
+      const float vraw = __uint_as_float(static_cast<uint32_t>(*reinterpret_cast<const unsigned short*>(smem + S_V + (r * D + c) * 2)) << 16);
+      const float qn = use_l2 ? bf16_round(qraw * sRnq[r]) : qraw;
+      const float kn = use_l2 ? bf16_round(kraw * sRnk[r]) : kraw;
+      const float br = sBeta[r];
+      const float e = ex2f(gv[r] - gmid);
+      const float en = ex2f(gmid - gv[r]);
+      float eg, ekg;
+      if (FAST_EXP) { eg = e * c1; ekg = en * c2; }
+      else { eg = ex2f(gv[r]); ekg = ex2f(glast - gv[r]); }
+
+      const float QG = qn * e, KQ = kn * e, KN = kn * en, KG = kn * ekg;
+      *reinterpret_cast<unsigned short*>(smem + S_QGH + off) = bf16_bits(QG);
+      float hi = bf16_round(KQ);
+      *reinterpret_cast<unsigned short*>(smem + S_KQH + off) = bf16_bits(hi);
+      *reinterpret_cast<unsigned short*>(smem + S_KQL + off) = bf16_bits(KQ - hi);
+      hi = bf16_round(KN);
+      *reinterpret_cast<unsigned short*>(smem + S_KNH + off) = bf16_bits(hi);
+      *reinterpret_cast<unsigned short*>(smem + S_KNL + off) = bf16_bits(KN - hi);
+      *reinterpret_cast<unsigned short*>(smem + S_QG + off) = bf16_bits(qn * eg);
+      hi = bf16_round(KG);
+      *reinterpret_cast<unsigned short*>(smem + S_KGH + off) = bf16_bits(hi);
+      *reinterpret_cast<unsigned short*>(smem + S_KGL + off) = bf16_bits(KG - hi);
+      kb[r] = (kn * br) * eg;
+      vb[r] = vraw * br;
+    }
+  }
+  __syncthreads();  // every thread has read its q/k/v/g column: the input tiles may be overwritten
+
+#pragma unroll
+  for (int r = 0; r < BT; ++r) {
+    const uint32_t off = swz_off(r, c);
+    *reinterpret_cast<unsigned short*>(smem + S_KBH + off) = bf16_bits(kb[r]);
+    const float hi = bf16_round(vb[r]);
+    *reinterpret_cast<unsigned short*>(smem + S_VBH + off) = bf16_bits(hi);
+    *reinterpret_cast<unsigned short*>(smem + S_VBL + off) = bf16_bits(vb[r] - hi);
+  }
+
+  // ---- phase C: Grams on the tensor cores (one 16x8 output tile per warp) ----
+  const int gq = lane >> 2, tq = lane & 3;
+  {
+    const int mt = warp >> 1;  // 0: Aqk, 1: Akk
+    const int nt = warp & 1;   // column block j in [8nt, 8nt+8)
+    const uint32_t a_hi = sbase + (mt == 0 ? S_QGH : S_KQH);
+    const uint32_t a_lo = sbase + S_KQL;
+    const int arow = (lane & 7) + ((lane >> 3) & 1) * 8, acol = (lane >> 4) * 8;
+    const int brow = nt * 8 + (lane & 7), bcol = ((lane >> 3) & 1) * 8;
+    float acc0[4] = {0, 0, 0, 0}, acc1[4] = {0, 0, 0, 0}, acc2[4] = {0, 0, 0, 0};
+#pragma unroll
+    for (int ks = 0; ks < 8; ++ks) {
+      uint32_t ah[4], bh0, bh1, bl0, bl1;
+      ldsm_x4(a_hi + swz_off(arow, ks * 16 + acol), ah[0], ah[1], ah[2], ah[3]);
+      ldsm_x2(sbase + S_KNH + swz_off(brow, ks * 16 + bcol), bh0, bh1);
+      ldsm_x2(sbase + S_KNL + swz_off(brow, ks * 16 + bcol), bl0, bl1);
+      mma_bf16(acc0, ah, bh0, bh1);
+      mma_bf16(acc1, ah, bl0, bl1);
+      if (mt == 1) {
+        uint32_t al[4];
+        ldsm_x4(a_lo + swz_off(arow, ks * 16 + acol), al[0], al[1], al[2], al[3]);
+        mma_bf16(acc2, al, bh0, bh1);
+      }
+    }
+#pragma unroll
+    for (int e = 0; e < 4; ++e) acc0[e] += acc1[e] + acc2[e];
+    const int j0 = nt * 8 + tq * 2;
+    if (mt == 0) {
+#pragma unroll
+      for (int hrow = 0; hrow < 2; ++hrow) {
+        const int i = gq + hrow * 8;
+        const float v0 = (i >= j0) ? acc0[hrow * 2] * p.scale : 0.f;
+        const float v1 = (i >= j0 + 1) ? acc0[hrow * 2 + 1] * p.scale : 0.f;
+        *reinterpret_cast<uint32_t*>(smem + S_AQK + (i * 16 + j0) * 2) = pack_bf16(v0, v1);
+      }
+    } else {
+#pragma unroll
+      for (int hrow = 0; hrow < 2; ++hrow) {
+        const int i = gq + hrow * 8;
+        const float bi = sBeta[i];
+        sL[i * 17 + j0] = (i > j0) ? acc0[hrow * 2] * bi : 0.f;
+        sL[i * 17 + j0 + 1] = (i > j0 + 1) ? acc0[hrow * 2 + 1] * bi : 0.f;
+      }
+    }
+  }
+  __syncthreads();
+
+  // ---- phase D: X = (I + L)^-1, lane j of warp 0 owns column j ---------------
+  if (warp == 0 && lane < 16) {
+    float x[BT];
+#pragma unroll
+    for (int i = 0; i < BT; ++i) x[i] = (i == lane) ? 1.f : 0.f;
+#pragma unroll
+    for (int m = 0; m < BT - 1; ++m) {
+      const float xm = x[m];
+#pragma unroll
+      for (int i = m + 1; i < BT; ++i) x[i] = fmaf(-sL[i * 17 + m], xm, x[i]);
+    }
+#pragma unroll
+    for (int i = 0; i < BT; ++i) {
+      const float hi = bf16_round(x[i]);
+      *reinterpret_cast<unsigned short*>(smem + SM::XH + (i * 16 + lane) * 2) = bf16_bits(hi);
+      *reinterpret_cast<unsigned short*>(smem + SM::XL + (i * 16 + lane) * 2) = bf16_bits(x[i] - hi);
+    }
+    if (p.ainv_out != nullptr) {
+#pragma unroll
+      for (int i = 0; i < BT; ++i)
+        if (i < nvalid) p.ainv_out[((static_cast<size_t>(b) * p.T + t0 + i) * p.H + h) * BT + lane] = x[i];
+    }
+  }
+  __syncthreads();
+
+  // ---- phase E: uT = (v beta)^T X^T (fp32-like), w = X (khat beta 2^g) (bf16) ----
+  {
+    // X as B operand of uT (stored [N=i][K=m]) and as A operand of w (row-major [M=i][K=m])
+    uint32_t xbh[4], xbl[4], xah[4], xal[4];
+    {
+      const int row = (lane & 7) + (lane >> 4) * 8, col = ((lane >> 3) & 1) * 8;
+      ldsm_x4(sbase + SM::XH + (row * 16 + col) * 2, xbh[0], xbh[1], xbh[2], xbh[3]);
+      ldsm_x4(sbase + SM::XL + (row * 16 + col) * 2, xbl[0], xbl[1], xbl[2], xbl[3]);
+      const int row2 = (lane & 7) + ((lane >> 3) & 1) * 8, col2 = (lane >> 4) * 8;
+      ldsm_x4(sbase + SM::XH + (row2 * 16 + col2) * 2, xah[0], xah[1], xah[2], xah[3]);
+      ldsm_x4(sbase + SM::XL + (row2 * 16 + col2) * 2, xal[0], xal[1], xal[2], xal[3]);
+    }
+#pragma unroll
+    for (int vi = 0; vi < 2; ++vi) {
+      const int vt = warp * 2 + vi;
+      const int tok = (lane & 7) + (lane >> 4) * 8, vcol = vt * 16 + ((lane >> 3) & 1) * 8;
+      uint32_t avh[4], avl[4];
+      ldsm_x4_t(sbase + S_VBH + swz_off(tok, vcol), avh[0], avh[1], avh[2], avh[3]);
+      ldsm_x4_t(sbase + S_VBL + swz_off(tok, vcol), avl[0], avl[1], avl[2], avl[3]);
+#pragma unroll
+      for (int j = 0; j < 2; ++j) {
+        float acc[4] = {0, 0, 0, 0}, accl[4] = {0, 0, 0, 0};
+        mma_bf16(acc, avh, xbh[2 * j], xbh[2 * j + 1]);
+        mma_bf16(accl, avl, xbh[2 * j], xbh[2 * j + 1]);
+        mma_bf16(accl, avh, xbl[2 * j], xbl[2 * j + 1]);
+        *reinterpret_cast<float4*>(smem + S_UF + ((vt * 2 + j) * 32 + lane) * 16) =
+            make_float4(acc[0] + accl[0], acc[1] + accl[1], acc[2] + accl[2], acc[3] + accl[3]);
+      }
+    }
+#pragma unroll
+    for (int ni = 0; ni < 2; ++ni) {
+      const int n0 = warp * 32 + ni * 16;
+      const int tok = (lane & 7) + ((lane >> 3) & 1) * 8, kcol = n0 + (lane >> 4) * 8;
+      uint32_t bk[4];
+      ldsm_x4_t(sbase + S_KBH + swz_off(tok, kcol), bk[0], bk[1], bk[2], bk[3]);
+#pragma unroll
+      for (int j = 0; j < 2; ++j) {
+        float acc[4] = {0, 0, 0, 0};
+        mma_bf16(acc, xah, bk[2 * j], bk[2 * j + 1]);
+        mma_bf16(acc, xal, bk[2 * j], bk[2 * j + 1]);
+        const int kc = n0 + j * 8 + tq * 2;
+        *reinterpret_cast<uint32_t*>(smem + S_W + swz_off(gq, kc)) = pack_bf16(acc[0], acc[1]);
+        *reinterpret_cast<uint32_t*>(smem + S_W + swz_off(gq + 8, kc)) = pack_bf16(acc[2], acc[3]);
+      }
+    }
+  }
+
+  // ---- write the record: three bulk stores ----------------------------------
+  fence_proxy_async();
+  __syncthreads();
+  if (tid == 0) {
+    bulk_s2g(rec + REC_W, sbase + S_W, TILE_BYTES);
+    bulk_s2g(rec + REC_QG, sbase + S_QG, REC_SHARED_BYTES - REC_QG);
+    bulk_s2g(rec + REC_U, sbase + S_UF, REC_BYTES - REC_U);
+    bulk_commit();
+    bulk_wait_read_all();
+  }
+}
+
+template <bool G_BF16, bool FAST_EXP>
+static cudaError_t launch_k1_t(const K1Params& p, int nblocks, cudaStream_t stream) {
+  constexpr int smem_bytes = K1Smem<G_BF16>::TOTAL;
+  static bool configured[64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 64 && !configured[dev]) {
+    cudaError_t e = cudaFuncSetAttribute(kda_k1_kernel<G_BF16, FAST_EXP>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         smem_bytes);
+    if (e != cudaSuccess) return e;
+    configured[dev] = true;
+  }
+  kda_k1_kernel<G_BF16, FAST_EXP><<<nblocks, 128, smem_bytes, stream>>>(p);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_k1(const K1Params& p, bool g_bf16, bool fast_exp, cudaStream_t stream) {
+  const int nblocks = p.B * p.NT * p.H;
+  if (g_bf16) return fast_exp ? launch_k1_t<true, true>(p, nblocks, stream) : launch_k1_t<true, false>(p, nblocks, stream);
+  return fast_exp ? launch_k1_t<false, true>(p, nblocks, stream) : launch_k1_t<false, false>(p, nblocks, stream);
+}
+
+}  // namespace kda

@@ -1,0 +1,43 @@
+// Internal launch interface between the C-ABI layer and the two kernels.
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace kda {
+
+struct K1Params {
+  const __nv_bfloat16* q;
+  const __nv_bfloat16* k;
+  const __nv_bfloat16* v;
+  const void* g;
+  const float* beta;
+  const float* A_log;
+  const float* dt_bias;
+  uint8_t* rec;      // first chunk record (workspace + header)
+  int* status;       // device status word
+  float* g_out;      // optional
+  float* ainv_out;   // optional
+  int B, T, H, NT;
+  int64_t q_s[3], k_s[3], v_s[3], g_s[3], beta_s[3];  // element strides (batch, token, head)
+  float scale, lower_bound;
+  uint32_t flags;
+};
+
+struct K2Params {
+  const uint8_t* rec;
+  const float* h0;   // [B,H,128,128] or null
+  __nv_bfloat16* o;  // may be null in state-only mode
+  float* ht;         // may be null
+  int* status;
+  int B, T, H, NT;
+  int64_t o_s[3];
+  float scale;
+  int zero_u;        // state-only mode: drop the u term
+};
+
+cudaError_t launch_k1(const K1Params& p, bool g_bf16, bool fast_exp, cudaStream_t stream);
+// vsplit in {1,2,4,8}: CTAs per (batch, head); each owns 128/vsplit rows of the state.
+cudaError_t launch_k2(const K2Params& p, int vsplit, bool state_only, cudaStream_t stream);
+
+}  // namespace kda
