@@ -82,7 +82,7 @@ typedef struct KdaFwdArgs {
 } KdaFwdArgs;
 
 /* Bytes of K1 -> K2 scratch for a (B, T, H) problem: a 256-byte status block
- * followed by one 25,600-byte record per (batch, head, chunk). */
+ * followed by one 26,112-byte record per (batch, head, chunk). */
 size_t kda_fwd_workspace_bytes(int32_t B, int32_t T, int32_t H);
 
 /* Whole forward: clears the status block, launches K1 then K2 on `stream`. */

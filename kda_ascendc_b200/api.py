@@ -28,7 +28,7 @@ from ._lib import KdaFwdArgs
 
 BT = 16
 HEAD_DIM = 128
-REC_BYTES = 25600
+REC_BYTES = 26112
 WS_HEADER_BYTES = 256
 
 _WORKSPACE_CACHE: dict[tuple, torch.Tensor] = {}

@@ -1,6 +1,6 @@
 // Shared device helpers and the K1 -> K2 chunk-record contract (sm_100a only).
 //
-// A "chunk record" is the 25,600-byte block K1 writes and K2 reads for one
+// A "chunk record" is the 26,112-byte block K1 writes and K2 reads for one
 // (batch, head, chunk-of-16-tokens).  Records are chunk-major:
 //   record index c = (b * H + h) * NT + n        (same order as the reference's
 //   chunk-major packing, python/kda_ascendc_v1/layout.py:17-25)
@@ -12,9 +12,10 @@
 //   4096    4096   qg   bf16 [16][128]  = bf16(qhat * 2^g)
 //   8192    4096   kg_h bf16 [16][128]  \ hi/lo split of khat * 2^(g_last - g)
 //   12288   4096   kg_l bf16 [16][128]  /
-//   16384   512    Aqk  bf16 [16 i][16 j] row-major, lower triangle incl. diag
-//   16896   512    dec  fp32 [128]      = 2^(g_last)
-//   17408   8192   uT   fp32, mma-fragment order [8 vtile][2 ntile][32 lane][4]
+//   16384   512    Aqk_h bf16 [16 i][16 j] row-major \ hi/lo split of the scaled lower
+//   16896   512    Aqk_l bf16 [16][16]               / triangle (incl. diagonal)
+//   17408   512    dec  fp32 [128]      = 2^(g_last)
+//   17920   8192   uT   fp32, mma-fragment order [8 vtile][2 ntile][32 lane][4]
 //
 // Swizzled bf16 tile: element (r, c) of a [16][128] tile lives at byte
 //   r*256 + ((((c>>3) ^ (r&7)) << 4) | ((c&7) << 1))
@@ -36,11 +37,12 @@ constexpr int REC_QG = 4096;
 constexpr int REC_KGH = 8192;
 constexpr int REC_KGL = 12288;
 constexpr int REC_AQK = 16384;
-constexpr int REC_DEC = 16896;
-constexpr int REC_U = 17408;
-constexpr int REC_SHARED_BYTES = 17408;  // everything every V-slice needs
+constexpr int REC_AQL = 16896;
+constexpr int REC_DEC = 17408;
+constexpr int REC_U = 17920;
+constexpr int REC_SHARED_BYTES = 17920;  // everything every V-slice needs
 constexpr int REC_U_TILE_BYTES = 1024;   // one 16-row V tile of uT
-constexpr int REC_BYTES = 25600;
+constexpr int REC_BYTES = 26112;
 constexpr int WS_HEADER_BYTES = 256;     // status block at the start of the workspace
 
 // status codes written to workspace[0] by a kernel that gave up on a wait

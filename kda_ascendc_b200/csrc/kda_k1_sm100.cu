@@ -18,7 +18,7 @@
 //
 // Data movement: the four 16x128 input tiles arrive by per-row bulk (TMA) copies that
 // complete on one mbarrier (rows may be strided: head-shard views need no copy); the
-// 25,600-byte chunk record leaves by three bulk stores.  See kda_common.cuh for the
+// 26,112-byte chunk record leaves by three bulk stores.  See kda_common.cuh for the
 // record layout.
 #include "kda_common.cuh"
 #include "kda_kernels.h"
@@ -26,12 +26,12 @@
 namespace kda {
 
 // shared-memory map (bytes)
-constexpr int S_QG = 0, S_KGH = 4096, S_KGL = 8192, S_AQK = 12288, S_DEC = 12800;  // -> record[4096, 17408)
-constexpr int S_GRAM = 13312;
-constexpr int S_QGH = S_GRAM, S_KQH = S_GRAM + 4096, S_KQL = S_GRAM + 8192, S_KNH = S_GRAM + 12288,
-              S_KNL = S_GRAM + 16384;
+constexpr int S_QG = 0, S_KGH = 4096, S_KGL = 8192, S_AQK = 12288, S_AQL = 12800, S_DEC = 13312;  // -> record[4096, 17920)
+constexpr int S_GRAM = 13824;
+constexpr int S_QGH = S_GRAM, S_QGL = S_GRAM + 4096, S_KQH = S_GRAM + 8192, S_KQL = S_GRAM + 12288,
+              S_KNH = S_GRAM + 16384, S_KNL = S_GRAM + 20480;
 constexpr int S_W = S_GRAM, S_UF = S_GRAM + 4096;  // reuse of the Gram tiles once the Grams are done
-constexpr int S_IN = S_GRAM + 20480;               // 33792
+constexpr int S_IN = S_GRAM + 24576;               // 38400
 constexpr int S_Q = S_IN, S_K = S_IN + 4096, S_V = S_IN + 8192, S_G = S_IN + 12288;
 constexpr int S_KBH = S_IN, S_VBH = S_IN + 4096, S_VBL = S_IN + 8192;  // reuse of q/k/v tiles after they are read
 
@@ -39,10 +39,11 @@ template <bool G_BF16>
 struct K1Smem {
   static constexpr int G_BYTES = G_BF16 ? 4096 : 8192;
   static constexpr int SMALL = S_G + G_BYTES;
-  static constexpr int L = SMALL;             // fp32 [16][17]
-  static constexpr int XH = SMALL + 1088;     // bf16 [16][16]
+  // L, X live in the gate tile, which is dead once phase B has read it
+  static constexpr int L = S_G;               // fp32 [16][17]
+  static constexpr int XH = S_G + 1088;       // bf16 [16][16]
   static constexpr int XL = XH + 512;
-  static constexpr int RNQ = XL + 512;        // fp32 [16]
+  static constexpr int RNQ = SMALL;           // fp32 [16]
   static constexpr int RNK = RNQ + 64;
   static constexpr int BETA = RNK + 64;
   static constexpr int MBAR = BETA + 64;      // 8 bytes
@@ -231,8 +232,10 @@ __global__ void __launch_bounds__(128, 4) kda_k1_kernel(const K1Params p) {
       else { eg = ex2f(gv[r]); ekg = ex2f(glast - gv[r]); }
 
       const float QG = qn * e, KQ = kn * e, KN = kn * en, KG = kn * ekg;
-      *reinterpret_cast<unsigned short*>(smem + S_QGH + off) = bf16_bits(QG);
-      float hi = bf16_round(KQ);
+      float hi = bf16_round(QG);
+      *reinterpret_cast<unsigned short*>(smem + S_QGH + off) = bf16_bits(hi);
+      *reinterpret_cast<unsigned short*>(smem + S_QGL + off) = bf16_bits(QG - hi);
+      hi = bf16_round(KQ);
       *reinterpret_cast<unsigned short*>(smem + S_KQH + off) = bf16_bits(hi);
       *reinterpret_cast<unsigned short*>(smem + S_KQL + off) = bf16_bits(KQ - hi);
       hi = bf16_round(KN);
@@ -263,23 +266,20 @@ __global__ void __launch_bounds__(128, 4) kda_k1_kernel(const K1Params p) {
     const int mt = warp >> 1;  // 0: Aqk, 1: Akk
     const int nt = warp & 1;   // column block j in [8nt, 8nt+8)
     const uint32_t a_hi = sbase + (mt == 0 ? S_QGH : S_KQH);
-    const uint32_t a_lo = sbase + S_KQL;
+    const uint32_t a_lo = sbase + (mt == 0 ? S_QGL : S_KQL);
     const int arow = (lane & 7) + ((lane >> 3) & 1) * 8, acol = (lane >> 4) * 8;
     const int brow = nt * 8 + (lane & 7), bcol = ((lane >> 3) & 1) * 8;
     float acc0[4] = {0, 0, 0, 0}, acc1[4] = {0, 0, 0, 0}, acc2[4] = {0, 0, 0, 0};
 #pragma unroll
     for (int ks = 0; ks < 8; ++ks) {
-      uint32_t ah[4], bh0, bh1, bl0, bl1;
+      uint32_t ah[4], al[4], bh0, bh1, bl0, bl1;
       ldsm_x4(a_hi + swz_off(arow, ks * 16 + acol), ah[0], ah[1], ah[2], ah[3]);
+      ldsm_x4(a_lo + swz_off(arow, ks * 16 + acol), al[0], al[1], al[2], al[3]);
       ldsm_x2(sbase + S_KNH + swz_off(brow, ks * 16 + bcol), bh0, bh1);
       ldsm_x2(sbase + S_KNL + swz_off(brow, ks * 16 + bcol), bl0, bl1);
       mma_bf16(acc0, ah, bh0, bh1);
       mma_bf16(acc1, ah, bl0, bl1);
-      if (mt == 1) {
-        uint32_t al[4];
-        ldsm_x4(a_lo + swz_off(arow, ks * 16 + acol), al[0], al[1], al[2], al[3]);
-        mma_bf16(acc2, al, bh0, bh1);
-      }
+      mma_bf16(acc2, al, bh0, bh1);
     }
 #pragma unroll
     for (int e = 0; e < 4; ++e) acc0[e] += acc1[e] + acc2[e];
@@ -290,7 +290,10 @@ __global__ void __launch_bounds__(128, 4) kda_k1_kernel(const K1Params p) {
         const int i = gq + hrow * 8;
         const float v0 = (i >= j0) ? acc0[hrow * 2] * p.scale : 0.f;
         const float v1 = (i >= j0 + 1) ? acc0[hrow * 2 + 1] * p.scale : 0.f;
-        *reinterpret_cast<uint32_t*>(smem + S_AQK + (i * 16 + j0) * 2) = pack_bf16(v0, v1);
+        uint32_t hi2, lo2;
+        split_pack(v0, v1, hi2, lo2);
+        *reinterpret_cast<uint32_t*>(smem + S_AQK + (i * 16 + j0) * 2) = hi2;
+        *reinterpret_cast<uint32_t*>(smem + S_AQL + (i * 16 + j0) * 2) = lo2;
       }
     } else {
 #pragma unroll

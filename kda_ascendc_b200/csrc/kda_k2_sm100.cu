@@ -17,7 +17,8 @@
 // never leaves the register file: no shared-memory or tensor-memory round trip sits on
 // the serial path, which is what bounds this kernel (NT dependent steps per head).
 // P2 uses a hi/lo bf16 split of both v_new and kg (three MMAs) because the state must
-// stay within 2e-3 of an fp32 implementation; P1 and P3 use plain bf16 operands.
+// stay within 2e-3 of an fp32 implementation; P3 does the same with v_new and Aqk (the
+// intra-chunk term dominates o); P1 uses plain bf16 operands.
 //
 // A CTA = VW consumer warps (a slice of VW*16 state rows of one (batch, head)) plus one
 // producer warp that streams the chunk records through a ring of shared-memory stages
@@ -196,10 +197,15 @@ __global__ void __launch_bounds__((VW + 1) * 32, 1) kda_k2_kernel(const K2Params
         for (int j = 0; j < 2; ++j)
 #pragma unroll
           for (int e = 0; e < 4; ++e) oa[j][e] = p.scale * (pq[0][j][e] + pq[1][j][e]);
-        uint32_t ba[4];
+        uint32_t ba[4], bl[4];
         ldsm_x4(sp + p3_off, ba[0], ba[1], ba[2], ba[3]);
+        ldsm_x4(sp + p3_off + (REC_AQL - REC_AQK), bl[0], bl[1], bl[2], bl[3]);
         mma_bf16(oa[0], avh, ba[0], ba[1]);
         mma_bf16(oa[1], avh, ba[2], ba[3]);
+        mma_bf16(oa[0], avl, ba[0], ba[1]);
+        mma_bf16(oa[1], avl, ba[2], ba[3]);
+        mma_bf16(oa[0], avh, bl[0], bl[1]);
+        mma_bf16(oa[1], avh, bl[2], bl[3]);
         const int t0 = n * BT;
         __nv_bfloat16* ob = p.o + b * p.o_s[0] + h * p.o_s[2] + vrow0 + gq;
 #pragma unroll

@@ -12,9 +12,9 @@ import torch
 
 CHUNK = 16
 D = 128
-REC_BYTES = 25600
+REC_BYTES = 26112
 WS_HEADER_BYTES = 256
-REC_W, REC_QG, REC_KGH, REC_KGL, REC_AQK, REC_DEC, REC_U = 0, 4096, 8192, 12288, 16384, 16896, 17408
+REC_W, REC_QG, REC_KGH, REC_KGL, REC_AQK, REC_AQL, REC_DEC, REC_U = 0, 4096, 8192, 12288, 16384, 16896, 17408, 17920
 
 
 def pack_tokens(x: torch.Tensor, chunk: int = CHUNK) -> torch.Tensor:
@@ -54,7 +54,7 @@ def _u_index(device) -> torch.Tensor:
 def unpack_records(workspace: torch.Tensor, B: int, T: int, H: int) -> dict:
     """Decode the chunk records of a finished K1 pass.
 
-    Returns ``w, qg`` (bf16), ``kg, u`` (fp32; kg = hi + lo), ``Aqk`` (bf16 ``[B,T,H,16]``)
+    Returns ``w, qg`` (bf16), ``kg, u`` (fp32; kg = hi + lo), ``Aqk`` (fp32 = hi + lo, ``[B,T,H,16]``)
     in the public token layout (rows past ``T`` dropped) and ``dec`` fp32 ``[B,H,NT,128]``.
     """
     nt = (T + CHUNK - 1) // CHUNK
@@ -73,7 +73,8 @@ def unpack_records(workspace: torch.Tensor, B: int, T: int, H: int) -> dict:
         return y[:, :T].contiguous()
 
     uT = rec[:, REC_U:REC_U + 8192].contiguous().view(torch.float32)[:, _u_index(dev)].view(c, CHUNK, D)
-    aqk = rec[:, REC_AQK:REC_AQK + 512].contiguous().view(torch.bfloat16).view(c, CHUNK, CHUNK)
+    aqk = (rec[:, REC_AQK:REC_AQK + 512].contiguous().view(torch.bfloat16).float() +
+           rec[:, REC_AQL:REC_AQL + 512].contiguous().view(torch.bfloat16).float()).view(c, CHUNK, CHUNK)
     dec = rec[:, REC_DEC:REC_DEC + 512].contiguous().view(torch.float32).view(B, H, nt, D)
     return dict(w=to_public(tile(REC_W)), qg=to_public(tile(REC_QG)),
                 kg=to_public(tile(REC_KGH).float() + tile(REC_KGL).float()),

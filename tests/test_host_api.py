@@ -1,0 +1,122 @@
+"""CPU checks of the host layer: validation rules, the C-ABI library, layouts."""
+import ctypes
+import re
+from pathlib import Path
+
+import pytest
+import torch
+
+import kda_ascendc_b200 as K
+from kda_ascendc_b200 import _lib, api, layout
+
+ROOT = Path(__file__).resolve().parents[1]
+D = 128
+
+
+def _mk(B=1, T=32, H=2):
+    q = torch.randn(B, T, H, D).bfloat16()
+    k = torch.randn(B, T, H, D).bfloat16()
+    v = torch.randn(B, T, H, D).bfloat16()
+    g = torch.randn(B, T, H, D)
+    beta = torch.randn(B, T, H)
+    return q, k, v, g, beta
+
+
+def test_library_exports_every_declared_symbol():
+    header = (ROOT / "include" / "kda_b200.h").read_text()
+    declared = set(re.findall(r"\b(kda_[a-z0-9_]+)\s*\(", header))
+    assert declared, "no declarations found"
+    lib = ctypes.CDLL(str(_lib.LIB_PATH))
+    for name in sorted(declared):
+        assert hasattr(lib, name), f"{name} is declared in include/kda_b200.h but not exported"
+    assert set(_lib.EXPORTS) <= declared
+
+
+def test_struct_layout_matches_header():
+    # 13 pointers, 4 int32, 6 x 3 int64, 2 floats, uint32, int32
+    assert ctypes.sizeof(_lib.KdaFwdArgs) == 13 * 8 + 4 * 4 + 18 * 8 + 4 * 4
+    assert _lib.KdaFwdArgs.q_stride.offset == 13 * 8 + 16
+    assert _lib.KdaFwdArgs.scale.offset == 13 * 8 + 16 + 18 * 8
+
+
+def test_workspace_bytes_and_version():
+    assert K.workspace_bytes(1, 8192, 32) == 256 + 32 * 512 * 26112
+    assert K.workspace_bytes(2, 17, 3) == 256 + 2 * 3 * 2 * 26112
+    assert b"sm_100a" in _lib.load().kda_version()
+
+
+def test_c_abi_rejects_bad_arguments_without_a_gpu():
+    lib = _lib.load()
+    a = _lib.KdaFwdArgs()
+    assert lib.kda_fwd(ctypes.byref(a), None) == -1
+    assert "positive" in _lib.last_error()
+    a.B, a.T, a.H = 1, 16, 1
+    assert lib.kda_fwd(ctypes.byref(a), None) == -1
+    assert "workspace" in _lib.last_error()
+    assert lib.kda_fwd(None, None) == -1
+
+
+def test_reference_validation_messages():
+    q, k, v, g, beta = _mk()
+    with pytest.raises(ValueError, match="q must be contiguous"):
+        K.kda_bt16_fwd(q.transpose(1, 2), k, v, g, beta, scale=0.0883)
+    with pytest.raises(TypeError, match="k must be bfloat16"):
+        K.kda_bt16_fwd(q, k.float(), v, g, beta, scale=0.0883)
+    v64 = torch.randn(1, 32, 2, 64).bfloat16()
+    with pytest.raises(ValueError, match="prototype targets K=V=128"):
+        K.kda_bt16_fwd(q, k, v64, g, beta, scale=0.0883)
+    with pytest.raises(ValueError, match="beta must be 3D"):
+        K.kda_bt16_fwd(q, k, v, g, beta[..., None], scale=0.1)
+    with pytest.raises(TypeError, match="beta must be float32"):
+        K.kda_bt16_fwd(q, k, v, g, beta.double(), scale=0.1)
+    with pytest.raises(ValueError, match="requires A_log"):
+        K.kda_bt16_fwd(q, k, v, g, beta, use_gate_in_kernel=True)
+    with pytest.raises(ValueError, match=r"range \(-11, 0\)"):
+        K.kda_bt16_fwd(q, k, v, g, beta, use_gate_in_kernel=True, A_log=torch.zeros(2), lower_bound=-12.0)
+    with pytest.raises(ValueError, match="initial_state.shape"):
+        K.kda_bt16_fwd(q, k, v, g, beta, initial_state=torch.zeros(1, 2, 128, 64))
+    with pytest.raises(TypeError, match="initial_state must be float32"):
+        K.kda_bt16_fwd(q, k, v, g, beta, initial_state=torch.zeros(1, 2, 128, 128, dtype=torch.float64))
+    with pytest.raises(ValueError, match=r"dt_bias.shape"):
+        K.kda_bt16_fwd(q, k, v, g, beta, use_gate_in_kernel=True, A_log=torch.zeros(2), dt_bias=torch.zeros(2, 128))
+
+
+def test_no_cpu_fallback():
+    q, k, v, g, beta = _mk()
+    with pytest.raises(RuntimeError, match="no CPU fallback"):
+        K.kda_bt16_fwd(q, k, v, g, beta, use_gate_in_kernel=True, use_qk_l2norm_in_kernel=True,
+                       use_beta_sigmoid_in_kernel=True, A_log=torch.zeros(2))
+    with pytest.raises(RuntimeError, match="no CPU fallback"):
+        K.kda_bt16_fwd_ascendc(q, k, v, g, beta, A_log=torch.zeros(2))
+
+
+def test_second_api_input_rules():
+    q, k, v, g, beta = _mk(T=24)
+    with pytest.raises(ValueError, match="T>=16"):
+        K.kda_bt16_fwd_ascendc(q, k, v, g, beta, A_log=torch.zeros(2))
+    q, k, v, g, beta = _mk()
+    with pytest.raises(ValueError, match="bias must be FP32"):
+        K.kda_bt16_fwd_ascendc(q, k, v, g, beta, A_log=torch.zeros(2), bias=torch.zeros(2 * 128))
+    with pytest.raises(ValueError, match="unsupported k2_mode"):
+        K.kda_bt16_fwd_ascendc(q, k, v, g, beta, A_log=torch.zeros(2), k2_mode="d12")
+
+
+def test_pack_unpack_tokens_roundtrip():
+    x = torch.randn(2, 48, 3, D)
+    p = K.pack_tokens(x)
+    assert p.shape == (2 * 3 * 3, 16, D)
+    # chunk-major order: c = (b*H + h)*NT + n
+    assert torch.equal(p[(1 * 3 + 2) * 3 + 1], x[1, 16:32, 2])
+    assert torch.equal(K.unpack_tokens(p, 2, 48, 3), x)
+    with pytest.raises(ValueError):
+        K.pack_tokens(torch.randn(1, 17, 1, D))
+
+
+def test_record_index_maps_are_permutations():
+    sw = layout._swizzle_index("cpu")
+    assert sorted(sw.tolist()) == list(range(16 * 128))
+    ui = layout._u_index("cpu")
+    assert sorted(ui.tolist()) == list(range(16 * 128))
+    # ldmatrix reads 8 rows at one 16-byte column unit: all eight must hit different units
+    units = sw.view(16, 128)[:8, 0] % 128 // 8
+    assert len(set(units.tolist())) == 8
