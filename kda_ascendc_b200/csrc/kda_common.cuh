@@ -168,6 +168,11 @@ __device__ __forceinline__ void split_pack(float x0, float x1, uint32_t& hi, uin
   hi = pack_bf16(x0, x1);
   lo = pack_bf16(x0 - bf16_lo_to_f32(hi), x1 - bf16_hi_to_f32(hi));
 }
+__device__ __forceinline__ float rcpf(float x) {
+  float y;
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
 __device__ __forceinline__ float ex2f(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));

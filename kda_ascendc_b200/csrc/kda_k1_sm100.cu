@@ -46,7 +46,10 @@ struct K1Smem {
   static constexpr int RNQ = SMALL;           // fp32 [16]
   static constexpr int RNK = RNQ + 64;
   static constexpr int BETA = RNK + 64;
-  static constexpr int MBAR = BETA + 64;      // 8 bytes
+  static constexpr int TOT = BETA + 64;       // fp32 [128] column sums of rows 0..7
+  static constexpr int GMID = TOT + 512;      // fp32 [128] g[mid]
+  static constexpr int GLAST = GMID + 512;    // fp32 [128] g[last]
+  static constexpr int MBAR = GLAST + 512;    // 8 bytes
   static constexpr int FLAG = MBAR + 8;
   static constexpr int TOTAL = FLAG + 8;
 };
@@ -75,6 +78,9 @@ __global__ void __launch_bounds__(128, 4) kda_k1_kernel(const K1Params p) {
   float* sRnq = reinterpret_cast<float*>(smem + SM::RNQ);
   float* sRnk = reinterpret_cast<float*>(smem + SM::RNK);
   float* sBeta = reinterpret_cast<float*>(smem + SM::BETA);
+  float* sTot = reinterpret_cast<float*>(smem + SM::TOT);
+  float* sGmid = reinterpret_cast<float*>(smem + SM::GMID);
+  float* sGlast = reinterpret_cast<float*>(smem + SM::GLAST);
   volatile int* sFlag = reinterpret_cast<volatile int*>(smem + SM::FLAG);
 
   if (tid == 0) {
@@ -115,16 +121,19 @@ __global__ void __launch_bounds__(128, 4) kda_k1_kernel(const K1Params p) {
     float bv = 0.f;
     if (r < nvalid) {
       bv = p.beta[b * p.beta_s[0] + static_cast<int64_t>(t0 + r) * p.beta_s[1] + h * p.beta_s[2]];
-      if (p.flags & 4u) bv = 1.0f / (1.0f + __expf(-bv));
+      if (p.flags & 4u) bv = 1.0f / (1.0f + __expf(-bv));  // 16 values per chunk: accuracy over speed
     }
     sBeta[r] = bv;
   }
   const bool use_gate = (p.flags & 1u) != 0;
   const bool use_l2 = (p.flags & 2u) != 0;
-  float expA = 1.f, bias = 0.f;
+  float expA = 1.f, bias0 = 0.f, bias1 = 0.f;
   if (use_gate) {
     expA = expf(p.A_log[h]);
-    if (p.dt_bias != nullptr) bias = p.dt_bias[h * D + tid];
+    if (p.dt_bias != nullptr) {
+      const float2 bb = *reinterpret_cast<const float2*>(p.dt_bias + h * D + (tid & 63) * 2);
+      bias0 = bb.x; bias1 = bb.y;
+    }
   }
 
   bool ok = true;
@@ -172,92 +181,130 @@ __global__ void __launch_bounds__(128, 4) kda_k1_kernel(const K1Params p) {
   }
   __syncthreads();
 
-  // ---- phase B: one column per thread: gate, cumsum, gated operands ---------
-  const int c = tid;
-  float kb[BT], vb[BT];
+  // ---- phase B: thread = (column pair, row half): gate, cumsum, gated operands ----
+  // Two adjacent columns per thread so that every bf16 conversion is the packed
+  // cvt.rn.bf16x2 (full-rate pipe) and every tile store is 32 bits wide.
+  const int cp = tid & 63, rh = tid >> 6;
+  const int c0 = cp * 2, r0 = rh * 8;
+  uint32_t kbh[8], vbh[8], vbl[8];
   {
-    float gv[BT];
+    float gv[2][8];
+    float gmid0, gmid1, glast0, glast1;
     if (use_gate) {
-      float run = 0.f;
+      const float nA = -expA * 1.4426950408889634f;  // exp(-z) = 2^(nA * (x + bias))
+      const int mid = min(BT / 2, nvalid - 1);
+      float run0 = 0.f, run1 = 0.f, m0 = 0.f, m1 = 0.f;
 #pragma unroll
-      for (int r = 0; r < BT; ++r) {
-        float x;
-        if (G_BF16) x = __uint_as_float(static_cast<uint32_t>(*reinterpret_cast<const unsigned short*>(smem + S_G + (r * D + c) * 2)) << 16);
-        else x = *reinterpret_cast<const float*>(smem + S_G + (r * D + c) * 4);
-        const float z = expA * (x + bias);
-        const float s = 1.0f / (1.0f + __expf(-z));
-        float gate = (p.lower_bound * s) * RCP_LN2;
-        if (r >= nvalid) gate = 0.f;
-        run += gate;
-        gv[r] = run;
+      for (int i = 0; i < 8; ++i) {
+        const int r = r0 + i;
+        float x0, x1;
+        if (G_BF16) {
+          const uint32_t gp = *reinterpret_cast<const uint32_t*>(smem + S_G + (r * D + c0) * 2);
+          x0 = bf16_lo_to_f32(gp); x1 = bf16_hi_to_f32(gp);
+        } else {
+          const float2 gp = *reinterpret_cast<const float2*>(smem + S_G + (r * D + c0) * 4);
+          x0 = gp.x; x1 = gp.y;
+        }
+        const float s0 = rcpf(1.0f + ex2f(nA * (x0 + bias0)));
+        const float s1 = rcpf(1.0f + ex2f(nA * (x1 + bias1)));
+        float gate0 = (p.lower_bound * s0) * RCP_LN2, gate1 = (p.lower_bound * s1) * RCP_LN2;
+        if (r >= nvalid) { gate0 = 0.f; gate1 = 0.f; }
+        run0 += gate0; run1 += gate1;
+        gv[0][i] = run0; gv[1][i] = run1;
+        if (r == mid) { m0 = run0; m1 = run1; }
       }
+      // rows 8..15 need the sum over rows 0..7, all rows need g[mid] and g[last]
+      if (rh == 0) *reinterpret_cast<float2*>(sTot + c0) = make_float2(run0, run1);
+      __syncthreads();
+      if (rh == 1) {
+        const float2 t = *reinterpret_cast<const float2*>(sTot + c0);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) { gv[0][i] += t.x; gv[1][i] += t.y; }
+        m0 += t.x; m1 += t.y;
+        *reinterpret_cast<float2*>(sGlast + c0) = make_float2(gv[0][7], gv[1][7]);
+      }
+      if (rh == (mid >> 3)) *reinterpret_cast<float2*>(sGmid + c0) = make_float2(m0, m1);
+      __syncthreads();
+      const float2 gm = *reinterpret_cast<const float2*>(sGmid + c0);
+      const float2 gl = *reinterpret_cast<const float2*>(sGlast + c0);
+      gmid0 = gm.x; gmid1 = gm.y; glast0 = gl.x; glast1 = gl.y;
     } else {
-      float last = 0.f;
+      // g already holds the chunk-local log2 cumsum; rows past the end repeat the last valid row
+      auto ldg = [&](int r) -> float2 {
+        if (G_BF16) {
+          const uint32_t gp = *reinterpret_cast<const uint32_t*>(smem + S_G + (r * D + c0) * 2);
+          return make_float2(bf16_lo_to_f32(gp), bf16_hi_to_f32(gp));
+        }
+        return *reinterpret_cast<const float2*>(smem + S_G + (r * D + c0) * 4);
+      };
 #pragma unroll
-      for (int r = 0; r < BT; ++r) {
-        float x;
-        if (G_BF16) x = __uint_as_float(static_cast<uint32_t>(*reinterpret_cast<const unsigned short*>(smem + S_G + (r * D + c) * 2)) << 16);
-        else x = *reinterpret_cast<const float*>(smem + S_G + (r * D + c) * 4);
-        if (r < nvalid) last = x;
-        gv[r] = last;
+      for (int i = 0; i < 8; ++i) {
+        const float2 x = ldg(min(r0 + i, nvalid - 1));
+        gv[0][i] = x.x; gv[1][i] = x.y;
       }
+      const float2 xm = ldg(min(BT / 2, nvalid - 1)), xl = ldg(nvalid - 1);
+      gmid0 = xm.x; gmid1 = xm.y; glast0 = xl.x; glast1 = xl.y;
     }
-    const int mid = min(BT / 2, nvalid - 1);
-    float gmid = gv[0];
-#pragma unroll
-    for (int r = 1; r <= BT / 2; ++r) gmid = (r == mid) ? gv[r] : gmid;
-    const float glast = gv[BT - 1];
-    const float c1 = ex2f(gmid), c2 = ex2f(glast - gmid);
-    *reinterpret_cast<float*>(smem + S_DEC + c * 4) = ex2f(glast);
+    const float c1_0 = ex2f(gmid0), c1_1 = ex2f(gmid1);
+    const float c2_0 = ex2f(glast0 - gmid0), c2_1 = ex2f(glast1 - gmid1);
+    if (rh == 1) *reinterpret_cast<float2*>(smem + S_DEC + c0 * 4) = make_float2(ex2f(glast0), ex2f(glast1));
 
     if (p.g_out != nullptr) {
 #pragma unroll
-      for (int r = 0; r < BT; ++r)
-        if (r < nvalid) p.g_out[((static_cast<size_t>(b) * p.T + t0 + r) * p.H + h) * D + c] = gv[r];
+      for (int i = 0; i < 8; ++i)
+        if (r0 + i < nvalid)
+          *reinterpret_cast<float2*>(p.g_out + ((static_cast<size_t>(b) * p.T + t0 + r0 + i) * p.H + h) * D + c0) =
+              make_float2(gv[0][i], gv[1][i]);
     }
 
 #pragma unroll
-    for (int r = 0; r < BT; ++r) {
-      const uint32_t off = swz_off(r, c);
-      const float qraw = __uint_as_float(static_cast<uint32_t>(*reinterpret_cast<const unsigned short*>(smem + S_Q + (r * D + c) * 2)) << 16);
-      const float kraw = __uint_as_float(static_cast<uint32_t>(*reinterpret_cast<const unsigned short*>(smem + S_K + (r * D + c) * 2)) << 16);
-      const float vraw = __uint_as_float(static_cast<uint32_t>(*reinterpret_cast<const unsigned short*>(smem + S_V + (r * D + c) * 2)) << 16);
-      const float qn = use_l2 ? bf16_round(qraw * sRnq[r]) : qraw;
-      const float kn = use_l2 ? bf16_round(kraw * sRnk[r]) : kraw;
+    for (int i = 0; i < 8; ++i) {
+      const int r = r0 + i;
+      const uint32_t off = swz_off(r, c0);
+      const uint32_t qp = *reinterpret_cast<const uint32_t*>(smem + S_Q + (r * D + c0) * 2);
+      const uint32_t kp = *reinterpret_cast<const uint32_t*>(smem + S_K + (r * D + c0) * 2);
+      const uint32_t vp = *reinterpret_cast<const uint32_t*>(smem + S_V + (r * D + c0) * 2);
+      float qn0 = bf16_lo_to_f32(qp), qn1 = bf16_hi_to_f32(qp);
+      float kn0 = bf16_lo_to_f32(kp), kn1 = bf16_hi_to_f32(kp);
+      if (use_l2) {
+        const float rq = sRnq[r], rk = sRnk[r];
+        const uint32_t qr = pack_bf16(qn0 * rq, qn1 * rq), kr = pack_bf16(kn0 * rk, kn1 * rk);
+        qn0 = bf16_lo_to_f32(qr); qn1 = bf16_hi_to_f32(qr);
+        kn0 = bf16_lo_to_f32(kr); kn1 = bf16_hi_to_f32(kr);
+      }
       const float br = sBeta[r];
-      const float e = ex2f(gv[r] - gmid);
-      const float en = ex2f(gmid - gv[r]);
-      float eg, ekg;
-      if (FAST_EXP) { eg = e * c1; ekg = en * c2; }
-      else { eg = ex2f(gv[r]); ekg = ex2f(glast - gv[r]); }
+      const float e0 = ex2f(gv[0][i] - gmid0), e1 = ex2f(gv[1][i] - gmid1);
+      const float en0 = ex2f(gmid0 - gv[0][i]), en1 = ex2f(gmid1 - gv[1][i]);
+      float eg0, eg1, ekg0, ekg1;
+      if (FAST_EXP) { eg0 = e0 * c1_0; eg1 = e1 * c1_1; ekg0 = en0 * c2_0; ekg1 = en1 * c2_1; }
+      else { eg0 = ex2f(gv[0][i]); eg1 = ex2f(gv[1][i]); ekg0 = ex2f(glast0 - gv[0][i]); ekg1 = ex2f(glast1 - gv[1][i]); }
 
-      const float QG = qn * e, KQ = kn * e, KN = kn * en, KG = kn * ekg;
-      float hi = bf16_round(QG);
-      *reinterpret_cast<unsigned short*>(smem + S_QGH + off) = bf16_bits(hi);
-      *reinterpret_cast<unsigned short*>(smem + S_QGL + off) = bf16_bits(QG - hi);
-      hi = bf16_round(KQ);
-      *reinterpret_cast<unsigned short*>(smem + S_KQH + off) = bf16_bits(hi);
-      *reinterpret_cast<unsigned short*>(smem + S_KQL + off) = bf16_bits(KQ - hi);
-      hi = bf16_round(KN);
-      *reinterpret_cast<unsigned short*>(smem + S_KNH + off) = bf16_bits(hi);
-      *reinterpret_cast<unsigned short*>(smem + S_KNL + off) = bf16_bits(KN - hi);
-      *reinterpret_cast<unsigned short*>(smem + S_QG + off) = bf16_bits(qn * eg);
-      hi = bf16_round(KG);
-      *reinterpret_cast<unsigned short*>(smem + S_KGH + off) = bf16_bits(hi);
-      *reinterpret_cast<unsigned short*>(smem + S_KGL + off) = bf16_bits(KG - hi);
-      kb[r] = (kn * br) * eg;
-      vb[r] = vraw * br;
+      uint32_t hi, lo;
+      split_pack(qn0 * e0, qn1 * e1, hi, lo);
+      *reinterpret_cast<uint32_t*>(smem + S_QGH + off) = hi;
+      *reinterpret_cast<uint32_t*>(smem + S_QGL + off) = lo;
+      split_pack(kn0 * e0, kn1 * e1, hi, lo);
+      *reinterpret_cast<uint32_t*>(smem + S_KQH + off) = hi;
+      *reinterpret_cast<uint32_t*>(smem + S_KQL + off) = lo;
+      split_pack(kn0 * en0, kn1 * en1, hi, lo);
+      *reinterpret_cast<uint32_t*>(smem + S_KNH + off) = hi;
+      *reinterpret_cast<uint32_t*>(smem + S_KNL + off) = lo;
+      *reinterpret_cast<uint32_t*>(smem + S_QG + off) = pack_bf16(qn0 * eg0, qn1 * eg1);
+      split_pack(kn0 * ekg0, kn1 * ekg1, hi, lo);
+      *reinterpret_cast<uint32_t*>(smem + S_KGH + off) = hi;
+      *reinterpret_cast<uint32_t*>(smem + S_KGL + off) = lo;
+      kbh[i] = pack_bf16((kn0 * br) * eg0, (kn1 * br) * eg1);
+      split_pack(bf16_lo_to_f32(vp) * br, bf16_hi_to_f32(vp) * br, vbh[i], vbl[i]);
     }
   }
-  __syncthreads();  // every thread has read its q/k/v/g column: the input tiles may be overwritten
+  __syncthreads();  // every thread has read its q/k/v/g elements: the input tiles may be overwritten
 
 #pragma unroll
-  for (int r = 0; r < BT; ++r) {
-    const uint32_t off = swz_off(r, c);
-    *reinterpret_cast<unsigned short*>(smem + S_KBH + off) = bf16_bits(kb[r]);
-    const float hi = bf16_round(vb[r]);
-    *reinterpret_cast<unsigned short*>(smem + S_VBH + off) = bf16_bits(hi);
-    *reinterpret_cast<unsigned short*>(smem + S_VBL + off) = bf16_bits(vb[r] - hi);
+  for (int i = 0; i < 8; ++i) {
+    const uint32_t off = swz_off(r0 + i, c0);
+    *reinterpret_cast<uint32_t*>(smem + S_KBH + off) = kbh[i];
+    *reinterpret_cast<uint32_t*>(smem + S_VBH + off) = vbh[i];
+    *reinterpret_cast<uint32_t*>(smem + S_VBL + off) = vbl[i];
   }
 
   // ---- phase C: Grams on the tensor cores (one 16x8 output tile per warp) ----
