@@ -78,7 +78,10 @@ typedef struct KdaFwdArgs {
   float scale;
   float lower_bound;
   uint32_t flags;
-  int32_t k2_vsplit;    /* 0 = choose; else number of V slices per (batch, head): 1, 2, 4 or 8 */
+  int32_t k2_vsplit;    /* 0 = choose; else CTAs per (batch, head): 1, 2, 4 or 8 (rows of the state) */
+  int32_t k2_ksplit;    /* 0 = choose; else warps per 16-row state tile: 1, 2 or 4 (columns of the state);
+                           (8 / k2_vsplit) * k2_ksplit must not exceed 8 */
+  int32_t reserved_;
 } KdaFwdArgs;
 
 /* Bytes of K1 -> K2 scratch for a (B, T, H) problem: a 256-byte status block

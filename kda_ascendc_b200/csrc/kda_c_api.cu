@@ -55,19 +55,38 @@ int check_k2(const KdaFwdArgs* a, bool state_only) {
   if (!state_only && a->o == nullptr) return fail(KDA_ERR_INVALID_ARG, "kda: o is NULL%s", "");
   if (a->k2_vsplit != 0 && a->k2_vsplit != 1 && a->k2_vsplit != 2 && a->k2_vsplit != 4 && a->k2_vsplit != 8)
     return fail(KDA_ERR_INVALID_ARG, "kda: k2_vsplit must be 0, 1, 2, 4 or 8%s (got %lld)", "", a->k2_vsplit);
+  if (a->k2_ksplit != 0 && a->k2_ksplit != 1 && a->k2_ksplit != 2 && a->k2_ksplit != 4)
+    return fail(KDA_ERR_INVALID_ARG, "kda: k2_ksplit must be 0, 1, 2 or 4%s (got %lld)", "", a->k2_ksplit);
+  if (a->k2_vsplit != 0 && a->k2_ksplit != 0 && (8 / a->k2_vsplit) * a->k2_ksplit > 8)
+    return fail(KDA_ERR_INVALID_ARG, "kda: (8 / k2_vsplit) * k2_ksplit must not exceed 8%s (vsplit %lld, ksplit %lld)", "",
+                a->k2_vsplit, a->k2_ksplit);
   return KDA_OK;
 }
 
-int pick_vsplit(const KdaFwdArgs* a) {
-  if (a->k2_vsplit != 0) return a->k2_vsplit;
+// How one head's 128x128 state is spread over warps.  The recurrence is a serial chain per
+// head whose step time is set by the tensor-pipe issue rate of one SM sub-partition, so the
+// aim is one consumer warp per sub-partition for as long as the heads leave room:
+// ksplit warps share a 16-row tile (they split K), vsplit CTAs share a head (they split V).
+void pick_split(const KdaFwdArgs* a, int* vsplit, int* ksplit) {
   int dev = 0, sms = 148;
   if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   const long long bh = static_cast<long long>(a->B) * a->H;
-  // as many state slices as still give every CTA an SM of its own
-  if (bh * 8 <= sms) return 8;
-  if (bh * 4 <= sms) return 4;
-  if (bh * 2 <= sms + sms / 2) return 2;
-  return 1;
+  const long long tiles = bh * 8, slots = 4LL * sms;
+  int ks = a->k2_ksplit;
+  if (ks == 0) {
+    ks = (tiles * 4 <= slots) ? 4 : (tiles * 2 <= slots) ? 2 : 1;
+    if (a->k2_vsplit != 0 && ks > a->k2_vsplit) ks = a->k2_vsplit;   // (8 / vsplit) * ksplit <= 8
+  }
+  int vs = a->k2_vsplit;
+  if (vs == 0) {
+    const int vw_max = 8 / ks;                 // at most 8 consumer warps per CTA
+    int vw = vw_max;
+    for (int cand = 1; cand <= vw_max; cand *= 2)   // smallest slice that still gives every CTA its own SM
+      if (bh * (8 / cand) <= sms) { vw = cand; break; }
+    vs = 8 / vw;
+  }
+  *vsplit = vs;
+  *ksplit = ks;
 }
 
 int* status_ptr(const KdaFwdArgs* a) { return static_cast<int*>(a->workspace); }
@@ -116,7 +135,10 @@ int do_k2(const KdaFwdArgs* a, bool state_only, int zero_u, cudaStream_t st) {
   for (int i = 0; i < 3; ++i) p.o_s[i] = a->o_stride[i];
   p.scale = a->scale;
   p.zero_u = zero_u;
-  cudaError_t e = kda::launch_k2(p, pick_vsplit(a), state_only, st);
+  int vsplit = 1, ksplit = 1;
+  pick_split(a, &vsplit, &ksplit);
+  if ((8 / vsplit) * ksplit > 8) vsplit = ksplit;   // one of the two was forced: keep the CTA at 8 warps
+  cudaError_t e = kda::launch_k2(p, vsplit, ksplit, state_only, st);
   if (e != cudaSuccess) return fail(KDA_ERR_CUDA, "kda: K2 launch failed: %s", cudaGetErrorString(e));
   ++g_launches;
   return KDA_OK;

@@ -98,12 +98,23 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
+__device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
 // Bounded wait: gives up after WAIT_LIMIT_NS (or as soon as *abort_flag is set by
 // another warp of the CTA) and returns false; the caller records a status code and
 // unwinds.  Never spins forever.
 __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity,
                                                   volatile int* abort_flag) {
-  if (mbar_try_wait(bar, parity)) return true;
+  if (mbar_test_wait(bar, parity)) return true;
   const unsigned long long t0 = globaltimer_ns();
   for (;;) {
 #pragma unroll 1
@@ -112,6 +123,15 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity,
     if (abort_flag != nullptr && *abort_flag != 0) return false;
     if (globaltimer_ns() - t0 > WAIT_LIMIT_NS) return false;
   }
+}
+
+// Bounded busy-poll for waits that are expected to last a few dozen cycles (a partner warp
+// on another SM sub-partition): polls with the non-blocking test_wait, same limits.
+__device__ __forceinline__ bool mbar_spin_bounded(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+#pragma unroll 1
+  for (int i = 0; i < 4096; ++i)
+    if (mbar_test_wait(bar, parity)) return true;
+  return mbar_wait_bounded(bar, parity, abort_flag);
 }
 
 // ---- bulk (TMA, untiled) copies ---------------------------------------------
@@ -147,6 +167,15 @@ __device__ __forceinline__ void ldsm_x2(uint32_t addr, uint32_t& r0, uint32_t& r
 // D(16x8,f32) += A(16x16,bf16,row) * B(16x8,bf16,col)
 __device__ __forceinline__ void mma_bf16(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
   asm(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+// same instruction, but pinned in program order (used where independent loads and stores are
+// deliberately interleaved with a long MMA sequence to fill the tensor pipe's issue gaps)
+__device__ __forceinline__ void mma_bf16_v(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile(
       "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
       : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
       : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));

@@ -33,8 +33,8 @@ def test_library_exports_every_declared_symbol():
 
 
 def test_struct_layout_matches_header():
-    # 13 pointers, 4 int32, 6 x 3 int64, 2 floats, uint32, int32
-    assert ctypes.sizeof(_lib.KdaFwdArgs) == 13 * 8 + 4 * 4 + 18 * 8 + 4 * 4
+    # 13 pointers, 4 int32, 6 x 3 int64, 2 floats, uint32, 3 int32
+    assert ctypes.sizeof(_lib.KdaFwdArgs) == 13 * 8 + 4 * 4 + 18 * 8 + 6 * 4
     assert _lib.KdaFwdArgs.q_stride.offset == 13 * 8 + 16
     assert _lib.KdaFwdArgs.scale.offset == 13 * 8 + 16 + 18 * 8
 
