@@ -78,9 +78,9 @@ typedef struct KdaFwdArgs {
   float scale;
   float lower_bound;
   uint32_t flags;
-  int32_t k2_vsplit;    /* 0 = choose; else CTAs per (batch, head): 1, 2, 4 or 8 (rows of the state) */
-  int32_t k2_ksplit;    /* 0 = choose; else warps per 16-row state tile: 1, 2 or 4 (columns of the state);
-                           (8 / k2_vsplit) * k2_ksplit must not exceed 8 */
+  int32_t k2_vsplit;    /* 0 = choose; else CTAs per (batch, head): 2, 4, 8 or 16 (rows of the state) */
+  int32_t k2_ntile;     /* 0 = choose; else 8-row state tiles per warp: 1 or 2;
+                           16 / (k2_vsplit * k2_ntile) warps per CTA must be 1, 2 or 4 */
   int32_t reserved_;
 } KdaFwdArgs;
 

@@ -53,40 +53,41 @@ int check_k1(const KdaFwdArgs* a) {
 int check_k2(const KdaFwdArgs* a, bool state_only) {
   if (int rc = check_common(a)) return rc;
   if (!state_only && a->o == nullptr) return fail(KDA_ERR_INVALID_ARG, "kda: o is NULL%s", "");
-  if (a->k2_vsplit != 0 && a->k2_vsplit != 1 && a->k2_vsplit != 2 && a->k2_vsplit != 4 && a->k2_vsplit != 8)
-    return fail(KDA_ERR_INVALID_ARG, "kda: k2_vsplit must be 0, 1, 2, 4 or 8%s (got %lld)", "", a->k2_vsplit);
-  if (a->k2_ksplit != 0 && a->k2_ksplit != 1 && a->k2_ksplit != 2 && a->k2_ksplit != 4)
-    return fail(KDA_ERR_INVALID_ARG, "kda: k2_ksplit must be 0, 1, 2 or 4%s (got %lld)", "", a->k2_ksplit);
-  if (a->k2_vsplit != 0 && a->k2_ksplit != 0 && (8 / a->k2_vsplit) * a->k2_ksplit > 8)
-    return fail(KDA_ERR_INVALID_ARG, "kda: (8 / k2_vsplit) * k2_ksplit must not exceed 8%s (vsplit %lld, ksplit %lld)", "",
-                a->k2_vsplit, a->k2_ksplit);
+  const int vs = a->k2_vsplit, nt = a->k2_ntile;
+  if (vs != 0 && vs != 2 && vs != 4 && vs != 8 && vs != 16)
+    return fail(KDA_ERR_INVALID_ARG, "kda: k2_vsplit must be 0, 2, 4, 8 or 16%s (got %lld)", "", vs);
+  if (nt != 0 && nt != 1 && nt != 2)
+    return fail(KDA_ERR_INVALID_ARG, "kda: k2_ntile must be 0, 1 or 2%s (got %lld)", "", nt);
+  if (vs != 0 && nt != 0 && (vs * nt > 16 || vs * nt < 4))
+    return fail(KDA_ERR_INVALID_ARG, "kda: 16 / (k2_vsplit * k2_ntile) must be 1, 2 or 4%s (vsplit %lld, ntile %lld)", "",
+                vs, nt);
   return KDA_OK;
 }
 
 // How one head's 128x128 state is spread over warps.  The recurrence is a serial chain per
 // head whose step time is set by the tensor-pipe issue rate of one SM sub-partition, so the
-// aim is one consumer warp per sub-partition for as long as the heads leave room:
-// ksplit warps share a 16-row tile (they split K), vsplit CTAs share a head (they split V).
-void pick_split(const KdaFwdArgs* a, int* vsplit, int* ksplit) {
+// aim is one consumer warp per sub-partition for as long as the heads leave room: a warp
+// owns ntile 8-row tiles of the state, vsplit CTAs share a head.
+void pick_split(const KdaFwdArgs* a, int* vsplit, int* ntile) {
   int dev = 0, sms = 148;
   if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   const long long bh = static_cast<long long>(a->B) * a->H;
-  const long long tiles = bh * 8, slots = 4LL * sms;
-  int ks = a->k2_ksplit;
-  if (ks == 0) {
-    ks = (tiles * 4 <= slots) ? 4 : (tiles * 2 <= slots) ? 2 : 1;
-    if (a->k2_vsplit != 0 && ks > a->k2_vsplit) ks = a->k2_vsplit;   // (8 / vsplit) * ksplit <= 8
+  int nt = a->k2_ntile;
+  if (nt == 0) {
+    nt = (bh * 16 <= 8LL * sms) ? 1 : 2;      // up to two narrow warps per sub-partition, else wide warps
+    if (a->k2_vsplit == 16) nt = 1;
+    if (a->k2_vsplit == 2) nt = 2;
   }
   int vs = a->k2_vsplit;
   if (vs == 0) {
-    const int vw_max = 8 / ks;                 // at most 8 consumer warps per CTA
-    int vw = vw_max;
-    for (int cand = 1; cand <= vw_max; cand *= 2)   // smallest slice that still gives every CTA its own SM
-      if (bh * (8 / cand) <= sms) { vw = cand; break; }
-    vs = 8 / vw;
+    const int vs_max = 16 / nt, vs_min = 4 / nt;   // 1 .. 4 consumer warps per CTA
+    vs = vs_min;
+    for (int cand = vs_max; cand >= vs_min; cand /= 2)   // most CTAs that still get an SM each
+      if (bh * cand <= sms) { vs = cand; break; }
+    if (vs * nt == 16 && bh * vs * 2 > sms) vs /= 2;    // prefer >= 2 warps per CTA unless SMs are plentiful
   }
   *vsplit = vs;
-  *ksplit = ks;
+  *ntile = nt;
 }
 
 int* status_ptr(const KdaFwdArgs* a) { return static_cast<int*>(a->workspace); }
@@ -135,10 +136,9 @@ int do_k2(const KdaFwdArgs* a, bool state_only, int zero_u, cudaStream_t st) {
   for (int i = 0; i < 3; ++i) p.o_s[i] = a->o_stride[i];
   p.scale = a->scale;
   p.zero_u = zero_u;
-  int vsplit = 1, ksplit = 1;
-  pick_split(a, &vsplit, &ksplit);
-  if ((8 / vsplit) * ksplit > 8) vsplit = ksplit;   // one of the two was forced: keep the CTA at 8 warps
-  cudaError_t e = kda::launch_k2(p, vsplit, ksplit, state_only, st);
+  int vsplit = 4, ntile = 1;
+  pick_split(a, &vsplit, &ntile);
+  cudaError_t e = kda::launch_k2(p, vsplit, ntile, state_only, st);
   if (e != cudaSuccess) return fail(KDA_ERR_CUDA, "kda: K2 launch failed: %s", cudaGetErrorString(e));
   ++g_launches;
   return KDA_OK;

@@ -15,7 +15,9 @@
 //   16384   512    Aqk_h bf16 [16 i][16 j] row-major \ hi/lo split of the scaled lower
 //   16896   512    Aqk_l bf16 [16][16]               / triangle (incl. diagonal)
 //   17408   512    dec  fp32 [128]      = 2^(g_last)
-//   17920   8192   uT   fp32, mma-fragment order [8 vtile][2 ntile][32 lane][4]
+//   17920   8192   u    fp32, accumulator-fragment order [16 column tile][32 lane][4]:
+//                       lane (g = lane/4, t = lane%4) holds u[tok g][v], u[tok g][v+1],
+//                       u[tok g+8][v], u[tok g+8][v+1] with v = 8*tile + 2t
 //
 // Swizzled bf16 tile: element (r, c) of a [16][128] tile lives at byte
 //   r*256 + ((((c>>3) ^ (r&7)) << 4) | ((c&7) << 1))
@@ -41,7 +43,7 @@ constexpr int REC_AQL = 16896;
 constexpr int REC_DEC = 17408;
 constexpr int REC_U = 17920;
 constexpr int REC_SHARED_BYTES = 17920;  // everything every V-slice needs
-constexpr int REC_U_TILE_BYTES = 1024;   // one 16-row V tile of uT
+constexpr int REC_U_TILE_BYTES = 512;    // one 8-column tile of u
 constexpr int REC_BYTES = 26112;
 constexpr int WS_HEADER_BYTES = 256;     // status block at the start of the workspace
 
@@ -160,6 +162,12 @@ __device__ __forceinline__ void ldsm_x4_t(uint32_t addr, uint32_t& r0, uint32_t&
   asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
                : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
                : "r"(addr));
+}
+// transpose an 8x8 b16 matrix held as one register per lane (fragment layout) inside the warp
+__device__ __forceinline__ uint32_t movmatrix_t(uint32_t a) {
+  uint32_t d;
+  asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(d) : "r"(a));
+  return d;
 }
 __device__ __forceinline__ void ldsm_x2(uint32_t addr, uint32_t& r0, uint32_t& r1) {
   asm volatile("ldmatrix.sync.aligned.m8n8.x2.shared.b16 {%0,%1}, [%2];" : "=r"(r0), "=r"(r1) : "r"(addr));

@@ -379,49 +379,42 @@ __global__ void __launch_bounds__(128, 4) kda_k1_kernel(const K1Params p) {
   }
   __syncthreads();
 
-  // ---- phase E: uT = (v beta)^T X^T (fp32-like), w = X (khat beta 2^g) (bf16) ----
+  // ---- phase E: u = X (v beta) (fp32-like, three split MMAs), w = X (khat beta 2^g) (bf16) ----
   {
-    // X as B operand of uT (stored [N=i][K=m]) and as A operand of w (row-major [M=i][K=m])
-    uint32_t xbh[4], xbl[4], xah[4], xal[4];
+    // X as A operand (row-major [M=i][K=m]), hi and lo parts
+    uint32_t xah[4], xal[4];
     {
-      const int row = (lane & 7) + (lane >> 4) * 8, col = ((lane >> 3) & 1) * 8;
-      ldsm_x4(sbase + SM::XH + (row * 16 + col) * 2, xbh[0], xbh[1], xbh[2], xbh[3]);
-      ldsm_x4(sbase + SM::XL + (row * 16 + col) * 2, xbl[0], xbl[1], xbl[2], xbl[3]);
       const int row2 = (lane & 7) + ((lane >> 3) & 1) * 8, col2 = (lane >> 4) * 8;
       ldsm_x4(sbase + SM::XH + (row2 * 16 + col2) * 2, xah[0], xah[1], xah[2], xah[3]);
       ldsm_x4(sbase + SM::XL + (row2 * 16 + col2) * 2, xal[0], xal[1], xal[2], xal[3]);
     }
-#pragma unroll
-    for (int vi = 0; vi < 2; ++vi) {
-      const int vt = warp * 2 + vi;
-      const int tok = (lane & 7) + (lane >> 4) * 8, vcol = vt * 16 + ((lane >> 3) & 1) * 8;
-      uint32_t avh[4], avl[4];
-      ldsm_x4_t(sbase + S_VBH + swz_off(tok, vcol), avh[0], avh[1], avh[2], avh[3]);
-      ldsm_x4_t(sbase + S_VBL + swz_off(tok, vcol), avl[0], avl[1], avl[2], avl[3]);
-#pragma unroll
-      for (int j = 0; j < 2; ++j) {
-        float acc[4] = {0, 0, 0, 0}, accl[4] = {0, 0, 0, 0};
-        mma_bf16(acc, avh, xbh[2 * j], xbh[2 * j + 1]);
-        mma_bf16(accl, avl, xbh[2 * j], xbh[2 * j + 1]);
-        mma_bf16(accl, avh, xbl[2 * j], xbl[2 * j + 1]);
-        *reinterpret_cast<float4*>(smem + S_UF + ((vt * 2 + j) * 32 + lane) * 16) =
-            make_float4(acc[0] + accl[0], acc[1] + accl[1], acc[2] + accl[2], acc[3] + accl[3]);
-      }
-    }
+    // B operands come from [tok][col] tiles through transposing ldmatrix; one x4 covers 16 columns
+    const int btok = (lane & 7) + ((lane >> 3) & 1) * 8;
 #pragma unroll
     for (int ni = 0; ni < 2; ++ni) {
       const int n0 = warp * 32 + ni * 16;
-      const int tok = (lane & 7) + ((lane >> 3) & 1) * 8, kcol = n0 + (lane >> 4) * 8;
-      uint32_t bk[4];
-      ldsm_x4_t(sbase + S_KBH + swz_off(tok, kcol), bk[0], bk[1], bk[2], bk[3]);
+      const int ccol = n0 + (lane >> 4) * 8;
+      uint32_t bvh[4], bvl[4], bk[4];
+      ldsm_x4_t(sbase + S_VBH + swz_off(btok, ccol), bvh[0], bvh[1], bvh[2], bvh[3]);
+      ldsm_x4_t(sbase + S_VBL + swz_off(btok, ccol), bvl[0], bvl[1], bvl[2], bvl[3]);
+      ldsm_x4_t(sbase + S_KBH + swz_off(btok, ccol), bk[0], bk[1], bk[2], bk[3]);
 #pragma unroll
       for (int j = 0; j < 2; ++j) {
-        float acc[4] = {0, 0, 0, 0};
-        mma_bf16(acc, xah, bk[2 * j], bk[2 * j + 1]);
-        mma_bf16(acc, xal, bk[2 * j], bk[2 * j + 1]);
+        // u tile: tokens x 8 value columns, stored as the raw accumulator fragment (K2 reads it back
+        // into the same fragment): [column tile][lane][4]
+        float acc[4] = {0, 0, 0, 0}, accl[4] = {0, 0, 0, 0};
+        mma_bf16(acc, xah, bvh[2 * j], bvh[2 * j + 1]);
+        mma_bf16(accl, xal, bvh[2 * j], bvh[2 * j + 1]);
+        mma_bf16(accl, xah, bvl[2 * j], bvl[2 * j + 1]);
+        const int vtile = (n0 >> 3) + j;
+        *reinterpret_cast<float4*>(smem + S_UF + (vtile * 32 + lane) * 16) =
+            make_float4(acc[0] + accl[0], acc[1] + accl[1], acc[2] + accl[2], acc[3] + accl[3]);
+        float accw[4] = {0, 0, 0, 0};
+        mma_bf16(accw, xah, bk[2 * j], bk[2 * j + 1]);
+        mma_bf16(accw, xal, bk[2 * j], bk[2 * j + 1]);
         const int kc = n0 + j * 8 + tq * 2;
-        *reinterpret_cast<uint32_t*>(smem + S_W + swz_off(gq, kc)) = pack_bf16(acc[0], acc[1]);
-        *reinterpret_cast<uint32_t*>(smem + S_W + swz_off(gq + 8, kc)) = pack_bf16(acc[2], acc[3]);
+        *reinterpret_cast<uint32_t*>(smem + S_W + swz_off(gq, kc)) = pack_bf16(accw[0], accw[1]);
+        *reinterpret_cast<uint32_t*>(smem + S_W + swz_off(gq + 8, kc)) = pack_bf16(accw[2], accw[3]);
       }
     }
   }

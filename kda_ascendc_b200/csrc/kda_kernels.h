@@ -37,9 +37,8 @@ struct K2Params {
 };
 
 cudaError_t launch_k1(const K1Params& p, bool g_bf16, bool fast_exp, cudaStream_t stream);
-// vsplit in {1,2,4,8}: CTAs per (batch, head), each owns 128/vsplit rows of the state;
-// ksplit in {1,2,4}: warps per 16-row tile, each owns 128/ksplit columns.  Only the
-// combinations with (8/vsplit)*ksplit <= 8 consumer warps per CTA exist.
-cudaError_t launch_k2(const K2Params& p, int vsplit, int ksplit, bool state_only, cudaStream_t stream);
+// vsplit: CTAs per (batch, head), each owns 128/vsplit rows of the state; ntile in {1,2}:
+// 8-row state tiles per warp.  16 / (vsplit * ntile) consumer warps per CTA must be 1, 2, 4 or 8.
+cudaError_t launch_k2(const K2Params& p, int vsplit, int ntile, bool state_only, cudaStream_t stream);
 
 }  // namespace kda

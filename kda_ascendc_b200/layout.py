@@ -41,14 +41,13 @@ def _swizzle_index(device) -> torch.Tensor:
 
 
 def _u_index(device) -> torch.Tensor:
-    """Position (in fp32 elements) of u[tok][v] inside the fragment-ordered uT block."""
+    """Position (in fp32 elements) of u[tok][v] inside the fragment-ordered u block."""
     tok = torch.arange(CHUNK, device=device)[:, None]
     v = torch.arange(D, device=device)[None, :]
-    vt, vr = v // 16, v % 16
-    j, tr = tok // 8, tok % 8
-    lane = (vr % 8) * 4 + tr // 2
-    e = (vr // 8) * 2 + tr % 2
-    return (((vt * 2 + j) * 32 + lane) * 4 + e).reshape(-1)
+    tile, vr = v // 8, v % 8
+    lane = (tok % 8) * 4 + vr // 2
+    e = (tok // 8) * 2 + vr % 2
+    return ((tile * 32 + lane) * 4 + e).reshape(-1)
 
 
 def unpack_records(workspace: torch.Tensor, B: int, T: int, H: int) -> dict:
