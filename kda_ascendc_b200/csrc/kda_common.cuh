@@ -205,6 +205,12 @@ __device__ __forceinline__ void split_pack(float x0, float x1, uint32_t& hi, uin
   hi = pack_bf16(x0, x1);
   lo = pack_bf16(x0 - bf16_lo_to_f32(hi), x1 - bf16_hi_to_f32(hi));
 }
+// packed variant on a float2 (one f32x2 FMA for the residual)
+__device__ __forceinline__ void split_pack2(float2 x, uint32_t& hi, uint32_t& lo) {
+  hi = pack_bf16(x.x, x.y);
+  const float2 r = __ffma2_rn(make_float2(bf16_lo_to_f32(hi), bf16_hi_to_f32(hi)), make_float2(-1.f, -1.f), x);
+  lo = pack_bf16(r.x, r.y);
+}
 __device__ __forceinline__ float rcpf(float x) {
   float y;
   asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));

@@ -40,8 +40,8 @@ struct K1Smem {
   static constexpr int G_BYTES = G_BF16 ? 4096 : 8192;
   static constexpr int SMALL = S_G + G_BYTES;
   // L, X live in the gate tile, which is dead once phase B has read it
-  static constexpr int L = S_G;               // fp32 [16][17]
-  static constexpr int XH = S_G + 1088;       // bf16 [16][16]
+  static constexpr int L = S_G;               // fp32 [16][16], holds -Akk
+  static constexpr int XH = S_G + 1024;       // bf16 [16][16]
   static constexpr int XL = XH + 512;
   static constexpr int RNQ = SMALL;           // fp32 [16]
   static constexpr int RNK = RNQ + 64;
@@ -182,81 +182,79 @@ __global__ void __launch_bounds__(128, 4) kda_k1_kernel(const K1Params p) {
   __syncthreads();
 
   // ---- phase B: thread = (column pair, row half): gate, cumsum, gated operands ----
-  // Two adjacent columns per thread so that every bf16 conversion is the packed
-  // cvt.rn.bf16x2 (full-rate pipe) and every tile store is 32 bits wide.
+  // Two adjacent columns per thread: every bf16 conversion is the packed cvt.rn.bf16x2
+  // (full-rate pipe), every tile store is 32 bits wide and the fp32 arithmetic runs as
+  // packed f32x2 instructions.
+  // Centring of the Gram exponents.  General path: the chunk's middle row, as in the reference
+  // (src/kda_bt16/kernels.py:129-139), which keeps every factor finite for any lower_bound
+  // in (-11, 0).  FAST_EXP (16*|lower_bound|*RCP_LN2 <= 120, e.g. the production -5): the
+  // LAST row, where 2^(g_last-g) <= 1 is exactly K2's kg operand, so the Grams reuse the kg
+  // tiles as their B operand and 2^g = 2^(g-g_last) * 2^g_last costs no third exponential.
   const int cp = tid & 63, rh = tid >> 6;
   const int c0 = cp * 2, r0 = rh * 8;
   uint32_t kbh[8], vbh[8], vbl[8];
   {
-    float gv[2][8];
-    float gmid0, gmid1, glast0, glast1;
+    float2 gv[8];
+    float2 gmid, glast;
+    auto ld_g = [&](int r) -> float2 {
+      if (G_BF16) {
+        const uint32_t gp = *reinterpret_cast<const uint32_t*>(smem + S_G + (r * D + c0) * 2);
+        return make_float2(bf16_lo_to_f32(gp), bf16_hi_to_f32(gp));
+      }
+      return *reinterpret_cast<const float2*>(smem + S_G + (r * D + c0) * 4);
+    };
     if (use_gate) {
-      const float nA = -expA * 1.4426950408889634f;  // exp(-z) = 2^(nA * (x + bias))
+      // exp(-z) = 2^(nA * x + nb) with nA = -exp(A_log) log2(e), nb = nA * bias
+      const float nA = -expA * 1.4426950408889634f;
+      const float2 nA2 = make_float2(nA, nA), nb2 = make_float2(nA * bias0, nA * bias1);
+      const float2 one2 = make_float2(1.f, 1.f);
+      const float lbr = p.lower_bound * RCP_LN2;
       const int mid = min(BT / 2, nvalid - 1);
-      float run0 = 0.f, run1 = 0.f, m0 = 0.f, m1 = 0.f;
+      float2 run = make_float2(0.f, 0.f), gm = run;
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
         const int r = r0 + i;
-        float x0, x1;
-        if (G_BF16) {
-          const uint32_t gp = *reinterpret_cast<const uint32_t*>(smem + S_G + (r * D + c0) * 2);
-          x0 = bf16_lo_to_f32(gp); x1 = bf16_hi_to_f32(gp);
-        } else {
-          const float2 gp = *reinterpret_cast<const float2*>(smem + S_G + (r * D + c0) * 4);
-          x0 = gp.x; x1 = gp.y;
-        }
-        const float s0 = rcpf(1.0f + ex2f(nA * (x0 + bias0)));
-        const float s1 = rcpf(1.0f + ex2f(nA * (x1 + bias1)));
-        float gate0 = (p.lower_bound * s0) * RCP_LN2, gate1 = (p.lower_bound * s1) * RCP_LN2;
-        if (r >= nvalid) { gate0 = 0.f; gate1 = 0.f; }
-        run0 += gate0; run1 += gate1;
-        gv[0][i] = run0; gv[1][i] = run1;
-        if (r == mid) { m0 = run0; m1 = run1; }
+        const float2 z = __ffma2_rn(ld_g(r), nA2, nb2);
+        const float2 den = __fadd2_rn(make_float2(ex2f(z.x), ex2f(z.y)), one2);
+        const float lb_r = (r < nvalid) ? lbr : 0.f;           // rows past the end add nothing
+        const float2 gate = __fmul2_rn(make_float2(rcpf(den.x), rcpf(den.y)), make_float2(lb_r, lb_r));
+        run = __fadd2_rn(run, gate);
+        gv[i] = run;
+        if (r == mid) gm = run;
       }
       // rows 8..15 need the sum over rows 0..7, all rows need g[mid] and g[last]
-      if (rh == 0) *reinterpret_cast<float2*>(sTot + c0) = make_float2(run0, run1);
+      if (rh == 0) *reinterpret_cast<float2*>(sTot + c0) = run;
       __syncthreads();
       if (rh == 1) {
         const float2 t = *reinterpret_cast<const float2*>(sTot + c0);
 #pragma unroll
-        for (int i = 0; i < 8; ++i) { gv[0][i] += t.x; gv[1][i] += t.y; }
-        m0 += t.x; m1 += t.y;
-        *reinterpret_cast<float2*>(sGlast + c0) = make_float2(gv[0][7], gv[1][7]);
+        for (int i = 0; i < 8; ++i) gv[i] = __fadd2_rn(gv[i], t);
+        gm = __fadd2_rn(gm, t);
+        *reinterpret_cast<float2*>(sGlast + c0) = gv[7];
       }
-      if (rh == (mid >> 3)) *reinterpret_cast<float2*>(sGmid + c0) = make_float2(m0, m1);
+      if (rh == (mid >> 3)) *reinterpret_cast<float2*>(sGmid + c0) = gm;
       __syncthreads();
-      const float2 gm = *reinterpret_cast<const float2*>(sGmid + c0);
-      const float2 gl = *reinterpret_cast<const float2*>(sGlast + c0);
-      gmid0 = gm.x; gmid1 = gm.y; glast0 = gl.x; glast1 = gl.y;
+      gmid = *reinterpret_cast<const float2*>(sGmid + c0);
+      glast = *reinterpret_cast<const float2*>(sGlast + c0);
     } else {
       // g already holds the chunk-local log2 cumsum; rows past the end repeat the last valid row
-      auto ldg = [&](int r) -> float2 {
-        if (G_BF16) {
-          const uint32_t gp = *reinterpret_cast<const uint32_t*>(smem + S_G + (r * D + c0) * 2);
-          return make_float2(bf16_lo_to_f32(gp), bf16_hi_to_f32(gp));
-        }
-        return *reinterpret_cast<const float2*>(smem + S_G + (r * D + c0) * 4);
-      };
 #pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        const float2 x = ldg(min(r0 + i, nvalid - 1));
-        gv[0][i] = x.x; gv[1][i] = x.y;
-      }
-      const float2 xm = ldg(min(BT / 2, nvalid - 1)), xl = ldg(nvalid - 1);
-      gmid0 = xm.x; gmid1 = xm.y; glast0 = xl.x; glast1 = xl.y;
+      for (int i = 0; i < 8; ++i) gv[i] = ld_g(min(r0 + i, nvalid - 1));
+      gmid = ld_g(min(BT / 2, nvalid - 1));
+      glast = ld_g(nvalid - 1);
     }
-    const float c1_0 = ex2f(gmid0), c1_1 = ex2f(gmid1);
-    const float c2_0 = ex2f(glast0 - gmid0), c2_1 = ex2f(glast1 - gmid1);
-    if (rh == 1) *reinterpret_cast<float2*>(smem + S_DEC + c0 * 4) = make_float2(ex2f(glast0), ex2f(glast1));
+    const float2 dec2 = make_float2(ex2f(glast.x), ex2f(glast.y));
+    if (rh == 1) *reinterpret_cast<float2*>(smem + S_DEC + c0 * 4) = dec2;
 
     if (p.g_out != nullptr) {
 #pragma unroll
       for (int i = 0; i < 8; ++i)
         if (r0 + i < nvalid)
-          *reinterpret_cast<float2*>(p.g_out + ((static_cast<size_t>(b) * p.T + t0 + r0 + i) * p.H + h) * D + c0) =
-              make_float2(gv[0][i], gv[1][i]);
+          *reinterpret_cast<float2*>(p.g_out + ((static_cast<size_t>(b) * p.T + t0 + r0 + i) * p.H + h) * D + c0) = gv[i];
     }
 
+    const float2 centre = FAST_EXP ? glast : gmid;
+    const float2 ncentre = make_float2(-centre.x, -centre.y);
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
       const int r = r0 + i;
@@ -264,37 +262,45 @@ __global__ void __launch_bounds__(128, 4) kda_k1_kernel(const K1Params p) {
       const uint32_t qp = *reinterpret_cast<const uint32_t*>(smem + S_Q + (r * D + c0) * 2);
       const uint32_t kp = *reinterpret_cast<const uint32_t*>(smem + S_K + (r * D + c0) * 2);
       const uint32_t vp = *reinterpret_cast<const uint32_t*>(smem + S_V + (r * D + c0) * 2);
-      float qn0 = bf16_lo_to_f32(qp), qn1 = bf16_hi_to_f32(qp);
-      float kn0 = bf16_lo_to_f32(kp), kn1 = bf16_hi_to_f32(kp);
+      float2 qn = make_float2(bf16_lo_to_f32(qp), bf16_hi_to_f32(qp));
+      float2 kn = make_float2(bf16_lo_to_f32(kp), bf16_hi_to_f32(kp));
       if (use_l2) {
         const float rq = sRnq[r], rk = sRnk[r];
-        const uint32_t qr = pack_bf16(qn0 * rq, qn1 * rq), kr = pack_bf16(kn0 * rk, kn1 * rk);
-        qn0 = bf16_lo_to_f32(qr); qn1 = bf16_hi_to_f32(qr);
-        kn0 = bf16_lo_to_f32(kr); kn1 = bf16_hi_to_f32(kr);
+        const float2 a = __fmul2_rn(qn, make_float2(rq, rq)), c = __fmul2_rn(kn, make_float2(rk, rk));
+        const uint32_t qr = pack_bf16(a.x, a.y), kr = pack_bf16(c.x, c.y);
+        qn = make_float2(bf16_lo_to_f32(qr), bf16_hi_to_f32(qr));
+        kn = make_float2(bf16_lo_to_f32(kr), bf16_hi_to_f32(kr));
       }
       const float br = sBeta[r];
-      const float e0 = ex2f(gv[0][i] - gmid0), e1 = ex2f(gv[1][i] - gmid1);
-      const float en0 = ex2f(gmid0 - gv[0][i]), en1 = ex2f(gmid1 - gv[1][i]);
-      float eg0, eg1, ekg0, ekg1;
-      if (FAST_EXP) { eg0 = e0 * c1_0; eg1 = e1 * c1_1; ekg0 = en0 * c2_0; ekg1 = en1 * c2_1; }
-      else { eg0 = ex2f(gv[0][i]); eg1 = ex2f(gv[1][i]); ekg0 = ex2f(glast0 - gv[0][i]); ekg1 = ex2f(glast1 - gv[1][i]); }
-
+      const float2 d = __fadd2_rn(gv[i], ncentre);                  // g - centre
+      const float2 e = make_float2(ex2f(d.x), ex2f(d.y));           // 2^(g - centre)
+      const float2 en = make_float2(ex2f(-d.x), ex2f(-d.y));        // 2^(centre - g)
+      float2 eg, ekg;                                               // 2^g, 2^(g_last - g)
+      if (FAST_EXP) { eg = __fmul2_rn(e, dec2); ekg = en; }
+      else {
+        eg = make_float2(ex2f(gv[i].x), ex2f(gv[i].y));
+        ekg = make_float2(ex2f(glast.x - gv[i].x), ex2f(glast.y - gv[i].y));
+      }
       uint32_t hi, lo;
-      split_pack(qn0 * e0, qn1 * e1, hi, lo);
+      split_pack2(__fmul2_rn(qn, e), hi, lo);
       *reinterpret_cast<uint32_t*>(smem + S_QGH + off) = hi;
       *reinterpret_cast<uint32_t*>(smem + S_QGL + off) = lo;
-      split_pack(kn0 * e0, kn1 * e1, hi, lo);
+      split_pack2(__fmul2_rn(kn, e), hi, lo);
       *reinterpret_cast<uint32_t*>(smem + S_KQH + off) = hi;
       *reinterpret_cast<uint32_t*>(smem + S_KQL + off) = lo;
-      split_pack(kn0 * en0, kn1 * en1, hi, lo);
-      *reinterpret_cast<uint32_t*>(smem + S_KNH + off) = hi;
-      *reinterpret_cast<uint32_t*>(smem + S_KNL + off) = lo;
-      *reinterpret_cast<uint32_t*>(smem + S_QG + off) = pack_bf16(qn0 * eg0, qn1 * eg1);
-      split_pack(kn0 * ekg0, kn1 * ekg1, hi, lo);
+      if (!FAST_EXP) {
+        split_pack2(__fmul2_rn(kn, en), hi, lo);
+        *reinterpret_cast<uint32_t*>(smem + S_KNH + off) = hi;
+        *reinterpret_cast<uint32_t*>(smem + S_KNL + off) = lo;
+      }
+      split_pack2(__fmul2_rn(kn, ekg), hi, lo);
       *reinterpret_cast<uint32_t*>(smem + S_KGH + off) = hi;
       *reinterpret_cast<uint32_t*>(smem + S_KGL + off) = lo;
-      kbh[i] = pack_bf16((kn0 * br) * eg0, (kn1 * br) * eg1);
-      split_pack(bf16_lo_to_f32(vp) * br, bf16_hi_to_f32(vp) * br, vbh[i], vbl[i]);
+      const float2 qgo = __fmul2_rn(qn, eg);
+      *reinterpret_cast<uint32_t*>(smem + S_QG + off) = pack_bf16(qgo.x, qgo.y);
+      const float2 kbv = __fmul2_rn(__fmul2_rn(kn, make_float2(br, br)), eg);
+      kbh[i] = pack_bf16(kbv.x, kbv.y);
+      split_pack2(__fmul2_rn(make_float2(bf16_lo_to_f32(vp), bf16_hi_to_f32(vp)), make_float2(br, br)), vbh[i], vbl[i]);
     }
   }
   __syncthreads();  // every thread has read its q/k/v/g elements: the input tiles may be overwritten
@@ -322,8 +328,8 @@ __global__ void __launch_bounds__(128, 4) kda_k1_kernel(const K1Params p) {
       uint32_t ah[4], al[4], bh0, bh1, bl0, bl1;
       ldsm_x4(a_hi + swz_off(arow, ks * 16 + acol), ah[0], ah[1], ah[2], ah[3]);
       ldsm_x4(a_lo + swz_off(arow, ks * 16 + acol), al[0], al[1], al[2], al[3]);
-      ldsm_x2(sbase + S_KNH + swz_off(brow, ks * 16 + bcol), bh0, bh1);
-      ldsm_x2(sbase + S_KNL + swz_off(brow, ks * 16 + bcol), bl0, bl1);
+      ldsm_x2(sbase + (FAST_EXP ? S_KGH : S_KNH) + swz_off(brow, ks * 16 + bcol), bh0, bh1);
+      ldsm_x2(sbase + (FAST_EXP ? S_KGL : S_KNL) + swz_off(brow, ks * 16 + bcol), bl0, bl1);
       mma_bf16(acc0, ah, bh0, bh1);
       mma_bf16(acc1, ah, bl0, bl1);
       mma_bf16(acc2, al, bh0, bh1);
@@ -347,23 +353,31 @@ __global__ void __launch_bounds__(128, 4) kda_k1_kernel(const K1Params p) {
       for (int hrow = 0; hrow < 2; ++hrow) {
         const int i = gq + hrow * 8;
         const float bi = sBeta[i];
-        sL[i * 17 + j0] = (i > j0) ? acc0[hrow * 2] * bi : 0.f;
-        sL[i * 17 + j0 + 1] = (i > j0 + 1) ? acc0[hrow * 2 + 1] * bi : 0.f;
+        // the solve consumes -Akk
+        *reinterpret_cast<float2*>(sL + i * 16 + j0) =
+            make_float2((i > j0) ? -acc0[hrow * 2] * bi : 0.f, (i > j0 + 1) ? -acc0[hrow * 2 + 1] * bi : 0.f);
       }
     }
   }
   __syncthreads();
 
   // ---- phase D: X = (I + L)^-1, lane j of warp 0 owns column j ---------------
+  // Column sweep (right-looking): once x[m] is final, every later row takes its update, so the
+  // dependent chain is 16 FMAs long; -L is read four columns at a time.
   if (warp == 0 && lane < 16) {
     float x[BT];
 #pragma unroll
     for (int i = 0; i < BT; ++i) x[i] = (i == lane) ? 1.f : 0.f;
 #pragma unroll
-    for (int m = 0; m < BT - 1; ++m) {
-      const float xm = x[m];
+    for (int mb = 0; mb < 4; ++mb) {
 #pragma unroll
-      for (int i = m + 1; i < BT; ++i) x[i] = fmaf(-sL[i * 17 + m], xm, x[i]);
+      for (int i = mb * 4 + 1; i < BT; ++i) {
+        const float4 l4 = *reinterpret_cast<const float4*>(sL + i * 16 + mb * 4);
+        const float lv[4] = {l4.x, l4.y, l4.z, l4.w};
+#pragma unroll
+        for (int mm = 0; mm < 4; ++mm)
+          if (mb * 4 + mm < i) x[i] = fmaf(lv[mm], x[mb * 4 + mm], x[i]);
+      }
     }
 #pragma unroll
     for (int i = 0; i < BT; ++i) {
