@@ -18,46 +18,59 @@
 //
 // Data movement: the four 16x128 input tiles arrive by per-row bulk (TMA) copies that
 // complete on one mbarrier (rows may be strided: head-shard views need no copy); the
-// 26,112-byte chunk record leaves by three bulk stores.  See kda_common.cuh for the
+// 26,112-byte chunk record leaves by four bulk stores.  See kda_common.cuh for the
 // record layout.
 #include "kda_common.cuh"
 #include "kda_kernels.h"
 
 namespace kda {
 
-// shared-memory map (bytes)
-constexpr int S_QG = 0, S_KGH = 4096, S_KGL = 8192, S_AQK = 12288, S_AQL = 12800, S_DEC = 13312;  // -> record[4096, 17920)
-constexpr int S_GRAM = 13824;
+// shared-memory map (bytes).  Sized so that five CTAs of the production variant (bf16 gate,
+// FAST_EXP) fit one SM: 5 * (45,648 + 1 KB) <= 228 KB.
+constexpr int S_QG = 0, S_KGH = 4096, S_KGL = 8192;   // -> record[4096, 16384)
+constexpr int S_GRAM = 12288;
 constexpr int S_QGH = S_GRAM, S_QGL = S_GRAM + 4096, S_KQH = S_GRAM + 8192, S_KQL = S_GRAM + 12288,
-              S_KNH = S_GRAM + 16384, S_KNL = S_GRAM + 20480;
-constexpr int S_W = S_GRAM, S_UF = S_GRAM + 4096;  // reuse of the Gram tiles once the Grams are done
-constexpr int S_IN = S_GRAM + 24576;               // 38400
-constexpr int S_Q = S_IN, S_K = S_IN + 4096, S_V = S_IN + 8192, S_G = S_IN + 12288;
-constexpr int S_KBH = S_IN, S_VBH = S_IN + 4096, S_VBL = S_IN + 8192;  // reuse of q/k/v tiles after they are read
+              S_KNH = S_GRAM + 16384, S_KNL = S_GRAM + 20480;   // KN tiles only without FAST_EXP
+constexpr int S_W = S_GRAM, S_UF = S_GRAM + 4096;     // reuse of the Gram tiles once the Grams are done
 
-template <bool G_BF16>
+template <bool G_BF16, bool FAST_EXP>
 struct K1Smem {
+  static constexpr int IN = S_GRAM + (FAST_EXP ? 16384 : 24576);
+  static constexpr int Q = IN, K = IN + 4096, V = IN + 8192, G = IN + 12288;
+  static constexpr int KBH = IN, VBH = IN + 4096, VBL = IN + 8192;   // reuse of q/k/v tiles after they are read
   static constexpr int G_BYTES = G_BF16 ? 4096 : 8192;
-  static constexpr int SMALL = S_G + G_BYTES;
-  // L, X live in the gate tile, which is dead once phase B has read it
-  static constexpr int L = S_G;               // fp32 [16][16], holds -Akk
-  static constexpr int XH = S_G + 1024;       // bf16 [16][16]
-  static constexpr int XL = XH + 512;
-  static constexpr int RNQ = SMALL;           // fp32 [16]
-  static constexpr int RNK = RNQ + 64;
-  static constexpr int BETA = RNK + 64;
-  static constexpr int TOT = BETA + 64;       // fp32 [128] column sums of rows 0..7
-  static constexpr int GMID = TOT + 512;      // fp32 [128] g[mid]
-  static constexpr int GLAST = GMID + 512;    // fp32 [128] g[last]
-  static constexpr int MBAR = GLAST + 512;    // 8 bytes
+  // the gate tile is dead once the gate phase has read it; it then holds
+  static constexpr int L = G;                 // fp32 [16][16], -Akk
+  static constexpr int XH = G + 1024;         // bf16 [16][16]
+  static constexpr int XL = G + 1536;
+  static constexpr int AQK = G + 2048;        // bf16 [16][16] hi   |
+  static constexpr int AQL = G + 2560;        // bf16 [16][16] lo   | -> record[16384, 17920)
+  static constexpr int DEC = G + 3072;        // fp32 [128]         |
+  static constexpr int SMALL = G + G_BYTES;
+  static constexpr int BETA = SMALL;          // fp32 [16]
+  static constexpr int TOT = BETA + 64;       // fp32 [128]: column sums of rows 0..7, then g[last]
+  static constexpr int GMID = TOT + 512;      // fp32 [128] g[mid] (not needed with FAST_EXP)
+  static constexpr int MBAR = GMID + (FAST_EXP ? 0 : 512);
   static constexpr int FLAG = MBAR + 8;
   static constexpr int TOTAL = FLAG + 8;
 };
 
+// Developer facility: with -DKDA_K1_PROFILE thread 0 of a few CTAs writes clock() stamps of the
+// phases to K1Params::ainv_out (which then is NOT the inverse) -- 16 stamps per CTA.
+#ifdef KDA_K1_PROFILE
+#define K1_STAMP(i) \
+  if (tid == 0 && (blockIdx.x % 1024) == 777) reinterpret_cast<unsigned*>(p.ainv_out)[(blockIdx.x / 1024) * 16 + (i)] = (unsigned)clock();
+#else
+#define K1_STAMP(i)
+#endif
+
 template <bool G_BF16, bool FAST_EXP>
-__global__ void __launch_bounds__(128, 4) kda_k1_kernel(const K1Params p) {
+__global__ void __launch_bounds__(128, 5) kda_k1_kernel(const K1Params p) {
   extern __shared__ __align__(128) uint8_t smem[];
-  using SM = K1Smem<G_BF16>;
+  using SM = K1Smem<G_BF16, FAST_EXP>;
+  constexpr int S_Q = SM::Q, S_K = SM::K, S_V = SM::V, S_G = SM::G;
+  constexpr int S_KBH = SM::KBH, S_VBH = SM::VBH, S_VBL = SM::VBL;
+  constexpr int S_AQK = SM::AQK, S_AQL = SM::AQL, S_DEC = SM::DEC;
   const int tid = threadIdx.x;
   const int lane = tid & 31;
   const int warp = tid >> 5;
@@ -75,14 +88,13 @@ __global__ void __launch_bounds__(128, 4) kda_k1_kernel(const K1Params p) {
   const uint32_t sbase = smem_u32(smem);
   const uint32_t mbar = sbase + SM::MBAR;
   float* sL = reinterpret_cast<float*>(smem + SM::L);
-  float* sRnq = reinterpret_cast<float*>(smem + SM::RNQ);
-  float* sRnk = reinterpret_cast<float*>(smem + SM::RNK);
   float* sBeta = reinterpret_cast<float*>(smem + SM::BETA);
   float* sTot = reinterpret_cast<float*>(smem + SM::TOT);
   float* sGmid = reinterpret_cast<float*>(smem + SM::GMID);
-  float* sGlast = reinterpret_cast<float*>(smem + SM::GLAST);
+  float* sGlast = sTot;   // the thread that reads sTot[c] is the one that then writes g[last] there
   volatile int* sFlag = reinterpret_cast<volatile int*>(smem + SM::FLAG);
 
+  K1_STAMP(0)
   if (tid == 0) {
     mbar_init(mbar, 1);
     *sFlag = 0;
@@ -136,6 +148,7 @@ __global__ void __launch_bounds__(128, 4) kda_k1_kernel(const K1Params p) {
     }
   }
 
+  K1_STAMP(1)
   bool ok = true;
   if (lane == 0) ok = mbar_wait_bounded(mbar, 0, sFlag);
   if (!ok) *sFlag = 1;
@@ -150,37 +163,47 @@ __global__ void __launch_bounds__(128, 4) kda_k1_kernel(const K1Params p) {
     return;
   }
 
-  // ---- phase A: row norms (8 threads per row) -------------------------------
-  {
+  K1_STAMP(2)
+  // ---- phase A: l2-normalise q and k in place (8 threads per row, 16 elements each) ----
+  if (use_l2) {
     const int r = tid >> 3, seg = tid & 7;
-    float rq = 1.f, rk = 1.f;
-    if (use_l2) {
-      float sq = 0.f, sk = 0.f;
+    uint4 qa[2], ka[2];
+    float sq = 0.f, sk = 0.f;
 #pragma unroll
-      for (int hseg = 0; hseg < 2; ++hseg) {
-        const uint4 a = *reinterpret_cast<const uint4*>(smem + S_Q + r * 256 + seg * 32 + hseg * 16);
-        const uint4 c = *reinterpret_cast<const uint4*>(smem + S_K + r * 256 + seg * 32 + hseg * 16);
-        const uint32_t aw[4] = {a.x, a.y, a.z, a.w}, cw[4] = {c.x, c.y, c.z, c.w};
+    for (int hseg = 0; hseg < 2; ++hseg) {
+      qa[hseg] = *reinterpret_cast<const uint4*>(smem + S_Q + r * 256 + seg * 32 + hseg * 16);
+      ka[hseg] = *reinterpret_cast<const uint4*>(smem + S_K + r * 256 + seg * 32 + hseg * 16);
+      const uint32_t aw[4] = {qa[hseg].x, qa[hseg].y, qa[hseg].z, qa[hseg].w};
+      const uint32_t cw[4] = {ka[hseg].x, ka[hseg].y, ka[hseg].z, ka[hseg].w};
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          float x0 = bf16_lo_to_f32(aw[i]), x1 = bf16_hi_to_f32(aw[i]);
-          float y0 = bf16_lo_to_f32(cw[i]), y1 = bf16_hi_to_f32(cw[i]);
-          sq = fmaf(x0, x0, sq); sq = fmaf(x1, x1, sq);
-          sk = fmaf(y0, y0, sk); sk = fmaf(y1, y1, sk);
-        }
+      for (int i = 0; i < 4; ++i) {
+        const float x0 = bf16_lo_to_f32(aw[i]), x1 = bf16_hi_to_f32(aw[i]);
+        const float y0 = bf16_lo_to_f32(cw[i]), y1 = bf16_hi_to_f32(cw[i]);
+        sq = fmaf(x0, x0, sq); sq = fmaf(x1, x1, sq);
+        sk = fmaf(y0, y0, sk); sk = fmaf(y1, y1, sk);
       }
-#pragma unroll
-      for (int m = 1; m < 8; m <<= 1) {
-        sq += __shfl_xor_sync(0xffffffffu, sq, m);
-        sk += __shfl_xor_sync(0xffffffffu, sk, m);
-      }
-      rq = 1.0f / sqrtf(sq + L2NORM_EPS);
-      rk = 1.0f / sqrtf(sk + L2NORM_EPS);
     }
-    if (seg == 0) { sRnq[r] = rq; sRnk[r] = rk; }
+#pragma unroll
+    for (int m = 1; m < 8; m <<= 1) {
+      sq += __shfl_xor_sync(0xffffffffu, sq, m);
+      sk += __shfl_xor_sync(0xffffffffu, sk, m);
+    }
+    const float rq = 1.0f / sqrtf(sq + L2NORM_EPS), rk = 1.0f / sqrtf(sk + L2NORM_EPS);
+    auto scale4 = [](uint4 v, float f) {
+      uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+      for (int i = 0; i < 4; ++i) w[i] = pack_bf16(bf16_lo_to_f32(w[i]) * f, bf16_hi_to_f32(w[i]) * f);
+      return make_uint4(w[0], w[1], w[2], w[3]);
+    };
+#pragma unroll
+    for (int hseg = 0; hseg < 2; ++hseg) {
+      *reinterpret_cast<uint4*>(smem + S_Q + r * 256 + seg * 32 + hseg * 16) = scale4(qa[hseg], rq);
+      *reinterpret_cast<uint4*>(smem + S_K + r * 256 + seg * 32 + hseg * 16) = scale4(ka[hseg], rk);
+    }
   }
   __syncthreads();
 
+  K1_STAMP(3)
   // ---- phase B: thread = (column pair, row half): gate, cumsum, gated operands ----
   // Two adjacent columns per thread: every bf16 conversion is the packed cvt.rn.bf16x2
   // (full-rate pipe), every tile store is 32 bits wide and the fp32 arithmetic runs as
@@ -193,6 +216,7 @@ __global__ void __launch_bounds__(128, 4) kda_k1_kernel(const K1Params p) {
   const int cp = tid & 63, rh = tid >> 6;
   const int c0 = cp * 2, r0 = rh * 8;
   uint32_t kbh[8], vbh[8], vbl[8];
+  float2 dec2;
   {
     float2 gv[8];
     float2 gmid, glast;
@@ -232,9 +256,9 @@ __global__ void __launch_bounds__(128, 4) kda_k1_kernel(const K1Params p) {
         gm = __fadd2_rn(gm, t);
         *reinterpret_cast<float2*>(sGlast + c0) = gv[7];
       }
-      if (rh == (mid >> 3)) *reinterpret_cast<float2*>(sGmid + c0) = gm;
+      if (!FAST_EXP && rh == (mid >> 3)) *reinterpret_cast<float2*>(sGmid + c0) = gm;
       __syncthreads();
-      gmid = *reinterpret_cast<const float2*>(sGmid + c0);
+      gmid = FAST_EXP ? make_float2(0.f, 0.f) : *reinterpret_cast<const float2*>(sGmid + c0);
       glast = *reinterpret_cast<const float2*>(sGlast + c0);
     } else {
       // g already holds the chunk-local log2 cumsum; rows past the end repeat the last valid row
@@ -243,8 +267,7 @@ __global__ void __launch_bounds__(128, 4) kda_k1_kernel(const K1Params p) {
       gmid = ld_g(min(BT / 2, nvalid - 1));
       glast = ld_g(nvalid - 1);
     }
-    const float2 dec2 = make_float2(ex2f(glast.x), ex2f(glast.y));
-    if (rh == 1) *reinterpret_cast<float2*>(smem + S_DEC + c0 * 4) = dec2;
+    dec2 = make_float2(ex2f(glast.x), ex2f(glast.y));
 
     if (p.g_out != nullptr) {
 #pragma unroll
@@ -253,6 +276,7 @@ __global__ void __launch_bounds__(128, 4) kda_k1_kernel(const K1Params p) {
           *reinterpret_cast<float2*>(p.g_out + ((static_cast<size_t>(b) * p.T + t0 + r0 + i) * p.H + h) * D + c0) = gv[i];
     }
 
+    K1_STAMP(4)
     const float2 centre = FAST_EXP ? glast : gmid;
     const float2 ncentre = make_float2(-centre.x, -centre.y);
 #pragma unroll
@@ -262,15 +286,8 @@ __global__ void __launch_bounds__(128, 4) kda_k1_kernel(const K1Params p) {
       const uint32_t qp = *reinterpret_cast<const uint32_t*>(smem + S_Q + (r * D + c0) * 2);
       const uint32_t kp = *reinterpret_cast<const uint32_t*>(smem + S_K + (r * D + c0) * 2);
       const uint32_t vp = *reinterpret_cast<const uint32_t*>(smem + S_V + (r * D + c0) * 2);
-      float2 qn = make_float2(bf16_lo_to_f32(qp), bf16_hi_to_f32(qp));
-      float2 kn = make_float2(bf16_lo_to_f32(kp), bf16_hi_to_f32(kp));
-      if (use_l2) {
-        const float rq = sRnq[r], rk = sRnk[r];
-        const float2 a = __fmul2_rn(qn, make_float2(rq, rq)), c = __fmul2_rn(kn, make_float2(rk, rk));
-        const uint32_t qr = pack_bf16(a.x, a.y), kr = pack_bf16(c.x, c.y);
-        qn = make_float2(bf16_lo_to_f32(qr), bf16_hi_to_f32(qr));
-        kn = make_float2(bf16_lo_to_f32(kr), bf16_hi_to_f32(kr));
-      }
+      const float2 qn = make_float2(bf16_lo_to_f32(qp), bf16_hi_to_f32(qp));   // already normalised
+      const float2 kn = make_float2(bf16_lo_to_f32(kp), bf16_hi_to_f32(kp));
       const float br = sBeta[r];
       const float2 d = __fadd2_rn(gv[i], ncentre);                  // g - centre
       const float2 e = make_float2(ex2f(d.x), ex2f(d.y));           // 2^(g - centre)
@@ -303,8 +320,10 @@ __global__ void __launch_bounds__(128, 4) kda_k1_kernel(const K1Params p) {
       split_pack2(__fmul2_rn(make_float2(bf16_lo_to_f32(vp), bf16_hi_to_f32(vp)), make_float2(br, br)), vbh[i], vbl[i]);
     }
   }
+  K1_STAMP(5)
   __syncthreads();  // every thread has read its q/k/v/g elements: the input tiles may be overwritten
 
+  if (rh == 1) *reinterpret_cast<float2*>(smem + S_DEC + c0 * 4) = dec2;
 #pragma unroll
   for (int i = 0; i < 8; ++i) {
     const uint32_t off = swz_off(r0 + i, c0);
@@ -313,6 +332,7 @@ __global__ void __launch_bounds__(128, 4) kda_k1_kernel(const K1Params p) {
     *reinterpret_cast<uint32_t*>(smem + S_VBL + off) = vbl[i];
   }
 
+  K1_STAMP(6)
   // ---- phase C: Grams on the tensor cores (one 16x8 output tile per warp) ----
   const int gq = lane >> 2, tq = lane & 3;
   {
@@ -361,6 +381,7 @@ __global__ void __launch_bounds__(128, 4) kda_k1_kernel(const K1Params p) {
   }
   __syncthreads();
 
+  K1_STAMP(7)
   // ---- phase D: X = (I + L)^-1, lane j of warp 0 owns column j ---------------
   // Column sweep (right-looking): once x[m] is final, every later row takes its update, so the
   // dependent chain is 16 FMAs long; -L is read four columns at a time.
@@ -385,14 +406,17 @@ __global__ void __launch_bounds__(128, 4) kda_k1_kernel(const K1Params p) {
       *reinterpret_cast<unsigned short*>(smem + SM::XH + (i * 16 + lane) * 2) = bf16_bits(hi);
       *reinterpret_cast<unsigned short*>(smem + SM::XL + (i * 16 + lane) * 2) = bf16_bits(x[i] - hi);
     }
+#ifndef KDA_K1_PROFILE
     if (p.ainv_out != nullptr) {
 #pragma unroll
       for (int i = 0; i < BT; ++i)
         if (i < nvalid) p.ainv_out[((static_cast<size_t>(b) * p.T + t0 + i) * p.H + h) * BT + lane] = x[i];
     }
+#endif
   }
   __syncthreads();
 
+  K1_STAMP(8)
   // ---- phase E: u = X (v beta) (fp32-like, three split MMAs), w = X (khat beta 2^g) (bf16) ----
   {
     // X as A operand (row-major [M=i][K=m]), hi and lo parts
@@ -433,27 +457,35 @@ __global__ void __launch_bounds__(128, 4) kda_k1_kernel(const K1Params p) {
     }
   }
 
-  // ---- write the record: three bulk stores ----------------------------------
+  K1_STAMP(9)
+  // ---- write the record: four bulk stores ----------------------------------
   fence_proxy_async();
   __syncthreads();
   if (tid == 0) {
     bulk_s2g(rec + REC_W, sbase + S_W, TILE_BYTES);
-    bulk_s2g(rec + REC_QG, sbase + S_QG, REC_SHARED_BYTES - REC_QG);
+    bulk_s2g(rec + REC_QG, sbase + S_QG, REC_AQK - REC_QG);
+    bulk_s2g(rec + REC_AQK, sbase + S_AQK, REC_U - REC_AQK);
     bulk_s2g(rec + REC_U, sbase + S_UF, REC_BYTES - REC_U);
     bulk_commit();
+    K1_STAMP(10)
     bulk_wait_read_all();
   }
+  K1_STAMP(11)
 }
 
 template <bool G_BF16, bool FAST_EXP>
 static cudaError_t launch_k1_t(const K1Params& p, int nblocks, cudaStream_t stream) {
-  constexpr int smem_bytes = K1Smem<G_BF16>::TOTAL;
+  constexpr int smem_bytes = K1Smem<G_BF16, FAST_EXP>::TOTAL;
   static bool configured[64] = {};
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev < 64 && !configured[dev]) {
     cudaError_t e = cudaFuncSetAttribute(kda_k1_kernel<G_BF16, FAST_EXP>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          smem_bytes);
+    if (e != cudaSuccess) return e;
+    // ask for the full 228 KB shared-memory carve-out: the fifth resident CTA needs it
+    e = cudaFuncSetAttribute(kda_k1_kernel<G_BF16, FAST_EXP>, cudaFuncAttributePreferredSharedMemoryCarveout,
+                             cudaSharedmemCarveoutMaxShared);
     if (e != cudaSuccess) return e;
     configured[dev] = true;
   }

@@ -221,6 +221,9 @@ def make_inputs(B, T, H, seed0=42, regime="baseline", h0_std=None, g_dtype=torch
     regime "long_memory": small-magnitude inputs with slow decay
         (q,k ~ 0.2 N, v ~ 0.1 N, g ~ 0.1 N, A_log in [-1,0.2], bias ~ 0.03 N,
         lower_bound -1) so that the state carries across many chunks.
+    regime "carry": almost no decay (gate input ~ N(-6, 0.3), A_log ~ 0, lower_bound -1):
+        what a segment leaves in the state is still there many segments later, so a wrong
+        state hand-over between segments cannot hide.
     h0_std: None -> no initial state; 0.0 -> zeros; else N(0, h0_std).
     t_offset/t_total: generate tokens [t_offset, t_offset+T) of a T=t_total sequence.
     Returns a dict with q,k,v,g,beta,A_log,dt_bias,initial_state,scale,lower_bound.
@@ -247,6 +250,10 @@ def make_inputs(B, T, H, seed0=42, regime="baseline", h0_std=None, g_dtype=torch
             a = -1.0 + 1.2 * u01(1)
             bias = 0.03 * r(D)
             sq, sv, sg = 0.2, 0.1, 0.1
+        elif regime == "carry":
+            a = 0.2 * u01(1) - 0.1
+            bias = 0.03 * r(D) - 6.0        # gate ~ -0.004 log2 units per token: the state survives
+            sq, sv, sg = 1.0, 1.0, 0.3      # thousands of tokens unless the delta rule overwrites it
         else:
             raise ValueError(regime)
         A_log[hh] = a

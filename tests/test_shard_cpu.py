@@ -1,0 +1,98 @@
+"""CPU checks of the multi-GPU host logic: head ranges, the segment fold, and the
+all-gather + fold of a sequence split run as two gloo ranks (the per-segment transforms come
+from the CPU oracle here; on GPUs the kernels produce them)."""
+import os
+import socket
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from kda_ascendc_b200 import shard
+from oracle import kda_oracle as O
+
+D = 128
+
+
+def test_head_range_partitions_heads():
+    for H, G in ((32, 8), (96, 8), (5, 4), (3, 8)):
+        covered = []
+        for r in range(G):
+            lo, hi = shard.head_range(H, G, r)
+            covered += list(range(lo, hi))
+        assert covered == list(range(H))
+    assert shard.head_range(32, 8, 3) == (12, 16)
+    with pytest.raises(ValueError):
+        shard.head_range(8, 4, 4)
+
+
+def _segment_transforms(inp, lo, hi):
+    """(M_seg, Q_seg) of tokens [lo, hi) from the oracle: Q from a zero state; M from the
+    identity with v = 0 (then u = 0)."""
+    seg = {k: (v[:, lo:hi] if torch.is_tensor(v) and v.ndim >= 3 and v.shape[1] == inp["q"].shape[1] else v)
+           for k, v in inp.items()}
+    B, _, H, _ = seg["q"].shape
+    seg["initial_state"] = None
+    _, Qs = O.run_chunk_reference(seg)
+    segM = dict(seg, v=torch.zeros_like(seg["v"]),
+                initial_state=torch.eye(D).expand(B, H, D, D).contiguous())
+    _, Ms = O.run_chunk_reference(segM)
+    return seg, Ms, Qs
+
+
+def test_compose_entry_states_matches_one_pass():
+    inp = O.make_inputs(1, 96, 2, seed0=5, regime="carry", h0_std=0.1)
+    o_full, h_full = O.run_chunk_reference(inp)
+    cuts = [0, 32, 64, 96]
+    parts = [_segment_transforms(inp, a, b) for a, b in zip(cuts[:-1], cuts[1:])]
+    states = shard.compose_entry_states([p[1] for p in parts], [p[2] for p in parts], inp["initial_state"])
+    assert (states[-1] - h_full).abs().max().item() < 2e-5 * max(1.0, h_full.abs().max().item())
+    outs = []
+    for (seg, _, _), S in zip(parts, states[:-1]):
+        seg = dict(seg, initial_state=S)
+        outs.append(O.run_chunk_reference(seg)[0])
+    o_cat = torch.cat(outs, 1)
+    assert (o_cat.float() - o_full.float()).abs().max().item() <= 2.0 ** -8 * o_full.float().abs().max().item()
+    # a wrong fold (segments swapped) is far off: the check has teeth
+    bad = shard.compose_entry_states([parts[1][1], parts[0][1], parts[2][1]],
+                                     [parts[1][2], parts[0][2], parts[2][2]], inp["initial_state"])
+    assert (bad[-1] - h_full).abs().max().item() > 1e-3 * h_full.abs().max().item()
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _rank_main(rank, world, port, ret):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        torch.set_num_threads(1)
+        T = 64
+        inp = O.make_inputs(1, T, 2, seed0=9, regime="carry", h0_std=0.1)
+        L = T // world
+        seg, M, Q = _segment_transforms(inp, rank * L, (rank + 1) * L)
+        Ms, Qs = shard.exchange_segment_transforms(M, Q)
+        states = shard.compose_entry_states(Ms, Qs, inp["initial_state"])
+        o_loc, _ = O.run_chunk_reference(dict(seg, initial_state=states[rank]))
+        o_full, h_full = O.run_chunk_reference(inp)
+        eo = (o_loc.float() - o_full[:, rank * L:(rank + 1) * L].float()).abs().max().item()
+        eh = (states[world] - h_full).abs().max().item()
+        ret[rank] = (eo, eh, o_full.float().abs().max().item(), h_full.abs().max().item())
+    finally:
+        dist.destroy_process_group()
+
+
+def test_sequence_split_over_two_gloo_ranks():
+    world = 2
+    mgr = mp.Manager()
+    ret = mgr.dict()
+    mp.spawn(_rank_main, args=(world, _free_port(), ret), nprocs=world, join=True)
+    assert sorted(ret.keys()) == [0, 1]
+    for r in range(world):
+        eo, eh, omax, hmax = ret[r]
+        assert eo <= 2.0 ** -8 * omax, (r, eo)
+        assert eh <= 2e-5 * max(1.0, hmax), (r, eh)
