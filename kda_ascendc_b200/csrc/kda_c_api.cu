@@ -118,7 +118,10 @@ int do_k1(const KdaFwdArgs* a, cudaStream_t st) {
   // 2^g may be factored as 2^(g-g_mid) * 2^(g_mid) only while no factor can underflow:
   // 16 tokens * |lower_bound| * RCP_LN2 must stay inside the fp32 exponent range.
   const bool fast_exp = (a->flags & KDA_FLAG_GATE_IN_KERNEL) && (16.0f * -a->lower_bound * kda::RCP_LN2 <= 120.0f);
-  cudaError_t e = kda::launch_k1(p, a->g_dtype == KDA_G_BF16, fast_exp, st);
+  const char* what = "";
+  cudaError_t e = kda::k1_encode_tensor_maps(p, a->g_dtype == KDA_G_BF16, &what);
+  if (e != cudaSuccess) return fail(KDA_ERR_CUDA, "kda: building the TMA descriptor failed for: %s", what);
+  e = kda::launch_k1(p, a->g_dtype == KDA_G_BF16, fast_exp, st);
   if (e != cudaSuccess) return fail(KDA_ERR_CUDA, "kda: K1 launch failed: %s", cudaGetErrorString(e));
   ++g_launches;
   return KDA_OK;

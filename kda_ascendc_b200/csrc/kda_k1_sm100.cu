@@ -17,8 +17,9 @@
 // kg = khat 2^(g_last-g) as a hi/lo bf16 pair, dec = 2^g_last -- the arrangement of
 // the reference's Ascend pipeline (python/kda_ascendc_v1/api.py:890-897).
 //
-// Data movement: the four 16x128 input tiles arrive by per-row bulk (TMA) copies that
-// complete on one mbarrier (rows may be strided: head-shard views need no copy); as soon as
+// Data movement: the four 16x128 input tiles arrive by tiled TMA copies (4-D tensor maps over
+// (d, head, token, batch) built from the caller's strides, so head-shard and segment views
+// need no copy; rows past T are zero-filled by the copy) that complete on one mbarrier; as soon as
 // a chunk's inputs have been consumed the copies of the CTA's next chunk are issued into the
 // same tiles, so the ~2.5 us load latency hides behind the rest of the chunk.  Of the
 // 26,112-byte chunk record (kda_common.cuh) the qg / kg / Aqk / dec part leaves by two bulk
@@ -81,7 +82,7 @@ __device__ __forceinline__ K1Item k1_item(const K1Params& p, int id) {
 }
 
 template <bool G_BF16, bool FAST_EXP>
-__global__ void __launch_bounds__(128, 4) kda_k1_kernel(const K1Params p) {
+__global__ void __launch_bounds__(128, 4) kda_k1_kernel(const __grid_constant__ K1Params p) {
   extern __shared__ __align__(128) uint8_t smem[];
   using SM = K1Smem<G_BF16, FAST_EXP>;
   constexpr int S_Q = SM::Q, S_K = SM::K, S_V = SM::V, S_G = SM::G;
@@ -114,31 +115,16 @@ __global__ void __launch_bounds__(128, 4) kda_k1_kernel(const K1Params p) {
   }
   __syncthreads();
 
-  // issue the input copies of one work item (threads 0..63: one row of one tensor each)
+  // issue the input copies of one work item: one tiled TMA box (16 tokens x 128) per tensor.
+  // The box may reach past T in the last chunk; those rows arrive as zeros and still count
+  // towards the transaction bytes.
   auto issue_loads = [&](const K1Item& w) {
-    if (tid == 0) mbar_arrive_expect_tx(mbar, w.nvalid * (3 * ROW_BYTES + G_ROW_BYTES));
-    if (tid < 64) {
-      const int which = tid >> 4, r = tid & 15;
-      const int64_t tok = w.t0 + r;
-      if (r < w.nvalid) {
-        if (which == 0)
-          bulk_g2s(sbase + S_Q + r * ROW_BYTES, p.q + w.b * p.q_s[0] + tok * p.q_s[1] + w.h * p.q_s[2], ROW_BYTES, mbar);
-        else if (which == 1)
-          bulk_g2s(sbase + S_K + r * ROW_BYTES, p.k + w.b * p.k_s[0] + tok * p.k_s[1] + w.h * p.k_s[2], ROW_BYTES, mbar);
-        else if (which == 2)
-          bulk_g2s(sbase + S_V + r * ROW_BYTES, p.v + w.b * p.v_s[0] + tok * p.v_s[1] + w.h * p.v_s[2], ROW_BYTES, mbar);
-        else {
-          const int64_t eoff = w.b * p.g_s[0] + tok * p.g_s[1] + w.h * p.g_s[2];
-          const uint8_t* src = static_cast<const uint8_t*>(p.g) + eoff * (G_BF16 ? 2 : 4);
-          bulk_g2s(sbase + S_G + r * G_ROW_BYTES, src, G_ROW_BYTES, mbar);
-        }
-      } else {
-        // rows past the end of the sequence: zero operands (plain stores, untouched by the copies)
-        const int off = (which == 0 ? S_Q : which == 1 ? S_K : which == 2 ? S_V : S_G) +
-                        r * (which == 3 ? G_ROW_BYTES : ROW_BYTES);
-        const int nb = which == 3 ? G_ROW_BYTES : ROW_BYTES;
-        for (int i = 0; i < nb; i += 16) *reinterpret_cast<uint4*>(smem + off + i) = make_uint4(0, 0, 0, 0);
-      }
+    if (tid == 0) {
+      mbar_arrive_expect_tx(mbar, BT * (3 * ROW_BYTES + G_ROW_BYTES));
+      tma_load_4d(sbase + S_Q, &p.tm_q, 0, w.h, w.t0, w.b, mbar);
+      tma_load_4d(sbase + S_K, &p.tm_k, 0, w.h, w.t0, w.b, mbar);
+      tma_load_4d(sbase + S_V, &p.tm_v, 0, w.h, w.t0, w.b, mbar);
+      tma_load_4d(sbase + S_G, &p.tm_g, 0, w.h, w.t0, w.b, mbar);
     }
   };
   // per-item parameters, fetched one item ahead so that their global-load latency is hidden
@@ -361,7 +347,7 @@ __global__ void __launch_bounds__(128, 4) kda_k1_kernel(const K1Params p) {
 
     // ---- prefetch: the next item's inputs go into the same tiles while this one finishes ----
     if (has_next) {
-      if (tid < 64) fence_proxy_async();   // order this CTA's earlier generic accesses before the async writes
+      if (tid == 0) fence_proxy_async();   // order the earlier generic accesses (made visible by the barrier) before the async writes
       issue_loads(nxt);
     }
 
@@ -538,6 +524,50 @@ static cudaError_t launch_k1_t(const K1Params& p, cudaStream_t stream) {
   const int grid = static_cast<int>(n_items < grid_cap[dev] ? n_items : grid_cap[dev]);
   kda_k1_kernel<G_BF16, FAST_EXP><<<grid, 128, smem_bytes, stream>>>(p);
   return cudaGetLastError();
+}
+
+namespace {
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiledFn get_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (fn == nullptr) {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(ptr);
+  }
+  return fn;
+}
+}  // namespace
+
+cudaError_t k1_encode_tensor_maps(K1Params& p, bool g_bf16, const char** what) {
+  EncodeTiledFn enc = get_encode_fn();
+  if (enc == nullptr) { *what = "cuTensorMapEncodeTiled is not available from this driver"; return cudaErrorNotSupported; }
+  struct T { CUtensorMap* m; const void* ptr; const int64_t* s; CUtensorMapDataType dt; int es; const char* name; };
+  const T ts[4] = {
+      {&p.tm_q, p.q, p.q_s, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, "q"},
+      {&p.tm_k, p.k, p.k_s, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, "k"},
+      {&p.tm_v, p.v, p.v_s, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, "v"},
+      {&p.tm_g, p.g, p.g_s, g_bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32, g_bf16 ? 2 : 4, "g"}};
+  for (const T& t : ts) {
+    // dims innermost first: (d, head, token, batch); strides in bytes for dims 1..3.  A size-1
+    // dimension may come with any stride: give it a legal one (it is never stepped).
+    const cuuint64_t dims[4] = {static_cast<cuuint64_t>(D), static_cast<cuuint64_t>(p.H), static_cast<cuuint64_t>(p.T),
+                                static_cast<cuuint64_t>(p.B)};
+    cuuint64_t strides[3] = {static_cast<cuuint64_t>(t.s[2]) * t.es, static_cast<cuuint64_t>(t.s[1]) * t.es,
+                             static_cast<cuuint64_t>(t.s[0]) * t.es};
+    for (int i = 0; i < 3; ++i)
+      if (dims[i + 1] == 1 || strides[i] == 0) strides[i] = static_cast<cuuint64_t>(D) * t.es;
+    const cuuint32_t box[4] = {static_cast<cuuint32_t>(D), 1, static_cast<cuuint32_t>(BT), 1};
+    const cuuint32_t estr[4] = {1, 1, 1, 1};
+    CUresult r = enc(t.m, t.dt, 4, const_cast<void*>(t.ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                     CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) { *what = t.name; return cudaErrorInvalidValue; }
+  }
+  return cudaSuccess;
 }
 
 cudaError_t launch_k1(const K1Params& p, bool g_bf16, bool fast_exp, cudaStream_t stream) {

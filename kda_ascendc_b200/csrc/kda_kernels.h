@@ -1,5 +1,6 @@
 // Internal launch interface between the C-ABI layer and the two kernels.
 #pragma once
+#include <cuda.h>
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
@@ -7,6 +8,9 @@
 namespace kda {
 
 struct K1Params {
+  // tiled TMA descriptors of q, k, v, g viewed as 4-D tensors (d, head, token, batch) with the
+  // caller's strides; one 16-token x 128 box per (tensor, chunk).  Rows past T read as zero.
+  CUtensorMap tm_q, tm_k, tm_v, tm_g;
   const __nv_bfloat16* q;
   const __nv_bfloat16* k;
   const __nv_bfloat16* v;
@@ -37,6 +41,8 @@ struct K2Params {
 };
 
 cudaError_t launch_k1(const K1Params& p, bool g_bf16, bool fast_exp, cudaStream_t stream);
+// Fills the four tensor maps of p from its pointers, sizes and strides (host, no device work).
+cudaError_t k1_encode_tensor_maps(K1Params& p, bool g_bf16, const char** what);
 // vsplit: CTAs per (batch, head), each owns 128/vsplit rows of the state; ntile in {1,2}:
 // 8-row state tiles per warp.  16 / (vsplit * ntile) consumer warps per CTA must be 1, 2, 4 or 8.
 cudaError_t launch_k2(const K2Params& p, int vsplit, int ntile, bool state_only, cudaStream_t stream);
