@@ -48,6 +48,9 @@ K1_BYTES_PER_TH = 2084.0     # reads q,k,v,g bf16 + beta; writes w,u bf16, g fp3
 K2_BYTES_PER_TH = 1856.0     # reads w,u,q,k,g,Aqk,g_last; writes o
 K1_FLOPS_PER_CHUNK = 262144.0
 K2_FLOPS_PER_CHUNK = 1638400.0
+# dram__bytes_read.sum + dram__bytes_write.sum of ONE launch on this workload, from the ncu
+# capture summarised in profiles/kda_k1_k2_B1_T8192_H32.md (bytes per launch)
+NCU_TRAFFIC_BYTES = {"kda_k1": 641.47e6, "kda_k2": 489.36e6}
 
 
 def load_peaks():
@@ -254,21 +257,52 @@ def run_gpu_arm(steps, warmup, n_gpus, kernels_only=False):
     h2d = sum(v.numel() * v.element_size() for v in host.values())
     d2h = o_host.numel() * o_host.element_size() + ht_host.numel() * ht_host.element_size()
 
-    def e2e_step():
-        x = {k: v.to(dev, non_blocking=True) for k, v in host.items()}
-        oo, hh = K.kda_bt16_fwd(x["q"], x["k"], x["v"], x["g"], x["beta"], scale=scale, initial_state=x["h0"],
-                                output_final_state=True, use_qk_l2norm_in_kernel=True, use_gate_in_kernel=True,
-                                use_beta_sigmoid_in_kernel=True, lower_bound=-5.0, A_log=x["A_log"],
-                                dt_bias=x["dt_bias"], reuse_workspace=True)
-        o_host.copy_(oo, non_blocking=True)
-        ht_host.copy_(hh, non_blocking=True)
+    # Two steps are in flight: while step i computes, step i+1's inputs cross PCIe and step
+    # i-1's outputs go back (three streams, two device-side input slots).  Every step still
+    # copies all of its inputs from pinned host memory and all of its results back.
+    cur = torch.cuda.current_stream()
+    s_in, s_cmp, s_out = torch.cuda.Stream(), torch.cuda.Stream(), torch.cuda.Stream()
+    slots = [{k: torch.empty_like(v) for k, v in d.items()} for _ in range(2)]
+    ev_ready = [torch.cuda.Event() for _ in range(2)]
+    ev_free = [torch.cuda.Event() for _ in range(2)]
+    ev_out = [torch.cuda.Event() for _ in range(2)]
 
-    for _ in range(max(warmup, 3)):
-        e2e_step()
+    def e2e_steps(count):
+        for st_ in (s_in, s_cmp, s_out):
+            st_.wait_stream(cur)
+        for i in range(count):
+            sl = i % 2
+            with torch.cuda.stream(s_in):
+                if i >= 2:
+                    s_in.wait_event(ev_free[sl])
+                for k_, v_ in host.items():
+                    slots[sl][k_].copy_(v_, non_blocking=True)
+                ev_ready[sl].record(s_in)
+            with torch.cuda.stream(s_cmp):
+                s_cmp.wait_event(ev_ready[sl])
+                x = slots[sl]
+                oo, hh = K.kda_bt16_fwd(x["q"], x["k"], x["v"], x["g"], x["beta"], scale=scale,
+                                        initial_state=x["h0"], output_final_state=True,
+                                        use_qk_l2norm_in_kernel=True, use_gate_in_kernel=True,
+                                        use_beta_sigmoid_in_kernel=True, lower_bound=-5.0, A_log=x["A_log"],
+                                        dt_bias=x["dt_bias"], reuse_workspace=True)
+                ev_free[sl].record(s_cmp)
+            with torch.cuda.stream(s_out):
+                s_out.wait_event(ev_free[sl])
+                if i >= 2:
+                    s_out.wait_event(ev_out[sl])
+                o_host.copy_(oo, non_blocking=True)
+                ht_host.copy_(hh, non_blocking=True)
+                oo.record_stream(s_out)
+                hh.record_stream(s_out)
+                ev_out[sl].record(s_out)
+        for st_ in (s_in, s_cmp, s_out):
+            cur.wait_stream(st_)
+
+    e2e_steps(max(warmup, 3))
     barrier()
     e0.record()
-    for _ in range(steps):
-        e2e_step()
+    e2e_steps(steps)
     e1.record()
     barrier()
     e2e_ms = e0.elapsed_time(e1)
@@ -294,10 +328,11 @@ def run_gpu_arm(steps, warmup, n_gpus, kernels_only=False):
             kern[name] = dict(us=t_ms * 1e3, algorithmic_GBps=gbs, hbm_frac=gbs / hbm_gbs, TFLOPs=tf,
                               tensor_frac=tf / tc_tflops)
         dom = "kda_k2" if k2_avg >= k1_avg else "kda_k1"
-        traffic = json.loads((ROOT / "profiles" / "traffic.json").read_text()).get(dom) \
-            if (ROOT / "profiles" / "traffic.json").exists() else None
+        traffic = NCU_TRAFFIC_BYTES.get(dom)
         roofline = dict(kernel=dom, bound="hbm", achieved=kern[dom]["algorithmic_GBps"], peak=hbm_gbs, unit="GB/s",
-                        frac=kern[dom]["hbm_frac"], traffic=traffic, peak_kind=peak_kind,
+                        frac=kern[dom]["hbm_frac"], traffic=traffic, traffic_unit="bytes per launch (ncu)",
+                        algorithmic_bytes=(K2_BYTES_PER_TH if dom == "kda_k2" else K1_BYTES_PER_TH) * th,
+                        peak_kind=peak_kind,
                         tensor_frac=kern[dom]["tensor_frac"], us_per_chunk_step=(k2_avg * 1e3) / (T // BT))
         line = dict(metric=METRIC, value=tokens_per_step * steps / (ms * 1e-3), unit="tokens/s", n_gpus=world,
                     steps=steps, warmup=max(warmup, 3), ms_per_step=ms / steps, higher_is_better=True,
@@ -306,7 +341,8 @@ def run_gpu_arm(steps, warmup, n_gpus, kernels_only=False):
                                 l2="inputs + K1->K2 records = 0.7 GB per step, larger than the 126 MB L2",
                                 global_batch=world * B, seq_len=T, heads=H),
                     e2e=dict(value=tokens_per_step * steps / (e2e_ms * 1e-3), unit="tokens/s",
-                             h2d_bytes_per_step=h2d, d2h_bytes_per_step=d2h, ms_per_step=e2e_ms / steps),
+                             h2d_bytes_per_step=h2d, d2h_bytes_per_step=d2h, ms_per_step=e2e_ms / steps,
+                             api="kda_ascendc_b200.kda_bt16_fwd", pipelining="2 steps in flight over 3 streams"),
                     gpu_launches=launches, roofline=roofline, kernels=kern, clocks=clocks)
         if world == 1:
             line["cpu_baseline"] = cpu_baseline_sample()
