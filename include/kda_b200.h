@@ -101,6 +101,20 @@ int kda_fwd_k2(const KdaFwdArgs* args, void* stream);
  * feeding h0 = I yields the segment's transition matrix. */
 int kda_fwd_k2_state(const KdaFwdArgs* args, int zero_u, void* stream);
 
+/* Whole forward with the K1 -> K2 scratch taken from a fixed array inside the library instead
+ * of args->workspace (which is ignored).  It has no counterpart in the reference, whose host
+ * code always allocates its intermediates itself.  It exists for callers that cannot obtain
+ * device memory at call time -- a serving loop that gave all free GPU memory to its own pool and
+ * keeps the CUDA allocator off the request path, or a plugin whose host passes tensors but no
+ * allocator.  Limits: the problem must satisfy
+ * kda_fwd_workspace_bytes(B, T, H) <= KDA_STATIC_SCRATCH_BYTES (else KDA_ERR_INVALID_ARG, nothing
+ * runs); the array occupies that much memory on every GPU that loads the library, until exit; all
+ * calls on a device share it, so calls that may overlap on the GPU must be ordered by the caller;
+ * the first call on a device resolves the array's address and should be made outside stream
+ * capture.  No allocation routine is called. */
+#define KDA_STATIC_SCRATCH_BYTES (32 * 1024 * 1024)
+int kda_fwd_static_scratch(const KdaFwdArgs* args, void* stream);
+
 /* Synchronising read of the device status word of a workspace (0 = every bounded
  * wait inside the kernels completed). */
 int kda_fwd_status(const void* workspace, void* stream, int32_t* status_out);

@@ -149,6 +149,11 @@ int do_k2(const KdaFwdArgs* a, bool state_only, int zero_u, cudaStream_t st) {
 
 }  // namespace
 
+namespace kda {
+// lets the other translation units of the library report through kda_last_error()
+void set_last_error(const char* msg) { snprintf(g_err, sizeof(g_err), "%s", msg); }
+}  // namespace kda
+
 extern "C" {
 
 size_t kda_fwd_workspace_bytes(int32_t B, int32_t T, int32_t H) {
