@@ -78,9 +78,11 @@ typedef struct KdaFwdArgs {
   float scale;
   float lower_bound;
   uint32_t flags;
-  int32_t k2_vsplit;    /* 0 = choose; else CTAs per (batch, head): 2, 4, 8 or 16 (rows of the state) */
-  int32_t k2_ntile;     /* 0 = choose; else 8-row state tiles per warp: 1 or 2;
-                           16 / (k2_vsplit * k2_ntile) warps per CTA must be 1, 2 or 4 */
+  int32_t k2_vsplit;    /* 0 = choose; else CTAs per (batch, head) that share the rows of its state */
+  int32_t k2_variant;   /* 0 = choose; how K2 maps state rows to warps:
+                           1 "n8":  8 rows per warp  (k2_vsplit 4, 8 or 16)
+                           2 "n16": 16 rows per warp (k2_vsplit 2, 4 or 8), rows on the MMA N dimension
+                           3 "m16": 16 rows per warp (k2_vsplit 2, 4 or 8), rows on the MMA M dimension */
   int32_t reserved_;
 } KdaFwdArgs;
 

@@ -30,7 +30,7 @@ class KdaFwdArgs(ctypes.Structure):
         ("q_stride", ctypes.c_int64 * 3), ("k_stride", ctypes.c_int64 * 3), ("v_stride", ctypes.c_int64 * 3),
         ("g_stride", ctypes.c_int64 * 3), ("o_stride", ctypes.c_int64 * 3), ("beta_stride", ctypes.c_int64 * 3),
         ("scale", ctypes.c_float), ("lower_bound", ctypes.c_float), ("flags", ctypes.c_uint32),
-        ("k2_vsplit", ctypes.c_int32), ("k2_ntile", ctypes.c_int32), ("reserved_", ctypes.c_int32),
+        ("k2_vsplit", ctypes.c_int32), ("k2_variant", ctypes.c_int32), ("reserved_", ctypes.c_int32),
     ]
 
 

@@ -154,7 +154,7 @@ def _ptr(x: Optional[torch.Tensor]):
 
 
 def make_args(q, k, v, g, beta, *, scale, lower_bound, A_log, dt_bias, h0, o, ht, workspace,
-              flags, g_out=None, ainv_out=None, k2_vsplit=0, k2_ntile=0) -> KdaFwdArgs:
+              flags, g_out=None, ainv_out=None, k2_vsplit=0, k2_variant=0) -> KdaFwdArgs:
     """Fill the C argument block from (possibly strided) tensors; keeps no references."""
     B, T, H, _ = q.shape
     a = KdaFwdArgs()
@@ -171,7 +171,7 @@ def make_args(q, k, v, g, beta, *, scale, lower_bound, A_log, dt_bias, h0, o, ht
     a.lower_bound = float(lower_bound if lower_bound is not None else -5.0)
     a.flags = int(flags)
     a.k2_vsplit = int(k2_vsplit)
-    a.k2_ntile = int(k2_ntile)
+    a.k2_variant = int(k2_variant)
     return a
 
 
@@ -214,7 +214,7 @@ def _flags(use_gate, use_l2, use_beta_sigmoid) -> int:
 
 def _forward(q, k, v, g, beta, scale, initial_state, output_final_state, use_qk_l2norm_in_kernel,
              use_gate_in_kernel, use_beta_sigmoid_in_kernel, lower_bound, A_log, dt_bias, state_v_first,
-             return_intermediates=False, reuse_workspace=False, k2_vsplit=0, k2_ntile=0, workspace=None):
+             return_intermediates=False, reuse_workspace=False, k2_vsplit=0, k2_variant=0, workspace=None):
     """Allocate, launch K1 + K2 on the current stream, return (o, ht[, intermediates])."""
     lib = _lib.load()
     B, T, H, K = q.shape
@@ -231,7 +231,7 @@ def _forward(q, k, v, g, beta, scale, initial_state, output_final_state, use_qk_
         ainv = torch.empty((B, T, H, BT), dtype=torch.float32, device=dev)
     args = make_args(q, k, v, g, beta, scale=scale, lower_bound=lower_bound, A_log=A_log, dt_bias=dt_bias,
                      h0=h0, o=o, ht=ht, workspace=ws, g_out=g_out, ainv_out=ainv, k2_vsplit=k2_vsplit,
-                     k2_ntile=k2_ntile,
+                     k2_variant=k2_variant,
                      flags=_flags(use_gate_in_kernel, use_qk_l2norm_in_kernel, use_beta_sigmoid_in_kernel))
     stream = _stream_handle()
     profile = os.environ.get("KDA_PROFILE", "0") == "1"

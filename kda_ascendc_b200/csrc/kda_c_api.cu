@@ -53,41 +53,41 @@ int check_k1(const KdaFwdArgs* a) {
 int check_k2(const KdaFwdArgs* a, bool state_only) {
   if (int rc = check_common(a)) return rc;
   if (!state_only && a->o == nullptr) return fail(KDA_ERR_INVALID_ARG, "kda: o is NULL%s", "");
-  const int vs = a->k2_vsplit, nt = a->k2_ntile;
+  const int vs = a->k2_vsplit, var = a->k2_variant;
+  if (var < 0 || var > 3) return fail(KDA_ERR_INVALID_ARG, "kda: k2_variant must be 0..3%s (got %lld)", "", var);
   if (vs != 0 && vs != 2 && vs != 4 && vs != 8 && vs != 16)
     return fail(KDA_ERR_INVALID_ARG, "kda: k2_vsplit must be 0, 2, 4, 8 or 16%s (got %lld)", "", vs);
-  if (nt != 0 && nt != 1 && nt != 2)
-    return fail(KDA_ERR_INVALID_ARG, "kda: k2_ntile must be 0, 1 or 2%s (got %lld)", "", nt);
-  if (vs != 0 && nt != 0 && (vs * nt > 16 || vs * nt < 4))
-    return fail(KDA_ERR_INVALID_ARG, "kda: 16 / (k2_vsplit * k2_ntile) must be 1, 2 or 4%s (vsplit %lld, ntile %lld)", "",
-                vs, nt);
+  if (vs != 0 && var != 0 && ((var == 1) ? (vs < 4) : (vs > 8)))
+    return fail(KDA_ERR_INVALID_ARG, "kda: k2_vsplit %lld%s does not go with k2_variant %lld", "", vs, var);
   return KDA_OK;
 }
 
-// How one head's 128x128 state is spread over warps.  The recurrence is a serial chain per
-// head whose step time is set by the tensor-pipe issue rate of one SM sub-partition, so the
-// aim is one consumer warp per sub-partition for as long as the heads leave room: a warp
-// owns ntile 8-row tiles of the state, vsplit CTAs share a head.
-void pick_split(const KdaFwdArgs* a, int* vsplit, int* ntile) {
+// How one head's 128x128 state is spread over warps.  The recurrence is a serial chain per head;
+// a warp alone on an SM sub-partition cannot overlap its own MMA issue with its other
+// instructions, so a step costs about 8 cycles per MMA plus its non-MMA instructions, and every
+// warp re-reads the shared operand tiles from shared memory.  Measured on B200 (T = 8192):
+// up to ~37 (batch x head) chains the 8-rows-per-warp "n8" form wins (two warps per SM while
+// chains x 8 CTAs fit the SMs, else four); beyond that the 16-rows-per-warp "m16" form with four
+// warps per CTA, which reads half the shared-memory bytes per MMA.
+void pick_split(const KdaFwdArgs* a, int* vsplit, int* variant) {
   int dev = 0, sms = 148;
   if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   const long long bh = static_cast<long long>(a->B) * a->H;
-  int nt = a->k2_ntile;
-  if (nt == 0) {
-    nt = (bh * 16 <= 8LL * sms) ? 1 : 2;      // up to two narrow warps per sub-partition, else wide warps
-    if (a->k2_vsplit == 16) nt = 1;
-    if (a->k2_vsplit == 2) nt = 2;
-  }
+  int var = a->k2_variant;
   int vs = a->k2_vsplit;
-  if (vs == 0) {
-    const int vs_max = 16 / nt, vs_min = 4 / nt;   // 1 .. 4 consumer warps per CTA
-    vs = vs_min;
-    for (int cand = vs_max; cand >= vs_min; cand /= 2)   // most CTAs that still get an SM each
-      if (bh * cand <= sms) { vs = cand; break; }
-    if (vs * nt == 16 && bh * vs * 2 > sms) vs /= 2;    // prefer >= 2 warps per CTA unless SMs are plentiful
+  if (var == 0) {
+    if (vs == 16) var = 1;
+    else if (vs == 2) var = 3;
+    else var = (bh * 4 <= sms) ? 1 : 3;
   }
+  if (vs == 0) {
+    if (var == 1) vs = (bh * 8 <= sms) ? 8 : 4;
+    else vs = (bh * 4 <= sms) ? 4 : 2;
+  }
+  if (var == 1 && vs < 4) vs = 4;
+  if (var != 1 && vs > 8) vs = 8;
   *vsplit = vs;
-  *ntile = nt;
+  *variant = var;
 }
 
 int* status_ptr(const KdaFwdArgs* a) { return static_cast<int*>(a->workspace); }
@@ -139,9 +139,10 @@ int do_k2(const KdaFwdArgs* a, bool state_only, int zero_u, cudaStream_t st) {
   for (int i = 0; i < 3; ++i) p.o_s[i] = a->o_stride[i];
   p.scale = a->scale;
   p.zero_u = zero_u;
-  int vsplit = 4, ntile = 1;
-  pick_split(a, &vsplit, &ntile);
-  cudaError_t e = kda::launch_k2(p, vsplit, ntile, state_only, st);
+  int vsplit = 4, variant = 3;
+  pick_split(a, &vsplit, &variant);
+  cudaError_t e = (variant == 3) ? kda::launch_k2m(p, vsplit, state_only, st)
+                                 : kda::launch_k2n(p, vsplit, variant, state_only, st);
   if (e != cudaSuccess) return fail(KDA_ERR_CUDA, "kda: K2 launch failed: %s", cudaGetErrorString(e));
   ++g_launches;
   return KDA_OK;

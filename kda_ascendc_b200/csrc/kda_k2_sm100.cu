@@ -234,8 +234,15 @@ __global__ void __launch_bounds__((CW + 1) * 32, 1) kda_k2_kernel(const K2Params
         bvl[nv][0] = movmatrix_t(l01); bvl[nv][1] = movmatrix_t(l23);
       }
 
-      // every shared-memory operand of this stage now sits in registers: release the stage and
-      // make sure the next one has landed
+      // release the stage only when every fragment load of it has landed: one register of each
+      // still-unconsumed load is read here, which makes the warp wait for those loads
+      {
+        uint32_t landed = 0;
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks) landed ^= kgh[ks][0] ^ kgl[ks][0];
+        if (!STATE_ONLY) landed ^= ah3[0] ^ al3[0];
+        asm volatile("" ::"r"(landed) : "memory");
+      }
       __syncwarp();
       if (lane == 0) mbar_arrive(empty0 + s * 8);
       const bool more = n + 1 < NT;
@@ -352,7 +359,7 @@ static cudaError_t launch_k2_t(const K2Params& p, cudaStream_t stream) {
   return cudaGetLastError();
 }
 
-cudaError_t launch_k2(const K2Params& p, int vsplit, int ntile, bool state_only, cudaStream_t stream) {
+cudaError_t launch_k2n(const K2Params& p, int vsplit, int ntile, bool state_only, cudaStream_t stream) {
   // vsplit CTAs per head, ntile 8-row tiles per warp  =>  16 / (vsplit * ntile) consumer warps per CTA
   // (at most 4: a fifth warp is the producer, and CTAs of more than 8 warps lose registers per thread)
 #define KDA_K2_CASE(VS, NT_, CW_)                                                                  \

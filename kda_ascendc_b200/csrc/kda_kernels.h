@@ -43,8 +43,13 @@ struct K2Params {
 cudaError_t launch_k1(const K1Params& p, bool g_bf16, bool fast_exp, cudaStream_t stream);
 // Fills the four tensor maps of p from its pointers, sizes and strides (host, no device work).
 cudaError_t k1_encode_tensor_maps(K1Params& p, bool g_bf16, const char** what);
-// vsplit: CTAs per (batch, head), each owns 128/vsplit rows of the state; ntile in {1,2}:
-// 8-row state tiles per warp.  16 / (vsplit * ntile) consumer warps per CTA must be 1, 2, 4 or 8.
-cudaError_t launch_k2(const K2Params& p, int vsplit, int ntile, bool state_only, cudaStream_t stream);
+// Two organisations of K2 (same arithmetic, bit-identical results within one organisation):
+//   "n8"/"n16": state rows on the MMA N dimension, ntile (1 or 2) 8-row tiles per warp,
+//               16 / (vsplit * ntile) in {1, 2, 4} consumer warps per CTA      (kda_k2_sm100.cu)
+//   "m16":      state rows on the MMA M dimension, 16 rows per warp,
+//               8 / vsplit in {1, 2, 4} consumer warps per CTA                 (kda_k2m_sm100.cu)
+// vsplit = CTAs per (batch, head).
+cudaError_t launch_k2n(const K2Params& p, int vsplit, int ntile, bool state_only, cudaStream_t stream);
+cudaError_t launch_k2m(const K2Params& p, int vsplit, bool state_only, cudaStream_t stream);
 
 }  // namespace kda

@@ -158,21 +158,30 @@ def test_segment_chaining_matches_one_pass(cuda_device):
 
 
 def test_all_state_slicings_agree(cuda_device):
-    """How a head's state rows are spread over warps and CTAs must not change a single bit."""
+    """Within one organisation of K2, how a head's state rows are spread over warps and CTAs must
+    not change a single bit; between the organisations only fp32 summation order differs."""
     from kda_ascendc_b200 import api
     inp = O.make_inputs(1, 128, 3, seed0=6, h0_std=0.5)
     d = to_device(inp, cuda_device)
 
-    def run(vs, nt):
+    def run(vs, var):
         return api._forward(d["q"], d["k"], d["v"], d["g"], d["beta"], d["scale"], d["initial_state"], True,
                             True, True, True, d["lower_bound"], d["A_log"], d["dt_bias"], True,
-                            k2_vsplit=vs, k2_ntile=nt)
+                            k2_vsplit=vs, k2_variant=var)
 
-    outs = [run(vs, nt) for vs, nt in ((0, 0), (4, 1), (8, 1), (16, 1), (2, 2), (4, 2), (8, 2))]
-    for o, ht in outs[1:]:
-        assert torch.equal(o, outs[0][0]) and torch.equal(ht, outs[0][1])
     o_r, h_r = O.run_chunk_reference(inp)
-    assert (outs[0][1].cpu() - h_r).abs().max().item() <= HT_TOL
+    ref = {}
+    for var, vss in ((1, (4, 8, 16)), (2, (2, 4, 8)), (3, (2, 4, 8))):
+        outs = [run(vs, var) for vs in vss]
+        for o, ht in outs[1:]:
+            assert torch.equal(o, outs[0][0]) and torch.equal(ht, outs[0][1]), (var, vss)
+        ref[var] = outs[0]
+        assert (outs[0][1].cpu() - h_r).abs().max().item() <= HT_TOL
+    assert torch.equal(ref[1][0], ref[2][0]) and torch.equal(ref[1][1], ref[2][1])      # n8 == n16
+    assert (ref[3][0].float() - ref[1][0].float()).abs().max().item() <= 5e-3 * o_r.float().abs().max().item()
+    assert (ref[3][1] - ref[1][1]).abs().max().item() <= 1e-4
+    auto = run(0, 0)
+    assert any(torch.equal(auto[0], ref[v][0]) for v in ref)
 
 
 def test_flag_variants(cuda_device):
