@@ -108,6 +108,8 @@ int do_k1(const KdaFwdArgs* a, cudaStream_t st) {
   p.g_out = a->g_out;
   p.ainv_out = a->ainv_out;
   p.B = a->B; p.T = a->T; p.H = a->H; p.NT = (a->T + kda::BT - 1) / kda::BT;
+  p.div_h.set(static_cast<uint32_t>(p.H));
+  p.div_nt.set(static_cast<uint32_t>(p.NT));
   for (int i = 0; i < 3; ++i) {
     p.q_s[i] = a->q_stride[i]; p.k_s[i] = a->k_stride[i]; p.v_s[i] = a->v_stride[i];
     p.g_s[i] = a->g_stride[i]; p.beta_s[i] = a->beta_stride[i];

@@ -71,10 +71,10 @@ struct K1Item {   // one (batch, head, chunk) work item
 __device__ __forceinline__ K1Item k1_item(const K1Params& p, int id) {
   // id -> (b, n, h) with h fastest: CTAs that run together read one contiguous span of tokens
   K1Item w;
-  w.h = id % p.H;
-  const int bn = id / p.H;
-  const int n = bn % p.NT;
-  w.b = bn / p.NT;
+  const int bn = static_cast<int>(p.div_h.div(id));
+  w.h = id - bn * p.H;
+  w.b = static_cast<int>(p.div_nt.div(bn));
+  const int n = bn - w.b * p.NT;
   w.t0 = n * BT;
   w.nvalid = min(BT, p.T - w.t0);
   w.rec_idx = (static_cast<size_t>(w.b) * p.H + w.h) * p.NT + n;
@@ -161,19 +161,28 @@ __global__ void __launch_bounds__(128, 4) kda_k1_kernel(const __grid_constant__ 
       nxt = k1_item(p, id + gridDim.x);
       par_next = load_params(nxt);
     }
+    // the item after next: pull its input boxes into L2 now, a whole iteration before the shared-
+    // memory copies are issued, so that those copies find their data on chip
+    if (tid == 0 && id + 2 * static_cast<int>(gridDim.x) < n_items) {
+      const K1Item w2 = k1_item(p, id + 2 * gridDim.x);
+      tma_prefetch_l2_4d(&p.tm_q, 0, w2.h, w2.t0, w2.b);
+      tma_prefetch_l2_4d(&p.tm_k, 0, w2.h, w2.t0, w2.b);
+      tma_prefetch_l2_4d(&p.tm_v, 0, w2.h, w2.t0, w2.b);
+      tma_prefetch_l2_4d(&p.tm_g, 0, w2.h, w2.t0, w2.b);
+    }
     const float expA = use_gate ? expf(par.a_log) : 1.f;
     const float bias0 = par.bias0, bias1 = par.bias1;
 
-    // the previous item's bulk stores must have read their tiles before those are rewritten
-    if (tid == 0) bulk_wait_read_all();
     if (tid < 16) {
       float bv = par.beta;
       if (tid < nvalid) { if (p.flags & 4u) bv = 1.0f / (1.0f + __expf(-bv)); } else bv = 0.f;
       sBeta[tid] = bv;
     }
 
+    K1_STAMP(8)
     bool ok = true;
     if (lane == 0) ok = mbar_wait_bounded(mbar, it & 1, sFlag);
+    K1_STAMP(9)
     if (!ok) *sFlag = 1;
     __syncthreads();
     if (*sFlag != 0) {
@@ -211,7 +220,7 @@ __global__ void __launch_bounds__(128, 4) kda_k1_kernel(const __grid_constant__ 
         sq += __shfl_xor_sync(0xffffffffu, sq, m);
         sk += __shfl_xor_sync(0xffffffffu, sk, m);
       }
-      const float rq = 1.0f / sqrtf(sq + L2NORM_EPS), rk = 1.0f / sqrtf(sk + L2NORM_EPS);
+      const float rq = rsqrtf(sq + L2NORM_EPS), rk = rsqrtf(sk + L2NORM_EPS);
       auto scale4 = [](uint4 v, float f) {
         uint32_t w[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
@@ -269,6 +278,9 @@ __global__ void __launch_bounds__(128, 4) kda_k1_kernel(const __grid_constant__ 
         }
         // rows 8..15 need the sum over rows 0..7, all rows need g[centre]
         if (rh == 0) *reinterpret_cast<float2*>(sTot + c0) = run;
+        // the previous item's bulk stores must have read the qg / kg / Aqk / dec tiles before the
+        // operand loop below rewrites them; by now they have had two phases to do so
+        if (tid == 0) bulk_wait_read_all();
         __syncthreads();
         if (rh == 1) {
           const float2 t = *reinterpret_cast<const float2*>(sTot + c0);
@@ -287,6 +299,8 @@ __global__ void __launch_bounds__(128, 4) kda_k1_kernel(const __grid_constant__ 
         for (int i = 0; i < 8; ++i) gv[i] = ld_g(min(r0 + i, nvalid - 1));
         gmid = ld_g(min(BT / 2, nvalid - 1));
         glast = ld_g(nvalid - 1);
+        if (tid == 0) bulk_wait_read_all();   // as above
+        __syncthreads();
       }
       dec2 = make_float2(ex2f(glast.x), ex2f(glast.y));
       if (rh == 1) *reinterpret_cast<float2*>(smem + S_DEC + c0 * 4) = dec2;
@@ -350,6 +364,7 @@ __global__ void __launch_bounds__(128, 4) kda_k1_kernel(const __grid_constant__ 
       if (tid == 0) fence_proxy_async();   // order the earlier generic accesses (made visible by the barrier) before the async writes
       issue_loads(nxt);
     }
+    K1_STAMP(10)
 
     // ---- phase C: Grams on the tensor cores (one 16x8 output tile per warp) ----
     {

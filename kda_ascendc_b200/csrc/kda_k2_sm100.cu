@@ -210,8 +210,9 @@ __global__ void __launch_bounds__((CW + 1) * 32, 1) kda_k2_kernel(const K2Params
         ldsm_x4_t(sp + REC_KGL + swz_off(a2_row, ks * 16 + a2_col), kgl[ks][0], kgl[ks][1], kgl[ks][2], kgl[ks][3]);
 #pragma unroll
         for (int nv = 0; nv < NVT; ++nv) {
-          hT[ks][nv][0] *= dk[ks][0]; hT[ks][nv][1] *= dk[ks][0];
-          hT[ks][nv][2] *= dk[ks][1]; hT[ks][nv][3] *= dk[ks][1];
+          const float2 lo = __fmul2_rn(make_float2(hT[ks][nv][0], hT[ks][nv][1]), make_float2(dk[ks][0], dk[ks][0]));
+          const float2 hi = __fmul2_rn(make_float2(hT[ks][nv][2], hT[ks][nv][3]), make_float2(dk[ks][1], dk[ks][1]));
+          hT[ks][nv][0] = lo.x; hT[ks][nv][1] = lo.y; hT[ks][nv][2] = hi.x; hT[ks][nv][3] = hi.y;
         }
       }
       uint32_t ah3[4], al3[4];
@@ -234,12 +235,11 @@ __global__ void __launch_bounds__((CW + 1) * 32, 1) kda_k2_kernel(const K2Params
         bvl[nv][0] = movmatrix_t(l01); bvl[nv][1] = movmatrix_t(l23);
       }
 
-      // release the stage only when every fragment load of it has landed: one register of each
-      // still-unconsumed load is read here, which makes the warp wait for those loads
+      // release the stage only when its fragment loads have landed: shared-memory loads of a warp
+      // return in issue order, so reading a register of the last-issued ones makes the warp wait
+      // for all of them
       {
-        uint32_t landed = 0;
-#pragma unroll
-        for (int ks = 0; ks < 8; ++ks) landed ^= kgh[ks][0] ^ kgl[ks][0];
+        uint32_t landed = kgh[7][0] ^ kgl[7][0];
         if (!STATE_ONLY) landed ^= ah3[0] ^ al3[0];
         asm volatile("" ::"r"(landed) : "memory");
       }

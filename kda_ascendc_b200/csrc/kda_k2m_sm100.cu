@@ -189,8 +189,13 @@ __global__ void __launch_bounds__((CW + 1) * 32, 1) kda_k2m_kernel(const K2Param
         ldsm_x4_t(sp + REC_KGH + swz_off(b2_row, ks * 16 + b2_col), kgh[ks][0], kgh[ks][1], kgh[ks][2], kgh[ks][3]);
         {
           const float2 d0 = dec[2 * ks], d1 = dec[2 * ks + 1];
-          hs[2 * ks][0] *= d0.x; hs[2 * ks][1] *= d0.y; hs[2 * ks][2] *= d0.x; hs[2 * ks][3] *= d0.y;
-          hs[2 * ks + 1][0] *= d1.x; hs[2 * ks + 1][1] *= d1.y; hs[2 * ks + 1][2] *= d1.x; hs[2 * ks + 1][3] *= d1.y;
+#pragma unroll
+          for (int half = 0; half < 2; ++half) {
+            const float2 dd = half ? d1 : d0;
+            float* t = hs[2 * ks + half];
+            const float2 lo = __fmul2_rn(make_float2(t[0], t[1]), dd), hi = __fmul2_rn(make_float2(t[2], t[3]), dd);
+            t[0] = lo.x; t[1] = lo.y; t[2] = hi.x; t[3] = hi.y;
+          }
         }
       }
 
@@ -245,9 +250,10 @@ __global__ void __launch_bounds__((CW + 1) * 32, 1) kda_k2m_kernel(const K2Param
           if (np == 4) { mma_bf16_v(oa[0], avh, bl[0], bl[1]); mma_bf16_v(oa[1], avh, bl[2], bl[3]); }
         }
         if (np == 3) {
-          // release the stage only when every fragment load of it has landed: one register of each
-          // still-unconsumed load is read here, which makes the warp wait for those loads
-          uint32_t landed = kgl[4][0] ^ kgl[5][0] ^ kgl[6][0] ^ kgl[7][0];
+          // release the stage only when its fragment loads have landed: shared-memory loads of a
+          // warp return in issue order, so reading a register of the last-issued ones makes the
+          // warp wait for all of them
+          uint32_t landed = kgl[7][0];
           if (!STATE_ONLY) landed ^= ba[0] ^ bl[0];
           asm volatile("" ::"r"(landed) : "memory");
           __syncwarp();

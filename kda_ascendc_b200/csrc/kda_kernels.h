@@ -7,6 +7,21 @@
 
 namespace kda {
 
+// division by a runtime constant as multiply-high + shift (n < 2^31): q = n / d
+struct FastDiv {
+  uint32_t mul, shr, d;
+  __host__ void set(uint32_t div) {
+    d = div;
+    if (div <= 1) { mul = 0; shr = 0; return; }
+    uint32_t lg = 0;
+    while ((1u << lg) < div) ++lg;                       // ceil(log2(d))
+    const unsigned p = 31 + lg;
+    mul = static_cast<uint32_t>(((1ull << p) + div - 1) / div);
+    shr = p - 32;
+  }
+  __device__ __forceinline__ uint32_t div(uint32_t n) const { return d <= 1 ? n : (__umulhi(n, mul) >> shr); }
+};
+
 struct K1Params {
   // tiled TMA descriptors of q, k, v, g viewed as 4-D tensors (d, head, token, batch) with the
   // caller's strides; one 16-token x 128 box per (tensor, chunk).  Rows past T read as zero.
@@ -23,6 +38,7 @@ struct K1Params {
   float* g_out;      // optional
   float* ainv_out;   // optional
   int B, T, H, NT;
+  FastDiv div_h, div_nt;   // item index -> (batch, chunk, head) without integer division
   int64_t q_s[3], k_s[3], v_s[3], g_s[3], beta_s[3];  // element strides (batch, token, head)
   float scale, lower_bound;
   uint32_t flags;
