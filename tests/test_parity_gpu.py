@@ -49,6 +49,7 @@ def test_matches_reference_golden(cuda_device, name):
 
 SHAPES = [
     # B, T, H, h0_std, g dtype        (benchmark distribution: h0 absent, zero or N(0, 0.02))
+    (1, 5, 1, None, torch.bfloat16),       # shorter than one chunk
     (1, 16, 1, None, torch.bfloat16),
     (1, 17, 1, 0.02, torch.float32),
     (1, 33, 2, 0.02, torch.bfloat16),
