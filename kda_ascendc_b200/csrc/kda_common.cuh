@@ -203,6 +203,19 @@ __device__ __forceinline__ void mma_bf16_v(float (&d)[4], const uint32_t (&a)[4]
       : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 
+// Read-only global loads pinned where they are written: used to fetch per-item parameters a whole
+// iteration before their use, which the compiler would otherwise sink next to the use.
+__device__ __forceinline__ float ldg_pinned(const float* p) {
+  float v;
+  asm volatile("ld.global.nc.f32 %0, [%1];" : "=f"(v) : "l"(p));
+  return v;
+}
+__device__ __forceinline__ float2 ldg_pinned2(const float* p) {
+  float2 v;
+  asm volatile("ld.global.nc.v2.f32 {%0, %1}, [%2];" : "=f"(v.x), "=f"(v.y) : "l"(p));
+  return v;
+}
+
 // ---- bf16 helpers -----------------------------------------------------------
 // pack two floats (round to nearest even) into one register: lo -> bits 0..15
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {

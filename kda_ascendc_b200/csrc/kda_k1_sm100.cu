@@ -22,8 +22,8 @@
 // need no copy; rows past T are zero-filled by the copy) that complete on one mbarrier; as soon as
 // a chunk's inputs have been consumed the copies of the CTA's next chunk are issued into the
 // same tiles, so the ~2.5 us load latency hides behind the rest of the chunk.  Of the
-// 26,112-byte chunk record (kda_common.cuh) the qg / kg / Aqk / dec part leaves by two bulk
-// stores; w and u are stored straight from the accumulator fragments.
+// 26,112-byte chunk record (kda_common.cuh) the qg / kg / Aqk / dec part and w leave by three
+// bulk stores; u is stored straight from the accumulator fragments (512 contiguous bytes per warp).
 #include "kda_common.cuh"
 #include "kda_kernels.h"
 
@@ -39,6 +39,7 @@ constexpr int S_QGH = S_GRAM, S_QGL = S_GRAM + 4096, S_KQH = S_GRAM + 8192, S_KQ
               S_KNH = S_GRAM + 16384, S_KNL = S_GRAM + 20480;   // KN tiles only without FAST_EXP
 // once the Grams are done their A tiles hold the B operands of w and u
 constexpr int S_KBH = S_GRAM, S_VBH = S_GRAM + 4096, S_VBL = S_GRAM + 8192;
+constexpr int S_WST = S_GRAM + 12288;   // staging tile of w (the fourth Gram tile slot), -> record[0, 4096)
 
 template <bool G_BF16, bool FAST_EXP>
 struct K1Smem {
@@ -131,15 +132,15 @@ __global__ void __launch_bounds__(128, 4) kda_k1_kernel(const __grid_constant__ 
   struct Par { float a_log, bias0, bias1, beta; };
   auto load_params = [&](const K1Item& w) {
     Par q;
-    q.a_log = use_gate ? p.A_log[w.h] : 0.f;
+    q.a_log = use_gate ? ldg_pinned(p.A_log + w.h) : 0.f;
     q.bias0 = q.bias1 = 0.f;
     if (use_gate && p.dt_bias != nullptr) {
-      const float2 bb = *reinterpret_cast<const float2*>(p.dt_bias + w.h * D + c0);
+      const float2 bb = ldg_pinned2(p.dt_bias + w.h * D + c0);
       q.bias0 = bb.x; q.bias1 = bb.y;
     }
     q.beta = 0.f;
     if (tid < 16 && tid < w.nvalid)
-      q.beta = p.beta[w.b * p.beta_s[0] + static_cast<int64_t>(w.t0 + tid) * p.beta_s[1] + w.h * p.beta_s[2]];
+      q.beta = ldg_pinned(p.beta + w.b * p.beta_s[0] + static_cast<int64_t>(w.t0 + tid) * p.beta_s[1] + w.h * p.beta_s[2]);
     return q;
   };
 
@@ -467,7 +468,7 @@ __global__ void __launch_bounds__(128, 4) kda_k1_kernel(const __grid_constant__ 
     }
 
     // ---- phase E: u = X (v beta) (fp32-like, three split MMAs), w = X (khat beta 2^g) (bf16),
-    //      both stored to the record straight from the accumulator fragments ----
+    //      u stored to the record straight from the accumulator fragments, w staged for a bulk store ----
     {
       // X as A operand (row-major [M=i][K=m]), hi and lo parts
       uint32_t xah[4], xal[4];
@@ -501,15 +502,22 @@ __global__ void __launch_bounds__(128, 4) kda_k1_kernel(const __grid_constant__ 
           mma_bf16(accw, xah, bk[2 * j], bk[2 * j + 1]);
           mma_bf16(accw, xal, bk[2 * j], bk[2 * j + 1]);
           const int kc = n0 + j * 8 + tq * 2;
-          *reinterpret_cast<uint32_t*>(rec + REC_W + swz_off(gq, kc)) = pack_bf16(accw[0], accw[1]);
-          *reinterpret_cast<uint32_t*>(rec + REC_W + swz_off(gq + 8, kc)) = pack_bf16(accw[2], accw[3]);
+          *reinterpret_cast<uint32_t*>(smem + S_WST + swz_off(gq, kc)) = pack_bf16(accw[0], accw[1]);
+          *reinterpret_cast<uint32_t*>(smem + S_WST + swz_off(gq + 8, kc)) = pack_bf16(accw[2], accw[3]);
         }
       }
+    }
+    // w leaves as one more bulk store (4-byte stores of a swizzled tile straight to global memory
+    // would cost eight sectors per instruction)
+    fence_proxy_async();
+    __syncthreads();   // also orders phase E's reads of X / KB / VB before the next item rewrites them
+    if (tid == 0) {
+      bulk_s2g(rec + REC_W, sbase + S_WST, TILE_BYTES);
+      bulk_commit();
     }
     K1_STAMP(7)
     cur = nxt;
     par = par_next;
-    // the next iteration's first barrier orders phase E's reads of X / KB / VB before their rewrite
   }
   if (tid == 0) bulk_wait_read_all();
 }
