@@ -47,8 +47,8 @@ struct K1Smem {
   static constexpr int Q = IN, K = IN + 4096, V = IN + 8192, G = IN + 12288;
   static constexpr int G_BYTES = G_BF16 ? 4096 : 8192;
   static constexpr int SMALL = G + G_BYTES;
-  static constexpr int BETA = SMALL;          // fp32 [16]
-  static constexpr int TOT = BETA + 64;       // fp32 [128]: column sums of rows 0..7, then g[last]
+  static constexpr int BETA = SMALL;          // fp32 [2][16] activated beta + [2] exp(A_log): this item / next item
+  static constexpr int TOT = BETA + 144;      // fp32 [128]: column sums of rows 0..7, then g[last]
   static constexpr int GMID = TOT + 512;      // fp32 [128] g[mid] (not needed with FAST_EXP)
   static constexpr int MBAR = GMID + (FAST_EXP ? 0 : 512);
   static constexpr int FLAG = MBAR + 8;
@@ -98,7 +98,7 @@ __global__ void __launch_bounds__(128, 4) kda_k1_kernel(const __grid_constant__ 
   const uint32_t sbase = smem_u32(smem);
   const uint32_t mbar = sbase + SM::MBAR;
   float* sL = reinterpret_cast<float*>(smem + S_L);
-  float* sBeta = reinterpret_cast<float*>(smem + SM::BETA);
+  float* sBetaAll = reinterpret_cast<float*>(smem + SM::BETA);   // [2][16], then expA[2] at +32
   float* sTot = reinterpret_cast<float*>(smem + SM::TOT);
   float* sGmid = reinterpret_cast<float*>(smem + SM::GMID);
   float* sGlast = sTot;   // the thread that reads sTot[c] is the one that then writes g[last] there
@@ -138,10 +138,21 @@ __global__ void __launch_bounds__(128, 4) kda_k1_kernel(const __grid_constant__ 
       const float2 bb = ldg_pinned2(p.dt_bias + w.h * D + c0);
       q.bias0 = bb.x; q.bias1 = bb.y;
     }
-    q.beta = 0.f;
-    if (tid < 16 && tid < w.nvalid)
-      q.beta = ldg_pinned(p.beta + w.b * p.beta_s[0] + static_cast<int64_t>(w.t0 + tid) * p.beta_s[1] + w.h * p.beta_s[2]);
+    q.beta = 0.f;   // held by threads 32..47 (warp 1), one token each
+    if (tid >= 32 && tid < 48 && tid - 32 < w.nvalid)
+      q.beta = ldg_pinned(p.beta + w.b * p.beta_s[0] + static_cast<int64_t>(w.t0 + tid - 32) * p.beta_s[1] + w.h * p.beta_s[2]);
     return q;
+  };
+
+  // Scalar per-item work -- exp(A_log) and the beta activation -- is done by warp 1 while warp 0
+  // runs the triangular solve of the previous item, and handed over through shared memory.
+  auto publish_params = [&](const Par& q, int nvalid_, int slot) {
+    if (tid >= 32 && tid < 48) {
+      float bv = q.beta;
+      if (tid - 32 < nvalid_) { if (p.flags & 4u) bv = 1.0f / (1.0f + __expf(-bv)); } else bv = 0.f;
+      sBetaAll[slot * 16 + tid - 32] = bv;
+    }
+    if (tid == 48) sBetaAll[32 + slot] = use_gate ? expf(q.a_log) : 1.f;
   };
 
   int id = blockIdx.x;
@@ -151,6 +162,7 @@ __global__ void __launch_bounds__(128, 4) kda_k1_kernel(const __grid_constant__ 
     cur = k1_item(p, id);
     issue_loads(cur);
     par = load_params(cur);
+    publish_params(par, cur.nvalid, 0);
   }
 
   for (int it = 0; id < n_items; ++it, id += gridDim.x) {
@@ -162,23 +174,8 @@ __global__ void __launch_bounds__(128, 4) kda_k1_kernel(const __grid_constant__ 
       nxt = k1_item(p, id + gridDim.x);
       par_next = load_params(nxt);
     }
-    // the item after next: pull its input boxes into L2 now, a whole iteration before the shared-
-    // memory copies are issued, so that those copies find their data on chip
-    if (tid == 0 && id + 2 * static_cast<int>(gridDim.x) < n_items) {
-      const K1Item w2 = k1_item(p, id + 2 * gridDim.x);
-      tma_prefetch_l2_4d(&p.tm_q, 0, w2.h, w2.t0, w2.b);
-      tma_prefetch_l2_4d(&p.tm_k, 0, w2.h, w2.t0, w2.b);
-      tma_prefetch_l2_4d(&p.tm_v, 0, w2.h, w2.t0, w2.b);
-      tma_prefetch_l2_4d(&p.tm_g, 0, w2.h, w2.t0, w2.b);
-    }
-    const float expA = use_gate ? expf(par.a_log) : 1.f;
     const float bias0 = par.bias0, bias1 = par.bias1;
-
-    if (tid < 16) {
-      float bv = par.beta;
-      if (tid < nvalid) { if (p.flags & 4u) bv = 1.0f / (1.0f + __expf(-bv)); } else bv = 0.f;
-      sBeta[tid] = bv;
-    }
+    const float* sBeta = sBetaAll + (it & 1) * 16;
 
     K1_STAMP(8)
     bool ok = true;
@@ -260,7 +257,7 @@ __global__ void __launch_bounds__(128, 4) kda_k1_kernel(const __grid_constant__ 
       };
       if (use_gate) {
         // exp(-z) = 2^(nA * x + nb) with nA = -exp(A_log) log2(e), nb = nA * bias
-        const float nA = -expA * 1.4426950408889634f;
+        const float nA = -sBetaAll[32 + (it & 1)] * 1.4426950408889634f;
         const float2 nA2 = make_float2(nA, nA), nb2 = make_float2(nA * bias0, nA * bias1);
         const float2 one2 = make_float2(1.f, 1.f);
         const float lbr = p.lower_bound * RCP_LN2;
@@ -423,6 +420,9 @@ __global__ void __launch_bounds__(128, 4) kda_k1_kernel(const __grid_constant__ 
       *reinterpret_cast<uint32_t*>(smem + S_VBH + off) = vbh[i];
       *reinterpret_cast<uint32_t*>(smem + S_VBL + off) = vbl[i];
     }
+
+    // next item's scalar parameters (warp 1, while warp 0 solves)
+    if (has_next) publish_params(par_next, nxt.nvalid, (it + 1) & 1);
 
     // ---- phase D: X = (I + L)^-1, lane j of warp 0 owns column j ---------------
     // Column sweep (right-looking): once x[m] is final, every later row takes its update, so the
