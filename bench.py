@@ -1,6 +1,6 @@
 """Benchmark of the KDA chunked forward (BT=16) -- one JSON line on stdout.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference|reference_gpu]
 
 A step is one whole forward (K1 + K2) over one batch of seeded synthetic inputs of the
 headline workload: B=1, T=8192, H=32, K=V=128, bf16 (q, k, v, g_raw ~ N(0,1) bf16, beta
@@ -21,6 +21,10 @@ taken during the timed region.
 (oracle/kda_oracle.py, looped exactly like the reference) on the host cores, one
 process per core over (head, token-slice) units, and prints the same line with
 "impl": "reference".
+
+`--impl reference_gpu` (an extra, not part of the two-arm contract) times the reference's
+own Triton kernels on this GPU when the reference package has been installed under
+baseline/_ref (git-ignored); without it the line says "unavailable".
 """
 from __future__ import annotations
 
@@ -352,17 +356,58 @@ def run_gpu_arm(steps, warmup, n_gpus, kernels_only=False):
         dist.destroy_process_group()
 
 
+def run_reference_gpu_arm(steps, warmup, n_gpus):
+    """The reference's Triton `kda_bt16_fwd` (unmodified, from baseline/_ref) on cuda:0, same
+    workload and metric; its in-kernel gate wants an fp32 g, so g is converted once, outside
+    the timed region."""
+    if int(os.environ.get("RANK", "0")) != 0:
+        return
+    ref_dir = ROOT / "baseline" / "_ref"
+    try:
+        sys.path.insert(0, str(ref_dir))
+        from kda_bt16 import kda_bt16_fwd as ref_fwd
+    except Exception as e:  # noqa: BLE001
+        print(json.dumps(dict(impl="reference_gpu", unavailable="reference package not importable from baseline/_ref: %r" % (e,))))
+        return
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    d = make_device_inputs(0, dev)
+    gf = d["g"].float()
+
+    def fwd():
+        return ref_fwd(d["q"], d["k"], d["v"], gf, d["beta"], scale=D ** -0.5, initial_state=d["h0"],
+                       output_final_state=True, use_qk_l2norm_in_kernel=True, use_gate_in_kernel=True,
+                       use_beta_sigmoid_in_kernel=True, safe_gate=True, lower_bound=-5.0, A_log=d["A_log"],
+                       dt_bias=d["dt_bias"], state_v_first=True)
+
+    for _ in range(max(warmup, 3)):
+        fwd()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        fwd()
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / steps
+    print(json.dumps(dict(impl="reference_gpu", metric=METRIC, value=B * T / (ms * 1e-3), unit="tokens/s", n_gpus=1,
+                          steps=steps, warmup=max(warmup, 3), ms_per_step=ms, higher_is_better=True, dtype="bf16",
+                          data="synthetic", config=dict(workload=WORKLOAD, kernels="reference Triton K1+K2, g fp32"))))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
-    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference", "reference_gpu"])
     ap.add_argument("--kernels-only", action="store_true",
                     help="skip the e2e and CPU-baseline legs (short run for profiler captures)")
     a = ap.parse_args()
     if a.impl == "reference":
         run_reference_arm(a.steps, a.warmup, a.gpus)
+    elif a.impl == "reference_gpu":
+        run_reference_gpu_arm(a.steps, a.warmup, a.gpus)
     else:
         run_gpu_arm(a.steps, a.warmup, a.gpus, a.kernels_only)
 
