@@ -84,7 +84,7 @@ __device__ __forceinline__ K1Item k1_item(const K1Params& p, int id) {
 
 template <bool G_BF16, bool FAST_EXP>
 __global__ void __launch_bounds__(128, 4) kda_k1_kernel(const __grid_constant__ K1Params p) {
-  extern __shared__ __align__(128) uint8_t smem[];
+  extern __shared__ __align__(1024) uint8_t smem[];
   using SM = K1Smem<G_BF16, FAST_EXP>;
   constexpr int S_Q = SM::Q, S_K = SM::K, S_V = SM::V, S_G = SM::G;
   constexpr uint32_t ROW_BYTES = D * 2;
@@ -368,18 +368,21 @@ __global__ void __launch_bounds__(128, 4) kda_k1_kernel(const __grid_constant__ 
     {
       const int mt = warp >> 1;  // 0: Aqk, 1: Akk
       const int nt = warp & 1;   // column block j in [8nt, 8nt+8)
-      const uint32_t a_hi = sbase + (mt == 0 ? S_QGH : S_KQH);
-      const uint32_t a_lo = sbase + (mt == 0 ? S_QGL : S_KQL);
       const int arow = (lane & 7) + ((lane >> 3) & 1) * 8, acol = (lane >> 4) * 8;
       const int brow = nt * 8 + (lane & 7), bcol = ((lane >> 3) & 1) * 8;
+      // swizzled address of k-step ks = (256-byte aligned tile base + lane part) ^ (ks << 5)
+      const uint32_t a_hi = sbase + (mt == 0 ? S_QGH : S_KQH) + swz_off(arow, acol);
+      const uint32_t b_hi = sbase + (FAST_EXP ? S_KGH : S_KNH) + swz_off(brow, bcol);
+      constexpr uint32_t A_LO = S_QGL - S_QGH, B_LO = FAST_EXP ? S_KGL - S_KGH : S_KNL - S_KNH;
+      static_assert(S_KQL - S_KQH == S_QGL - S_QGH && S_GRAM % 256 == 0, "tile layout");
       float acc0[4] = {0, 0, 0, 0}, acc1[4] = {0, 0, 0, 0}, acc2[4] = {0, 0, 0, 0};
 #pragma unroll
       for (int ks = 0; ks < 8; ++ks) {
         uint32_t ah[4], al[4], bh0, bh1, bl0, bl1;
-        ldsm_x4(a_hi + swz_off(arow, ks * 16 + acol), ah[0], ah[1], ah[2], ah[3]);
-        ldsm_x4(a_lo + swz_off(arow, ks * 16 + acol), al[0], al[1], al[2], al[3]);
-        ldsm_x2(sbase + (FAST_EXP ? S_KGH : S_KNH) + swz_off(brow, ks * 16 + bcol), bh0, bh1);
-        ldsm_x2(sbase + (FAST_EXP ? S_KGL : S_KNL) + swz_off(brow, ks * 16 + bcol), bl0, bl1);
+        ldsm_x4(a_hi ^ (ks << 5), ah[0], ah[1], ah[2], ah[3]);
+        ldsm_x4((a_hi ^ (ks << 5)) + A_LO, al[0], al[1], al[2], al[3]);
+        ldsm_x2(b_hi ^ (ks << 5), bh0, bh1);
+        ldsm_x2((b_hi ^ (ks << 5)) + B_LO, bl0, bl1);
         mma_bf16(acc0, ah, bh0, bh1);
         mma_bf16(acc1, ah, bl0, bl1);
         mma_bf16(acc2, al, bh0, bh1);

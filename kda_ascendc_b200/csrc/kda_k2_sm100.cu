@@ -62,7 +62,7 @@ struct K2Smem {
 
 template <int CW, int NVT, bool STATE_ONLY>
 __global__ void __launch_bounds__((CW + 1) * 32, 1) kda_k2_kernel(const K2Params p) {
-  extern __shared__ __align__(128) uint8_t smem[];
+  extern __shared__ __align__(1024) uint8_t smem[];
   using SM = K2Smem<CW, NVT>;
   constexpr int VCOLS = CW * NVT * 8;   // state rows (v) per CTA
   constexpr int NV = D / VCOLS;         // CTAs per (batch, head)
@@ -140,6 +140,12 @@ __global__ void __launch_bounds__((CW + 1) * 32, 1) kda_k2_kernel(const K2Params
     const int a1_row = (lane & 7) + ((lane >> 3) & 1) * 8, a1_col = (lane >> 4) * 8;   // [w;qg]: rows tok, cols k
     const int a2_row = (lane & 7) + (lane >> 4) * 8, a2_col = ((lane >> 3) & 1) * 8;   // kg^T via .trans
     const uint32_t a3_off = REC_AQK + (a1_row * 16 + a1_col) * 2;                      // Aqk: rows i, cols j
+    // Swizzled tile address of k-step ks = (256-byte aligned tile base + lane part) ^ (ks << 5): the
+    // k-step only moves bits 5..7 of the address, which the tile base leaves clear (stages and tile
+    // offsets are multiples of 256 bytes), so one XOR with an immediate replaces the index arithmetic.
+    static_assert(SM::STAGE % 256 == 0 && REC_W % 256 == 0 && REC_QG % 256 == 0 && REC_KGH % 256 == 0 && REC_KGL % 256 == 0,
+                  "tile bases must keep address bits 5..7 clear");
+    const uint32_t a1_lane = swz_off(a1_row, a1_col), a2_lane = swz_off(a2_row, a2_col);
     const uint32_t u_off = REC_SHARED_BYTES + warp * (NVT * REC_U_TILE_BYTES) + lane * 16;
     __nv_bfloat16* const ob = STATE_ONLY ? nullptr : p.o + b * p.o_s[0] + h * p.o_s[2] + v0 + tq * 2;
     const bool use_u = !(STATE_ONLY && p.zero_u);
@@ -156,9 +162,9 @@ __global__ void __launch_bounds__((CW + 1) * 32, 1) kda_k2_kernel(const K2Params
     } else {
 #pragma unroll
       for (int ks = 0; ks < 8; ++ks) {
-        ldsm_x4(sbase + REC_W + swz_off(a1_row, ks * 16 + a1_col), aw[ks][0], aw[ks][1], aw[ks][2], aw[ks][3]);
+        ldsm_x4(((sbase + a1_lane) ^ (ks << 5)) + REC_W, aw[ks][0], aw[ks][1], aw[ks][2], aw[ks][3]);
         if (!STATE_ONLY)
-          ldsm_x4(sbase + REC_QG + swz_off(a1_row, ks * 16 + a1_col), aq[ks][0], aq[ks][1], aq[ks][2], aq[ks][3]);
+          ldsm_x4(((sbase + a1_lane) ^ (ks << 5)) + REC_QG, aq[ks][0], aq[ks][1], aq[ks][2], aq[ks][3]);
         dk[ks][0] = *reinterpret_cast<const float*>(smem + REC_DEC + (ks * 16 + gq) * 4);
         dk[ks][1] = *reinterpret_cast<const float*>(smem + REC_DEC + (ks * 16 + gq + 8) * 4);
       }
@@ -170,6 +176,7 @@ __global__ void __launch_bounds__((CW + 1) * 32, 1) kda_k2_kernel(const K2Params
     for (int n = 0; n < NT && !failed; ++n) {
       const int s = n % K2_STAGES;
       const uint32_t sp = sbase + s * SM::STAGE;
+      const uint32_t t2 = sp + a2_lane;
       K2_STAMP(0)
 
       // the previous step's output tile (always a full chunk)
@@ -202,12 +209,12 @@ __global__ void __launch_bounds__((CW + 1) * 32, 1) kda_k2_kernel(const K2Params
       for (int ks = 0; ks < 8; ++ks) {
 #pragma unroll
         for (int nv = 0; nv < NVT; ++nv) mma_bf16_v(pw[ks & 1][nv], aw[ks], bh[ks][nv][0], bh[ks][nv][1]);
-        ldsm_x4_t(sp + REC_KGH + swz_off(a2_row, ks * 16 + a2_col), kgh[ks][0], kgh[ks][1], kgh[ks][2], kgh[ks][3]);
+        ldsm_x4_t((t2 ^ (ks << 5)) + REC_KGH, kgh[ks][0], kgh[ks][1], kgh[ks][2], kgh[ks][3]);
         if (!STATE_ONLY) {
 #pragma unroll
           for (int nv = 0; nv < NVT; ++nv) mma_bf16_v(pq[ks & 1][nv], aq[ks], bh[ks][nv][0], bh[ks][nv][1]);
         }
-        ldsm_x4_t(sp + REC_KGL + swz_off(a2_row, ks * 16 + a2_col), kgl[ks][0], kgl[ks][1], kgl[ks][2], kgl[ks][3]);
+        ldsm_x4_t((t2 ^ (ks << 5)) + REC_KGL, kgl[ks][0], kgl[ks][1], kgl[ks][2], kgl[ks][3]);
 #pragma unroll
         for (int nv = 0; nv < NVT; ++nv) {
           const float2 lo = __fmul2_rn(make_float2(hT[ks][nv][0], hT[ks][nv][1]), make_float2(dk[ks][0], dk[ks][0]));
@@ -249,6 +256,7 @@ __global__ void __launch_bounds__((CW + 1) * 32, 1) kda_k2_kernel(const K2Params
       const int s1 = (n + 1) % K2_STAGES;
       const uint32_t sp1 = sbase + s1 * SM::STAGE;
       const uint8_t* spg1 = smem + s1 * SM::STAGE;
+      const uint32_t t1n = sp1 + a1_lane;
       if (more) {
         if (!__all_sync(0xffffffffu, mbar_wait_bounded(full0 + s1 * 8, ((n + 1) / K2_STAGES) & 1, sAbort))) {
           if (*sAbort == 0) { *sAbort = 1; atomicExch(p.status, ST_K2_FULL_TIMEOUT); }
@@ -264,7 +272,7 @@ __global__ void __launch_bounds__((CW + 1) * 32, 1) kda_k2_kernel(const K2Params
       for (int m = 0; m < 8; ++m) {
 #pragma unroll
         for (int nv = 0; nv < NVT; ++nv) mma_bf16_v(hT[m][nv], kgh[m], bvh[nv][0], bvh[nv][1]);
-        if (more) ldsm_x4(sp1 + REC_W + swz_off(a1_row, m * 16 + a1_col), aw[m][0], aw[m][1], aw[m][2], aw[m][3]);
+        if (more) ldsm_x4((t1n ^ (m << 5)) + REC_W, aw[m][0], aw[m][1], aw[m][2], aw[m][3]);
       }
 #pragma unroll
       for (int m = 0; m < 8; ++m) {
@@ -280,7 +288,7 @@ __global__ void __launch_bounds__((CW + 1) * 32, 1) kda_k2_kernel(const K2Params
 #pragma unroll
         for (int nv = 0; nv < NVT; ++nv) mma_bf16_v(hT[m][nv], kgl[m], bvh[nv][0], bvh[nv][1]);
         if (!STATE_ONLY && more)
-          ldsm_x4(sp1 + REC_QG + swz_off(a1_row, m * 16 + a1_col), aq[m][0], aq[m][1], aq[m][2], aq[m][3]);
+          ldsm_x4((t1n ^ (m << 5)) + REC_QG, aq[m][0], aq[m][1], aq[m][2], aq[m][3]);
       }
       K2_STAMP(3)
 

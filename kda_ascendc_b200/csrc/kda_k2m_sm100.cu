@@ -36,7 +36,7 @@ struct K2mSmem {
 
 template <int CW, bool STATE_ONLY>
 __global__ void __launch_bounds__((CW + 1) * 32, 1) kda_k2m_kernel(const K2Params p) {
-  extern __shared__ __align__(128) uint8_t smem[];
+  extern __shared__ __align__(1024) uint8_t smem[];
   using SM = K2mSmem<CW>;
   constexpr int NV = 8 / CW;            // CTAs per (batch, head)
   const int tid = threadIdx.x;
@@ -109,6 +109,8 @@ __global__ void __launch_bounds__((CW + 1) * 32, 1) kda_k2m_kernel(const K2Param
     // per-lane ldmatrix address components (constant across steps)
     const int b1_row = (lane & 7) + (lane >> 4) * 8, b1_col = ((lane >> 3) & 1) * 8;   // w, qg: [N=tok][K=k]
     const int b2_row = (lane & 7) + ((lane >> 3) & 1) * 8, b2_col = (lane >> 4) * 8;   // kg: [K=tok][N=k], .trans
+    // swizzled address of k-step ks = (256-byte aligned tile base + lane part) ^ (ks << 5)
+    const uint32_t b1_lane = swz_off(b1_row, b1_col), b2_lane = swz_off(b2_row, b2_col);
     const uint32_t b3_off = REC_AQK + (((lane & 7) + (lane >> 4) * 8) * 16 + ((lane >> 3) & 1) * 8) * 2;
     // u^T fragment of this warp out of the record's [8-column tile][lane][4] blocks (see kda_common.cuh):
     // element (v = vrow0 + gq + 8a, tok = 2tq + j + 8c)  ->  tile 2*warp + a, lane (2tq+j)*4 + gq/2, slot 2c + gq%2
@@ -137,9 +139,9 @@ __global__ void __launch_bounds__((CW + 1) * 32, 1) kda_k2m_kernel(const K2Param
       for (int nt = nt0; nt < nt1; ++nt) dec[nt] = *reinterpret_cast<const float2*>(spg + REC_DEC + (nt * 8 + tq * 2) * 4);
     };
     auto load_b1 = [&](uint32_t sp, int ks, int slot) {
-      ldsm_x4(sp + REC_W + swz_off(b1_row, ks * 16 + b1_col), bw[slot][0], bw[slot][1], bw[slot][2], bw[slot][3]);
+      ldsm_x4(((sp + b1_lane) ^ (ks << 5)) + REC_W, bw[slot][0], bw[slot][1], bw[slot][2], bw[slot][3]);
       if (!STATE_ONLY)
-        ldsm_x4(sp + REC_QG + swz_off(b1_row, ks * 16 + b1_col), bq[slot][0], bq[slot][1], bq[slot][2], bq[slot][3]);
+        ldsm_x4(((sp + b1_lane) ^ (ks << 5)) + REC_QG, bq[slot][0], bq[slot][1], bq[slot][2], bq[slot][3]);
     };
 
     bool failed = false;
@@ -186,7 +188,7 @@ __global__ void __launch_bounds__((CW + 1) * 32, 1) kda_k2m_kernel(const K2Param
           mma_bf16_v(pq[1], ah, bq[sl][2], bq[sl][3]);
         }
         if (ks + 2 < 8) load_b1(sp, ks + 2, sl);
-        ldsm_x4_t(sp + REC_KGH + swz_off(b2_row, ks * 16 + b2_col), kgh[ks][0], kgh[ks][1], kgh[ks][2], kgh[ks][3]);
+        ldsm_x4_t(((sp + b2_lane) ^ (ks << 5)) + REC_KGH, kgh[ks][0], kgh[ks][1], kgh[ks][2], kgh[ks][3]);
         {
           const float2 d0 = dec[2 * ks], d1 = dec[2 * ks + 1];
 #pragma unroll
@@ -211,7 +213,7 @@ __global__ void __launch_bounds__((CW + 1) * 32, 1) kda_k2m_kernel(const K2Param
       for (int np = 0; np < 8; ++np) {
         mma_bf16_v(hs[2 * np], avh, kgh[np][0], kgh[np][1]);
         mma_bf16_v(hs[2 * np + 1], avh, kgh[np][2], kgh[np][3]);
-        ldsm_x4_t(sp + REC_KGL + swz_off(b2_row, np * 16 + b2_col), kgl[np][0], kgl[np][1], kgl[np][2], kgl[np][3]);
+        ldsm_x4_t(((sp + b2_lane) ^ (np << 5)) + REC_KGL, kgl[np][0], kgl[np][1], kgl[np][2], kgl[np][3]);
       }
       uint32_t ba[4], bl[4];
       if (!STATE_ONLY) {
