@@ -34,8 +34,11 @@ struct K2mSmem {
   static constexpr int TOTAL = FLAG + 16;
 };
 
-template <int CW, bool STATE_ONLY>
-__global__ void __launch_bounds__((CW + 1) * 32, 1) kda_k2m_kernel(const K2Params p) {
+// MINB = CTAs that must fit on one SM.  With 2 (register cap 168) eight consumer warps share an
+// SM; that pays as soon as there are more CTAs than SMs (measured: B1 T8192 H96 765 -> 677 us),
+// while a grid that fits in one wave is faster with the uncapped registers.
+template <int CW, bool STATE_ONLY, int MINB>
+__global__ void __launch_bounds__((CW + 1) * 32, MINB) kda_k2m_kernel(const K2Params p) {
   extern __shared__ __align__(1024) uint8_t smem[];
   using SM = K2mSmem<CW>;
   constexpr int NV = 8 / CW;            // CTAs per (batch, head)
@@ -315,28 +318,47 @@ __global__ void __launch_bounds__((CW + 1) * 32, 1) kda_k2m_kernel(const K2Param
   }
 }
 
-template <int CW, bool STATE_ONLY>
-static cudaError_t launch_k2m_t(const K2Params& p, cudaStream_t stream) {
+template <int CW, bool STATE_ONLY, int MINB>
+static cudaError_t launch_k2m_t(const K2Params& p, int nblocks, cudaStream_t stream) {
   constexpr int smem_bytes = K2mSmem<CW>::TOTAL;
   static bool configured[64] = {};
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev < 64 && !configured[dev]) {
-    cudaError_t e = cudaFuncSetAttribute(kda_k2m_kernel<CW, STATE_ONLY>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    cudaError_t e = cudaFuncSetAttribute(kda_k2m_kernel<CW, STATE_ONLY, MINB>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          smem_bytes);
     if (e != cudaSuccess) return e;
+    if (MINB > 1) {
+      e = cudaFuncSetAttribute(kda_k2m_kernel<CW, STATE_ONLY, MINB>, cudaFuncAttributePreferredSharedMemoryCarveout,
+                               cudaSharedmemCarveoutMaxShared);
+      if (e != cudaSuccess) return e;
+    }
     configured[dev] = true;
   }
-  const int nblocks = p.B * p.H * (8 / CW);
-  kda_k2m_kernel<CW, STATE_ONLY><<<nblocks, (CW + 1) * 32, smem_bytes, stream>>>(p);
+  kda_k2m_kernel<CW, STATE_ONLY, MINB><<<nblocks, (CW + 1) * 32, smem_bytes, stream>>>(p);
   return cudaGetLastError();
+}
+
+template <int CW, bool STATE_ONLY>
+static cudaError_t launch_k2m_c(const K2Params& p, cudaStream_t stream) {
+  static int sms[64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev >= 64) return cudaErrorInvalidDevice;
+  if (sms[dev] == 0) {
+    cudaError_t e = cudaDeviceGetAttribute(&sms[dev], cudaDevAttrMultiProcessorCount, dev);
+    if (e != cudaSuccess) return e;
+  }
+  const int nblocks = p.B * p.H * (8 / CW);
+  if (CW == 4 && nblocks > sms[dev]) return launch_k2m_t<CW, STATE_ONLY, 2>(p, nblocks, stream);
+  return launch_k2m_t<CW, STATE_ONLY, 1>(p, nblocks, stream);
 }
 
 cudaError_t launch_k2m(const K2Params& p, int vsplit, bool state_only, cudaStream_t stream) {
   switch (vsplit) {
-    case 2: return state_only ? launch_k2m_t<4, true>(p, stream) : launch_k2m_t<4, false>(p, stream);
-    case 4: return state_only ? launch_k2m_t<2, true>(p, stream) : launch_k2m_t<2, false>(p, stream);
-    case 8: return state_only ? launch_k2m_t<1, true>(p, stream) : launch_k2m_t<1, false>(p, stream);
+    case 2: return state_only ? launch_k2m_c<4, true>(p, stream) : launch_k2m_c<4, false>(p, stream);
+    case 4: return state_only ? launch_k2m_c<2, true>(p, stream) : launch_k2m_c<2, false>(p, stream);
+    case 8: return state_only ? launch_k2m_c<1, true>(p, stream) : launch_k2m_c<1, false>(p, stream);
     default: return cudaErrorInvalidValue;
   }
 }
