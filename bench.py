@@ -170,6 +170,14 @@ class ClockSampler:
         return dict(sm_mhz=statistics.median(sm), sm_max_mhz=max(mx), reasons=sorted(reasons), samples=len(sm))
 
 
+def _latency_stats(samples_ms):
+    """min / median / p20 / p80 of single-forward latencies (K1 + K2 of one step, synchronised
+    per step), the figures the reference's own benchmarks report."""
+    xs = sorted(samples_ms)
+    pick = lambda f: xs[min(len(xs) - 1, int(f * len(xs)))]
+    return dict(min=xs[0], median=statistics.median(xs), p20=pick(0.2), p80=pick(0.8), samples=len(xs))
+
+
 def make_device_inputs(rank: int, device):
     """Seeded inputs of the workload, generated on the device (per-rank seed)."""
     g = torch.Generator(device=device).manual_seed(42 + 1000 * rank)
@@ -347,7 +355,8 @@ def run_gpu_arm(steps, warmup, n_gpus, kernels_only=False):
                     e2e=dict(value=tokens_per_step * steps / (e2e_ms * 1e-3), unit="tokens/s",
                              h2d_bytes_per_step=h2d, d2h_bytes_per_step=d2h, ms_per_step=e2e_ms / steps,
                              api="kda_ascendc_b200.kda_bt16_fwd", pipelining="2 steps in flight over 3 streams"),
-                    gpu_launches=launches, roofline=roofline, kernels=kern, clocks=clocks)
+                    gpu_launches=launches, roofline=roofline, kernels=kern, clocks=clocks,
+                    latency_ms=_latency_stats([a_ + b_ for a_, b_ in zip(k1_ms, k2_ms)]))
         if world == 1:
             line["cpu_baseline"] = cpu_baseline_sample()
         print(json.dumps(line), flush=True)
