@@ -178,6 +178,42 @@ def _latency_stats(samples_ms):
     return dict(min=xs[0], median=statistics.median(xs), p20=pick(0.2), p80=pick(0.8), samples=len(xs))
 
 
+def decode_leg(device, hbm_gbs):
+    """The token recurrence (decode) on B=64 sequences x 32 heads, one token per call through the C
+    ABI, device-timed; three state sets (268 MB) are rotated so that no call finds its state in L2.
+    An extra figure beside the headline: the step is bound by the 128 KiB of state it moves per head."""
+    import kda_ascendc_b200 as K
+    from kda_ascendc_b200 import _lib, api
+    lib = _lib.load()
+    Bd, Td = 64, 1
+    g = torch.Generator(device=device).manual_seed(7)
+    rn = lambda *s: torch.randn(*s, device=device, generator=g)
+    q, k, v, gr = (rn(Bd, Td, H, D).bfloat16() for _ in range(4))
+    beta = rn(Bd, Td, H)
+    A_log = torch.log(1.0 + 15.0 * torch.rand(H, device=device, generator=g))
+    dtb = torch.rand(H * D, device=device, generator=g) * 0.2 - 0.1
+    states = [rn(Bd, H, D, D) * 0.1 for _ in range(3)]
+    o = torch.empty(Bd, Td, H, D, dtype=torch.bfloat16, device=device)
+    argl = [api.make_args(q, k, v, gr, beta, scale=D ** -0.5, lower_bound=-5.0, A_log=A_log, dt_bias=dtb, h0=s_, o=o,
+                          ht=s_, workspace=None, flags=7) for s_ in states]
+    stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    n = 30
+    for i in range(3):
+        assert lib.kda_recurrent_fwd(ctypes.byref(argl[i % 3]), stream) == 0, _lib.last_error()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(n):
+        assert lib.kda_recurrent_fwd(ctypes.byref(argl[i % 3]), stream) == 0, _lib.last_error()
+    e1.record()
+    torch.cuda.synchronize()
+    us = e0.elapsed_time(e1) / n * 1e3
+    nbytes = Bd * H * 2 * D * D * 4 + Bd * Td * H * (4 * D * 2 + 4 + D * 2)
+    gbs = nbytes / (us * 1e-6) / 1e9
+    return dict(workload="token recurrence B=64 T=1 H=32 (decode step, in-place state)", us_per_step=us,
+                tokens_per_s=Bd * Td / (us * 1e-6), bytes_per_step=nbytes, achieved_GBps=gbs, hbm_frac=gbs / hbm_gbs)
+
+
 def make_device_inputs(rank: int, device):
     """Seeded inputs of the workload, generated on the device (per-rank seed)."""
     g = torch.Generator(device=device).manual_seed(42 + 1000 * rank)
@@ -358,6 +394,7 @@ def run_gpu_arm(steps, warmup, n_gpus, kernels_only=False):
                     gpu_launches=launches, roofline=roofline, kernels=kern, clocks=clocks,
                     latency_ms=_latency_stats([a_ + b_ for a_, b_ in zip(k1_ms, k2_ms)]))
         if world == 1:
+            line["decode"] = decode_leg(dev, hbm_gbs)
             line["cpu_baseline"] = cpu_baseline_sample()
         print(json.dumps(line), flush=True)
     if dist is not None:

@@ -103,6 +103,16 @@ int kda_fwd_k2(const KdaFwdArgs* args, void* stream);
  * feeding h0 = I yields the segment's transition matrix. */
 int kda_fwd_k2_state(const KdaFwdArgs* args, int zero_u, void* stream);
 
+/* Token-by-token recurrence for decode steps and short sequences (T of one to a few dozen
+ * tokens): reads the state from args->h0 (NULL = zeros), applies args->T tokens, writes the
+ * outputs to args->o and the new state to args->ht (may be NULL; may be the same buffer as h0
+ * for an in-place update).  Needs all three KDA_FLAG_* bits; args->workspace is not used.
+ * The reference has no decode kernel (README.md:503-505 lists it as future work); the
+ * arithmetic is the token recurrence its tests take as the gold (fused_recurrent_kda,
+ * tests/test_kda_bt16.py:26-39) with the chunk path's rounding of the normalised q and k, so a
+ * prefill by kda_fwd followed by steps of this function continues the same sequence. */
+int kda_recurrent_fwd(const KdaFwdArgs* args, void* stream);
+
 /* Whole forward with the K1 -> K2 scratch taken from a fixed array inside the library instead
  * of args->workspace (which is ignored).  It has no counterpart in the reference, whose host
  * code always allocates its intermediates itself.  It exists for callers that cannot obtain

@@ -15,7 +15,8 @@ STATIC_SCRATCH_BYTES = 32 * 1024 * 1024   # KDA_STATIC_SCRATCH_BYTES of include/
 FLAG_GATE, FLAG_L2NORM, FLAG_BETA_SIGMOID = 1, 2, 4
 
 EXPORTS = (
-    "kda_fwd_workspace_bytes", "kda_fwd", "kda_fwd_k1", "kda_fwd_k2", "kda_fwd_k2_state", "kda_fwd_static_scratch",
+    "kda_fwd_workspace_bytes", "kda_fwd", "kda_fwd_k1", "kda_fwd_k2", "kda_fwd_k2_state", "kda_recurrent_fwd",
+    "kda_fwd_static_scratch",
     "kda_fwd_status", "kda_last_launch_count", "kda_last_error", "kda_version",
 )
 
@@ -49,7 +50,7 @@ def load() -> ctypes.CDLL:
     lib = ctypes.CDLL(str(LIB_PATH))
     lib.kda_fwd_workspace_bytes.restype = ctypes.c_size_t
     lib.kda_fwd_workspace_bytes.argtypes = [ctypes.c_int32] * 3
-    for name in ("kda_fwd", "kda_fwd_k1", "kda_fwd_k2", "kda_fwd_static_scratch"):
+    for name in ("kda_fwd", "kda_fwd_k1", "kda_fwd_k2", "kda_fwd_static_scratch", "kda_recurrent_fwd"):
         fn = getattr(lib, name)
         fn.restype = ctypes.c_int
         fn.argtypes = [ctypes.POINTER(KdaFwdArgs), ctypes.c_void_p]

@@ -33,7 +33,7 @@ WS_HEADER_BYTES = 256
 
 _WORKSPACE_CACHE: dict[tuple, torch.Tensor] = {}
 _LAST_PROFILE: dict[str, object] = {}
-_LAUNCH_COUNTS = {"kda_k1": 0, "kda_k2": 0}
+_LAUNCH_COUNTS = {"kda_k1": 0, "kda_k2": 0, "kda_recurrent": 0}
 
 
 # ---------------------------------------------------------------------------
@@ -259,6 +259,43 @@ def _forward(q, k, v, g, beta, scale, initial_state, output_final_state, use_qk_
         inter["g"] = g_out
         inter["A_inv"] = ainv
         return o, ht, inter
+    return o, ht
+
+
+def kda_recurrent_fwd(q, k, v, g, beta, scale=None, initial_state=None, output_final_state=True,
+                      lower_bound=-5.0, A_log=None, dt_bias=None, inplace_state=False):
+    """Token-by-token KDA recurrence for decode steps and short sequences.
+
+    Same tensors as :func:`kda_bt16_fwd` with the in-kernel gate, l2-norm and beta sigmoid
+    (``g`` raw, ``beta`` logits, ``A_log`` required), any ``T >= 1`` (meant for one to a few dozen
+    tokens), V-first fp32 state ``[B, H, 128, 128]``.  Returns ``(o, state)``; with
+    ``inplace_state=True`` the new state overwrites ``initial_state`` (which is returned).
+    The reference has no decode function; the arithmetic is the token recurrence its tests use
+    as the gold (``fused_recurrent_kda``, ``tests/test_kda_bt16.py:26-39`` of the reference) with
+    the chunk path's bf16 rounding of the normalised q and k, so that a prefill by
+    :func:`kda_bt16_fwd` followed by steps of this function continues the same sequence.
+    """
+    _validate_kda_inputs(q, k, v, g, beta, initial_state, True, True, lower_bound, A_log, dt_bias, True,
+                         require_contiguous=False)
+    _require_cuda(q)
+    if inplace_state and initial_state is None:
+        raise ValueError("inplace_state=True needs an initial_state to update")
+    if initial_state is not None and not initial_state.is_contiguous():
+        raise ValueError("initial_state must be contiguous")
+    B, T, H, K = q.shape
+    if scale is None:
+        scale = K ** -0.5
+    dev = q.device
+    o = torch.empty((B, T, H, HEAD_DIM), dtype=torch.bfloat16, device=dev)
+    if inplace_state:
+        ht = initial_state
+    else:
+        ht = torch.empty((B, H, HEAD_DIM, HEAD_DIM), dtype=torch.float32, device=dev) if output_final_state else None
+    args = make_args(q, k, v, g, beta, scale=scale, lower_bound=lower_bound, A_log=A_log, dt_bias=dt_bias,
+                     h0=initial_state, o=o, ht=ht, workspace=None, flags=_flags(True, True, True))
+    with torch.cuda.device(dev):
+        _check(_lib.load().kda_recurrent_fwd(ctypes.byref(args), _stream_handle()))
+    _LAUNCH_COUNTS["kda_recurrent"] += 1
     return o, ht
 
 

@@ -198,6 +198,48 @@ int kda_fwd_k2_state(const KdaFwdArgs* a, int zero_u, void* stream) {
   return do_k2(a, true, zero_u, static_cast<cudaStream_t>(stream));
 }
 
+int kda_recurrent_fwd(const KdaFwdArgs* a, void* stream) {
+  g_launches = 0;
+  if (a == nullptr) return fail(KDA_ERR_INVALID_ARG, "kda: args is NULL%s", "");
+  if (a->B <= 0 || a->T <= 0 || a->H <= 0)
+    return fail(KDA_ERR_INVALID_ARG, "kda: B, T, H must be positive%s (T=%lld, H=%lld)", "", a->T, a->H);
+  if (!a->q || !a->k || !a->v || !a->g || !a->beta || !a->o || !a->A_log)
+    return fail(KDA_ERR_INVALID_ARG, "kda: the recurrent step needs q, k, v, g, beta, A_log and o%s", "");
+  const uint32_t all = KDA_FLAG_GATE_IN_KERNEL | KDA_FLAG_QK_L2NORM | KDA_FLAG_BETA_SIGMOID;
+  if ((a->flags & all) != all)
+    return fail(KDA_ERR_INVALID_ARG, "kda: the recurrent step computes gate, l2-norm and beta sigmoid in the kernel%s; set all three flags", "");
+  if (a->g_dtype != KDA_G_FP32 && a->g_dtype != KDA_G_BF16)
+    return fail(KDA_ERR_INVALID_ARG, "kda: g_dtype must be KDA_G_FP32 or KDA_G_BF16%s (got %lld)", "", a->g_dtype);
+  if (!(a->lower_bound > -11.0f && a->lower_bound < 0.0f))
+    return fail(KDA_ERR_INVALID_ARG, "kda: lower_bound must be in (-11, 0)%s", "");
+  if (!row_aligned(a->q, a->q_stride, 2) || !row_aligned(a->k, a->k_stride, 2) || !row_aligned(a->v, a->v_stride, 2) ||
+      !row_aligned(a->g, a->g_stride, a->g_dtype == KDA_G_BF16 ? 2 : 4) || !row_aligned(a->o, a->o_stride, 2))
+    return fail(KDA_ERR_INVALID_ARG, "kda: q/k/v/g/o rows must start on 16-byte boundaries%s", "");
+  for (const void* ptr : {static_cast<const void*>(a->h0), static_cast<const void*>(a->ht), static_cast<const void*>(a->dt_bias)})
+    if (ptr != nullptr && reinterpret_cast<uintptr_t>(ptr) % 16 != 0)
+      return fail(KDA_ERR_INVALID_ARG, "kda: h0, ht and dt_bias must be 16-byte aligned%s", "");
+  kda::RecurrentParams p;
+  memset(&p, 0, sizeof(p));
+  p.q = static_cast<const __nv_bfloat16*>(a->q);
+  p.k = static_cast<const __nv_bfloat16*>(a->k);
+  p.v = static_cast<const __nv_bfloat16*>(a->v);
+  p.g = a->g; p.beta = a->beta; p.A_log = a->A_log; p.dt_bias = a->dt_bias;
+  p.h0 = a->h0; p.ht = a->ht; p.o = static_cast<__nv_bfloat16*>(a->o);
+  p.B = a->B; p.T = a->T; p.H = a->H;
+  for (int i = 0; i < 3; ++i) {
+    p.q_s[i] = a->q_stride[i]; p.k_s[i] = a->k_stride[i]; p.v_s[i] = a->v_stride[i];
+    p.g_s[i] = a->g_stride[i]; p.beta_s[i] = a->beta_stride[i]; p.o_s[i] = a->o_stride[i];
+  }
+  p.scale = a->scale;
+  p.lower_bound = a->lower_bound;
+  int dev = 0, sms = 148;
+  if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  cudaError_t e = kda::launch_recurrent(p, a->g_dtype == KDA_G_BF16, sms, static_cast<cudaStream_t>(stream));
+  if (e != cudaSuccess) return fail(KDA_ERR_CUDA, "kda: recurrent launch failed: %s", cudaGetErrorString(e));
+  ++g_launches;
+  return KDA_OK;
+}
+
 int kda_fwd_status(const void* workspace, void* stream, int32_t* status_out) {
   if (workspace == nullptr || status_out == nullptr)
     return fail(KDA_ERR_INVALID_ARG, "kda: workspace and status_out are required%s", "");

@@ -68,4 +68,18 @@ cudaError_t k1_encode_tensor_maps(K1Params& p, bool g_bf16, const char** what);
 cudaError_t launch_k2n(const K2Params& p, int vsplit, int ntile, bool state_only, cudaStream_t stream);
 cudaError_t launch_k2m(const K2Params& p, int vsplit, bool state_only, cudaStream_t stream);
 
+// Token recurrence (decode / short sequences): no chunking, no workspace (kda_recurrent_sm100.cu).
+struct RecurrentParams {
+  const __nv_bfloat16 *q, *k, *v;
+  const void* g;            // raw gate, bf16 or fp32
+  const float *beta, *A_log, *dt_bias;   // dt_bias may be null
+  const float* h0;          // [B,H,128,128] or null; may alias ht (each CTA reads its rows before it writes them)
+  float* ht;                // may be null
+  __nv_bfloat16* o;
+  int B, T, H;
+  int64_t q_s[3], k_s[3], v_s[3], g_s[3], beta_s[3], o_s[3];
+  float scale, lower_bound;
+};
+cudaError_t launch_recurrent(const RecurrentParams& p, bool g_bf16, int sms, cudaStream_t stream);
+
 }  // namespace kda

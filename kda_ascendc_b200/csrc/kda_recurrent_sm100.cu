@@ -1,0 +1,130 @@
+// Token-by-token KDA recurrence for decode and short sequences.  sm_100a.
+//
+// The reference has no decode kernel (its README lists prefill/decode separation as future work,
+// README.md:503-505); the arithmetic is the token recurrence its tests use as the gold
+// (fused_recurrent_kda at tests/test_kda_bt16.py:26-39), with the rounding points of the chunk
+// path (normalised q, k rounded to bf16, everything else fp32), V-first state h[V][K]:
+//   h   <- h * 2^gate[k]                       gate = lower_bound * sigmoid(e^A_log (g + bias)) / ln 2
+//   v'  =  beta * (v - h khat)
+//   h   <- h + v' (x) khat
+//   o   =  scale * h qhat
+// Every state row v is independent, so a warp owns ROWS rows of one (batch, head) state and keeps
+// them in registers over all T tokens: lane l holds columns 4l..4l+3 of each row (one 16-byte
+// load per row), the two dot products per row and token are warp reductions.  The kernel moves
+// 64 KiB of state in and out per (batch, head) and a few hundred bytes per token: HBM bound; the
+// grid is (batch x head) x (128 / rows per CTA) CTAs.
+#include "kda_common.cuh"
+#include "kda_kernels.h"
+
+namespace kda {
+
+namespace {
+constexpr int REC_WARPS = 4;   // warps per CTA
+
+__device__ __forceinline__ float warp_sum(float x) {
+#pragma unroll
+  for (int m = 16; m > 0; m >>= 1) x += __shfl_xor_sync(0xffffffffu, x, m);
+  return x;
+}
+
+template <int ROWS, bool G_BF16>
+__global__ void __launch_bounds__(REC_WARPS * 32) kda_recurrent_kernel(const RecurrentParams p) {
+  constexpr int ROWS_PER_CTA = ROWS * REC_WARPS;
+  constexpr int SLICES = D / ROWS_PER_CTA;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int bh = blockIdx.x / SLICES, slice = blockIdx.x % SLICES;
+  const int b = bh / p.H, h = bh % p.H;
+  const int v0 = slice * ROWS_PER_CTA + warp * ROWS;   // first state row of this warp
+  const int k0 = lane * 4;                             // first state column of this lane
+
+  float4 s[ROWS];
+  if (p.h0 != nullptr) {
+    const float* h0 = p.h0 + (static_cast<size_t>(bh) * D + v0) * D + k0;
+#pragma unroll
+    for (int r = 0; r < ROWS; ++r) s[r] = *reinterpret_cast<const float4*>(h0 + r * D);
+  } else {
+#pragma unroll
+    for (int r = 0; r < ROWS; ++r) s[r] = make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+
+  const float expA = expf(p.A_log[h]);
+  float4 bias = make_float4(0.f, 0.f, 0.f, 0.f);
+  if (p.dt_bias != nullptr) bias = *reinterpret_cast<const float4*>(p.dt_bias + h * D + k0);
+  const float lbr = p.lower_bound * RCP_LN2;
+
+  const __nv_bfloat16* qp = p.q + b * p.q_s[0] + h * p.q_s[2] + k0;
+  const __nv_bfloat16* kp = p.k + b * p.k_s[0] + h * p.k_s[2] + k0;
+  const __nv_bfloat16* vp = p.v + b * p.v_s[0] + h * p.v_s[2] + v0 + (lane % ROWS);
+  const uint8_t* gp = static_cast<const uint8_t*>(p.g) + (b * p.g_s[0] + h * p.g_s[2] + k0) * (G_BF16 ? 2 : 4);
+  const float* bp = p.beta + b * p.beta_s[0] + h * p.beta_s[2];
+  __nv_bfloat16* op = p.o + b * p.o_s[0] + h * p.o_s[2] + v0;
+
+  auto load4 = [](const __nv_bfloat16* src) {
+    const uint2 raw = *reinterpret_cast<const uint2*>(src);
+    return make_float4(bf16_lo_to_f32(raw.x), bf16_hi_to_f32(raw.x), bf16_lo_to_f32(raw.y), bf16_hi_to_f32(raw.y));
+  };
+
+  for (int t = 0; t < p.T; ++t) {
+    const float4 qr = load4(qp + t * p.q_s[1]);
+    const float4 kr = load4(kp + t * p.k_s[1]);
+    float4 gr;
+    if (G_BF16) gr = load4(reinterpret_cast<const __nv_bfloat16*>(gp + t * p.g_s[1] * 2));
+    else gr = *reinterpret_cast<const float4*>(gp + t * p.g_s[1] * 4);
+    const float vmine = __bfloat162float(vp[t * p.v_s[1]]);   // lane l holds v of row l % ROWS
+    float beta = bp[t * p.beta_s[1]];
+    beta = 1.0f / (1.0f + __expf(-beta));
+
+    // l2 normalisation, rounded to bf16 like the chunk path
+    const float rq = rsqrtf(warp_sum(qr.x * qr.x + qr.y * qr.y + qr.z * qr.z + qr.w * qr.w) + L2NORM_EPS);
+    const float rk = rsqrtf(warp_sum(kr.x * kr.x + kr.y * kr.y + kr.z * kr.z + kr.w * kr.w) + L2NORM_EPS);
+    const float4 qn = make_float4(bf16_round(qr.x * rq), bf16_round(qr.y * rq), bf16_round(qr.z * rq), bf16_round(qr.w * rq));
+    const float4 kn = make_float4(bf16_round(kr.x * rk), bf16_round(kr.y * rk), bf16_round(kr.z * rk), bf16_round(kr.w * rk));
+
+    // decay 2^(lb * sigmoid(e^A (g + bias)) / ln 2) of this lane's four columns
+    auto dec1 = [&](float g, float bi) {
+      const float z = expA * (g + bi);
+      return ex2f(lbr / (1.0f + __expf(-z)));
+    };
+    const float4 dc = make_float4(dec1(gr.x, bias.x), dec1(gr.y, bias.y), dec1(gr.z, bias.z), dec1(gr.w, bias.w));
+
+    float oacc = 0.f;   // lane r keeps o of row r
+#pragma unroll
+    for (int r = 0; r < ROWS; ++r) {
+      s[r].x *= dc.x; s[r].y *= dc.y; s[r].z *= dc.z; s[r].w *= dc.w;
+      const float pred = warp_sum(s[r].x * kn.x + s[r].y * kn.y + s[r].z * kn.z + s[r].w * kn.w);
+      const float vr = __shfl_sync(0xffffffffu, vmine, r);
+      const float vn = beta * (vr - pred);
+      s[r].x = fmaf(vn, kn.x, s[r].x); s[r].y = fmaf(vn, kn.y, s[r].y);
+      s[r].z = fmaf(vn, kn.z, s[r].z); s[r].w = fmaf(vn, kn.w, s[r].w);
+      const float od = warp_sum(s[r].x * qn.x + s[r].y * qn.y + s[r].z * qn.z + s[r].w * qn.w);
+      if (lane == r) oacc = od;
+    }
+    if (lane < ROWS) op[t * p.o_s[1] + lane] = __float2bfloat16(p.scale * oacc);
+  }
+
+  if (p.ht != nullptr) {
+    float* ht = p.ht + (static_cast<size_t>(bh) * D + v0) * D + k0;
+#pragma unroll
+    for (int r = 0; r < ROWS; ++r) *reinterpret_cast<float4*>(ht + r * D) = s[r];
+  }
+}
+
+template <int ROWS>
+cudaError_t launch_rows(const RecurrentParams& p, bool g_bf16, cudaStream_t stream) {
+  const int grid = p.B * p.H * (D / (ROWS * REC_WARPS));
+  if (g_bf16) kda_recurrent_kernel<ROWS, true><<<grid, REC_WARPS * 32, 0, stream>>>(p);
+  else kda_recurrent_kernel<ROWS, false><<<grid, REC_WARPS * 32, 0, stream>>>(p);
+  return cudaGetLastError();
+}
+}  // namespace
+
+// rows per warp: 8 (four CTAs per head) once there are enough heads to fill the GPU, else 2
+// (sixteen CTAs per head) so that a handful of heads still spreads over many SMs
+cudaError_t launch_recurrent(const RecurrentParams& p, bool g_bf16, int sms, cudaStream_t stream) {
+  const long long bh = static_cast<long long>(p.B) * p.H;
+  if (bh * 4 >= 2LL * sms) return launch_rows<8>(p, g_bf16, stream);
+  if (bh * 8 >= 2LL * sms) return launch_rows<4>(p, g_bf16, stream);
+  return launch_rows<2>(p, g_bf16, stream);
+}
+
+}  // namespace kda

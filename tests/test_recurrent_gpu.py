@@ -1,0 +1,105 @@
+"""Token recurrence (decode / short sequences) against the oracle and against the chunk kernels.
+
+Tolerances: outputs of benchmark-distributed inputs are O(0.06), bf16 output -> 1e-3 max-abs as
+for the chunk path; states 2e-3.  The float64 token recurrence of the oracle is the gold; the
+chunk forward of this build is the consistency partner (a prefill followed by decode steps must
+continue the sequence the chunk forward would have produced in one go).
+"""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+from oracle import kda_oracle as O  # noqa: E402
+
+
+def _dev(inp):
+    dev = torch.device("cuda", 0)
+    return {k: (v.to(dev) if torch.is_tensor(v) else v) for k, v in inp.items()}
+
+
+def _kw(d):
+    return dict(scale=d["scale"], lower_bound=d["lower_bound"], A_log=d["A_log"], dt_bias=d["dt_bias"])
+
+
+@pytest.mark.parametrize("B,T,H,h0_std,g_dtype", [(2, 1, 4, 0.5, torch.bfloat16), (1, 7, 3, None, torch.float32),
+                                                   (3, 33, 5, 0.02, torch.bfloat16), (40, 2, 32, 0.3, torch.bfloat16)])
+def test_recurrent_matches_gold_and_chunk_oracle(B, T, H, h0_std, g_dtype):
+    import kda_ascendc_b200 as K
+    inp = O.make_inputs(B, T, H, seed0=11, h0_std=h0_std, g_dtype=g_dtype)
+    d = _dev(inp)
+    o, ht = K.kda_recurrent_fwd(d["q"], d["k"], d["v"], d["g"], d["beta"], initial_state=d["initial_state"], **_kw(d))
+    torch.cuda.synchronize()
+    o_g, ht_g = O.run_recurrent_gold(inp)
+    o_c, ht_c = O.run_chunk_reference(inp)
+    o, ht = o.float().cpu(), ht.cpu()
+    scale_o = max(1.0, o_g.abs().max().item() / 0.06)
+    scale_h = max(1.0, ht_g.abs().max().item())
+    assert (o - o_g.float()).abs().max().item() <= 1e-3 * scale_o
+    assert (ht - ht_g.float()).abs().max().item() <= 2e-3 * scale_h
+    assert (o - o_c.float()).abs().max().item() <= 1e-3 * scale_o
+    assert (ht - ht_c).abs().max().item() <= 2e-3 * scale_h
+
+
+def test_prefill_then_decode_continues_the_sequence():
+    import kda_ascendc_b200 as K
+    B, T, H, n_dec = 2, 200, 4, 9           # prefill ends inside a chunk (200 = 12 * 16 + 8)
+    inp = O.make_inputs(B, T + n_dec, H, seed0=5, regime="carry", h0_std=0.3)
+    d = _dev(inp)
+    flags = dict(use_qk_l2norm_in_kernel=True, use_gate_in_kernel=True, use_beta_sigmoid_in_kernel=True,
+                 output_final_state=True)
+    o_full, ht_full = K.kda_bt16_fwd(d["q"], d["k"], d["v"], d["g"], d["beta"], initial_state=d["initial_state"],
+                                     **flags, **_kw(d))
+    sl = lambda x, a, b: x[:, a:b]
+    o_pre, state = K.kda_bt16_fwd(*(sl(d[n], 0, T).contiguous() for n in ("q", "k", "v", "g", "beta")),
+                                  initial_state=d["initial_state"], **flags, **_kw(d))
+    outs = []
+    for t in range(T, T + n_dec):            # one token per call, state updated in place
+        o_t, state = K.kda_recurrent_fwd(*(sl(d[n], t, t + 1) for n in ("q", "k", "v", "g", "beta")),
+                                         initial_state=state, inplace_state=True, **_kw(d))
+        outs.append(o_t)
+    torch.cuda.synchronize()
+    o_dec = torch.cat(outs, dim=1).float()
+    ref = o_full[:, T:].float()
+    tol_o = 2e-2 * ref.abs().max().item()    # the reference's relative bound for O(1) states
+    assert (o_dec - ref).abs().max().item() <= tol_o
+    assert (o_pre.float() - o_full[:, :T].float()).abs().max().item() <= tol_o
+    assert (state - ht_full).abs().max().item() <= 2e-2 * ht_full.abs().max().item()
+    # and against the float64 gold over the whole sequence
+    o_g, ht_g = O.run_recurrent_gold(inp)
+    assert (o_dec.cpu() - o_g[:, T:].float()).abs().max().item() <= 2e-2 * o_g.abs().max().item()
+    assert (state.cpu() - ht_g.float()).abs().max().item() <= 2e-2 * ht_g.abs().max().item()
+
+
+def test_recurrent_inplace_and_strided_views():
+    import kda_ascendc_b200 as K
+    B, T, H = 2, 3, 6
+    inp = O.make_inputs(B, T, H, seed0=3, h0_std=0.2)
+    d = _dev(inp)
+    o_ref, ht_ref = K.kda_recurrent_fwd(d["q"], d["k"], d["v"], d["g"], d["beta"], initial_state=d["initial_state"], **_kw(d))
+    # in place
+    st = d["initial_state"].clone()
+    o_ip, st2 = K.kda_recurrent_fwd(d["q"], d["k"], d["v"], d["g"], d["beta"], initial_state=st, inplace_state=True, **_kw(d))
+    assert st2.data_ptr() == st.data_ptr()
+    assert torch.equal(o_ip, o_ref) and torch.equal(st, ht_ref)
+    # head-sliced views of a larger problem (strides passed through, no copy)
+    hs = slice(2, 5)
+    o_v, ht_v = K.kda_recurrent_fwd(d["q"][:, :, hs], d["k"][:, :, hs], d["v"][:, :, hs], d["g"][:, :, hs], d["beta"][:, :, hs],
+                                    initial_state=d["initial_state"][:, hs].contiguous(), scale=d["scale"],
+                                    lower_bound=d["lower_bound"], A_log=d["A_log"][hs].contiguous(),
+                                    dt_bias=d["dt_bias"].view(H, 128)[hs].contiguous().view(-1))
+    assert torch.equal(o_v, o_ref[:, :, hs]) and torch.equal(ht_v, ht_ref[:, hs])
+    # zero state when none is given
+    o_z, _ = K.kda_recurrent_fwd(d["q"], d["k"], d["v"], d["g"], d["beta"], initial_state=None, **_kw(d))
+    o_z2, _ = K.kda_recurrent_fwd(d["q"], d["k"], d["v"], d["g"], d["beta"], initial_state=torch.zeros_like(d["initial_state"]), **_kw(d))
+    assert torch.equal(o_z, o_z2)
+
+
+def test_recurrent_argument_errors():
+    import kda_ascendc_b200 as K
+    inp = O.make_inputs(1, 1, 2, seed0=1, h0_std=0.1)
+    d = _dev(inp)
+    with pytest.raises(ValueError):
+        K.kda_recurrent_fwd(d["q"], d["k"], d["v"], d["g"], d["beta"], initial_state=None, inplace_state=True, **_kw(d))
+    with pytest.raises((ValueError, TypeError)):
+        K.kda_recurrent_fwd(d["q"], d["k"], d["v"], d["g"], d["beta"], scale=d["scale"], A_log=None, dt_bias=d["dt_bias"])
