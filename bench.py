@@ -45,7 +45,7 @@ import torch  # noqa: E402
 
 B, T, H, D = 1, 8192, 32, 128
 BT = 16
-WORKLOAD = "KDA fwd B=1 T=8192 H=32 K=V=128 BT=16 bf16 (BASELINE config 2) per GPU"
+WORKLOAD = "KDA fwd B=1 T=8192 H=32 K=V=128 BT=16 bf16 (headline benchmark shape) per GPU"
 METRIC = "KDA fwd tokens/s at B1 T8192 H32 K=V=128 bf16"
 # algorithmic bytes / flops per (token, head) of the two-kernel contract of the reference
 K1_BYTES_PER_TH = 2084.0     # reads q,k,v,g bf16 + beta; writes w,u bf16, g fp32, Aqk bf16

@@ -83,7 +83,15 @@ typedef struct KdaFwdArgs {
                            1 "n8":  8 rows per warp  (k2_vsplit 4, 8 or 16)
                            2 "n16": 16 rows per warp (k2_vsplit 2, 4 or 8), rows on the MMA N dimension
                            3 "m16": 16 rows per warp (k2_vsplit 2, 4 or 8), rows on the MMA M dimension */
-  int32_t reserved_;
+  /* Packed variable-length sequences (optional; not in the reference, whose README.md:509 lists
+   * it as future work).  n_seqs > 0 selects it: B must be 1, T is the total number of packed
+   * tokens, h0 / ht are [n_seqs, H, 128, 128], and the two tables (DEVICE memory, int32, made by
+   * kda_varlen_fill_tables) say where every sequence and every 16-token chunk lies.  The workspace
+   * then holds one record per (chunk, head): kda_fwd_workspace_bytes(1, 16 * n_chunks, H). */
+  int32_t n_seqs;
+  const int32_t* chunk_table;  /* [n_chunks][4]: first token, valid tokens, first record, chunks of its sequence */
+  const int32_t* seq_table;    /* [n_seqs][4]:   first token, chunks, first record, length */
+  int32_t n_chunks;
 } KdaFwdArgs;
 
 /* Bytes of K1 -> K2 scratch for a (B, T, H) problem: a 256-byte status block
@@ -112,6 +120,13 @@ int kda_fwd_k2_state(const KdaFwdArgs* args, int zero_u, void* stream);
  * tests/test_kda_bt16.py:26-39) with the chunk path's rounding of the normalised q and k, so a
  * prefill by kda_fwd followed by steps of this function continues the same sequence. */
 int kda_recurrent_fwd(const KdaFwdArgs* args, void* stream);
+
+/* Host helper for packed variable-length input: from cu_seqlens[0..n_seqs] (HOST memory,
+ * non-decreasing, cu_seqlens[0] = 0, no empty sequence) fills chunk_table ([n_chunks][4]) and
+ * seq_table ([n_seqs][4]) in HOST memory for H heads; the caller copies them to the device.
+ * Called with chunk_table == NULL it only counts.  Returns n_chunks, or a negative error. */
+int kda_varlen_fill_tables(const int32_t* cu_seqlens, int32_t n_seqs, int32_t H, int32_t* chunk_table,
+                           int32_t* seq_table);
 
 /* Whole forward with the K1 -> K2 scratch taken from a fixed array inside the library instead
  * of args->workspace (which is ignored).  It has no counterpart in the reference, whose host

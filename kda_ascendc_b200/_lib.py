@@ -16,7 +16,7 @@ FLAG_GATE, FLAG_L2NORM, FLAG_BETA_SIGMOID = 1, 2, 4
 
 EXPORTS = (
     "kda_fwd_workspace_bytes", "kda_fwd", "kda_fwd_k1", "kda_fwd_k2", "kda_fwd_k2_state", "kda_recurrent_fwd",
-    "kda_fwd_static_scratch",
+    "kda_varlen_fill_tables", "kda_fwd_static_scratch",
     "kda_fwd_status", "kda_last_launch_count", "kda_last_error", "kda_version",
 )
 
@@ -31,7 +31,9 @@ class KdaFwdArgs(ctypes.Structure):
         ("q_stride", ctypes.c_int64 * 3), ("k_stride", ctypes.c_int64 * 3), ("v_stride", ctypes.c_int64 * 3),
         ("g_stride", ctypes.c_int64 * 3), ("o_stride", ctypes.c_int64 * 3), ("beta_stride", ctypes.c_int64 * 3),
         ("scale", ctypes.c_float), ("lower_bound", ctypes.c_float), ("flags", ctypes.c_uint32),
-        ("k2_vsplit", ctypes.c_int32), ("k2_variant", ctypes.c_int32), ("reserved_", ctypes.c_int32),
+        ("k2_vsplit", ctypes.c_int32), ("k2_variant", ctypes.c_int32),
+        ("n_seqs", ctypes.c_int32), ("chunk_table", ctypes.c_void_p), ("seq_table", ctypes.c_void_p),
+        ("n_chunks", ctypes.c_int32),
     ]
 
 
@@ -56,6 +58,9 @@ def load() -> ctypes.CDLL:
         fn.argtypes = [ctypes.POINTER(KdaFwdArgs), ctypes.c_void_p]
     lib.kda_fwd_k2_state.restype = ctypes.c_int
     lib.kda_fwd_k2_state.argtypes = [ctypes.POINTER(KdaFwdArgs), ctypes.c_int, ctypes.c_void_p]
+    lib.kda_varlen_fill_tables.restype = ctypes.c_int
+    lib.kda_varlen_fill_tables.argtypes = [ctypes.POINTER(ctypes.c_int32), ctypes.c_int32, ctypes.c_int32,
+                                           ctypes.POINTER(ctypes.c_int32), ctypes.POINTER(ctypes.c_int32)]
     lib.kda_fwd_status.restype = ctypes.c_int
     lib.kda_fwd_status.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.POINTER(ctypes.c_int32)]
     lib.kda_last_launch_count.restype = ctypes.c_int

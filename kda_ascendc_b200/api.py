@@ -40,7 +40,7 @@ _LAUNCH_COUNTS = {"kda_k1": 0, "kda_k2": 0, "kda_recurrent": 0}
 # validation (same checks, order and messages as the reference's shared validator)
 # ---------------------------------------------------------------------------
 def _validate_kda_inputs(q, k, v, g, beta, initial_state, use_gate_in_kernel, safe_gate, lower_bound,
-                         A_log, dt_bias, state_v_first, require_contiguous=True):
+                         A_log, dt_bias, state_v_first, require_contiguous=True, n_states=None):
     for name, x, nd, lay in (("q", q, 4, "[B, T, H, D]"), ("k", k, 4, "[B, T, H, D]"),
                              ("v", v, 4, "[B, T, HV, V]"), ("g", g, 4, "[B, T, HV, D]"),
                              ("beta", beta, 3, "[B, T, HV]")):
@@ -92,7 +92,8 @@ def _validate_kda_inputs(q, k, v, g, beta, initial_state, use_gate_in_kernel, sa
             raise TypeError(f"initial_state must be float32, got {initial_state.dtype}")
         if initial_state.device != q.device:
             raise ValueError(f"initial_state device {initial_state.device} must match q ({q.device})")
-        expected = (B, HV, V, K) if state_v_first else (B, HV, K, V)
+        ns = B if n_states is None else n_states   # packed sequences carry one state per sequence
+        expected = (ns, HV, V, K) if state_v_first else (ns, HV, K, V)
         if tuple(initial_state.shape) != expected:
             raise ValueError(f"initial_state.shape {tuple(initial_state.shape)} must be {expected} "
                              f"(state_v_first={state_v_first})")
@@ -207,6 +208,33 @@ def _get_workspace(device, B, T, H, reuse: bool) -> torch.Tensor:
     return torch.empty(nbytes, dtype=torch.uint8, device=device)
 
 
+def _varlen_tables(cu_seqlens, T: int, H: int, device):
+    """(n_seqs, n_chunks, chunk_table, seq_table) for packed sequences; tables on ``device``.
+
+    ``cu_seqlens``: 1-D integer tensor (any device) or sequence, ``[0, ..., T]``, non-decreasing,
+    no empty sequence.  The tables are built on the host by the library's own helper (one
+    device-to-host read if ``cu_seqlens`` lives on the GPU) and copied over.
+    """
+    cu = torch.as_tensor(cu_seqlens).detach().to("cpu", torch.int32).contiguous()
+    if cu.ndim != 1 or cu.numel() < 2:
+        raise ValueError("cu_seqlens must be 1-D with at least two entries")
+    if int(cu[-1]) != T:
+        raise ValueError(f"cu_seqlens must end at the number of packed tokens T={T}, got {int(cu[-1])}")
+    n_seqs = cu.numel() - 1
+    lib = _lib.load()
+    i32p = ctypes.POINTER(ctypes.c_int32)
+    cu_p = ctypes.cast(cu.data_ptr(), i32p)
+    n_chunks = lib.kda_varlen_fill_tables(cu_p, n_seqs, H, None, None)
+    _check(min(n_chunks, 0))
+    host = torch.empty((n_chunks + n_seqs, 4), dtype=torch.int32).pin_memory() if torch.cuda.is_available() \
+        else torch.empty((n_chunks + n_seqs, 4), dtype=torch.int32)
+    rc = lib.kda_varlen_fill_tables(cu_p, n_seqs, H, ctypes.cast(host.data_ptr(), i32p),
+                                    ctypes.cast(host[n_chunks:].data_ptr(), i32p))
+    _check(min(rc, 0))
+    dev_tab = host.to(device, non_blocking=True)
+    return n_seqs, n_chunks, dev_tab[:n_chunks], dev_tab[n_chunks:], host
+
+
 def _flags(use_gate, use_l2, use_beta_sigmoid) -> int:
     return ((_lib.FLAG_GATE if use_gate else 0) | (_lib.FLAG_L2NORM if use_l2 else 0) |
             (_lib.FLAG_BETA_SIGMOID if use_beta_sigmoid else 0))
@@ -214,7 +242,8 @@ def _flags(use_gate, use_l2, use_beta_sigmoid) -> int:
 
 def _forward(q, k, v, g, beta, scale, initial_state, output_final_state, use_qk_l2norm_in_kernel,
              use_gate_in_kernel, use_beta_sigmoid_in_kernel, lower_bound, A_log, dt_bias, state_v_first,
-             return_intermediates=False, reuse_workspace=False, k2_vsplit=0, k2_variant=0, workspace=None):
+             return_intermediates=False, reuse_workspace=False, k2_vsplit=0, k2_variant=0, workspace=None,
+             cu_seqlens=None):
     """Allocate, launch K1 + K2 on the current stream, return (o, ht[, intermediates])."""
     lib = _lib.load()
     B, T, H, K = q.shape
@@ -223,8 +252,12 @@ def _forward(q, k, v, g, beta, scale, initial_state, output_final_state, use_qk_
     if h0 is not None and not state_v_first:
         h0 = h0.transpose(-1, -2).contiguous()  # kernels keep the state V-first
     o = torch.empty((B, T, H, HEAD_DIM), dtype=torch.bfloat16, device=dev)
-    ht = torch.empty((B, H, HEAD_DIM, HEAD_DIM), dtype=torch.float32, device=dev) if output_final_state else None
-    ws = workspace if workspace is not None else _get_workspace(dev, B, T, H, reuse_workspace)
+    n_states, ws_tokens, tables = B, T, None
+    if cu_seqlens is not None:
+        tables = _varlen_tables(cu_seqlens, T, H, dev)
+        n_states, ws_tokens = tables[0], BT * tables[1]
+    ht = torch.empty((n_states, H, HEAD_DIM, HEAD_DIM), dtype=torch.float32, device=dev) if output_final_state else None
+    ws = workspace if workspace is not None else _get_workspace(dev, B, ws_tokens, H, reuse_workspace)
     g_out = ainv = None
     if return_intermediates:
         g_out = torch.empty((B, T, H, HEAD_DIM), dtype=torch.float32, device=dev)
@@ -233,6 +266,9 @@ def _forward(q, k, v, g, beta, scale, initial_state, output_final_state, use_qk_
                      h0=h0, o=o, ht=ht, workspace=ws, g_out=g_out, ainv_out=ainv, k2_vsplit=k2_vsplit,
                      k2_variant=k2_variant,
                      flags=_flags(use_gate_in_kernel, use_qk_l2norm_in_kernel, use_beta_sigmoid_in_kernel))
+    if tables is not None:
+        args.n_seqs, args.n_chunks = tables[0], tables[1]
+        args.chunk_table, args.seq_table = _ptr(tables[2]), _ptr(tables[3])
     stream = _stream_handle()
     profile = os.environ.get("KDA_PROFILE", "0") == "1"
     with torch.cuda.device(dev):
@@ -305,7 +341,7 @@ def kda_recurrent_fwd(q, k, v, g, beta, scale=None, initial_state=None, output_f
 def kda_bt16_fwd(q, k, v, g, beta, scale=None, initial_state=None, output_final_state=False,
                  use_qk_l2norm_in_kernel=False, use_gate_in_kernel=False, use_beta_sigmoid_in_kernel=False,
                  safe_gate=True, lower_bound=-5.0, A_log=None, dt_bias=None, state_v_first=True,
-                 use_fused_kernel=False, reuse_workspace=False):
+                 use_fused_kernel=False, reuse_workspace=False, cu_seqlens=None):
     """KDA forward, chunk size 16.
 
     q/k: ``[B, T, H, 128]`` bf16; v: ``[B, T, H, 128]`` bf16; g: raw gate ``[B, T, H, 128]``
@@ -317,15 +353,26 @@ def kda_bt16_fwd(q, k, v, g, beta, scale=None, initial_state=None, output_final_
     ``use_fused_kernel`` is accepted for signature compatibility: the reference's
     single-kernel variant computes the same function, and this build has one device path.
     ``reuse_workspace`` caches only the internal scratch per shape (never the outputs).
+
+    ``cu_seqlens`` (not in the reference, which lists variable-length input as future work,
+    ``README.md:509``; the convention is that of ``chunk_kda`` in flash-linear-attention): packed
+    sequences in one ``[1, T, H, 128]`` batch, ``cu_seqlens = [0, ..., T]``; every sequence is
+    chunked from its own first token, ``initial_state`` / the returned state are
+    ``[n_seqs, H, 128, 128]``.
     """
+    n_states = None
+    if cu_seqlens is not None:
+        if q.ndim == 4 and q.shape[0] != 1:
+            raise ValueError(f"cu_seqlens needs a packed batch of size 1, got B={q.shape[0]}")
+        n_states = len(cu_seqlens) - 1
     _validate_kda_inputs(q, k, v, g, beta, initial_state, use_gate_in_kernel, safe_gate, lower_bound,
-                         A_log, dt_bias, state_v_first)
+                         A_log, dt_bias, state_v_first, n_states=n_states)
     _require_cuda(q)
     if scale is None:
         scale = q.shape[-1] ** -0.5
     return _forward(q, k, v, g, beta, scale, initial_state, output_final_state, use_qk_l2norm_in_kernel,
                     use_gate_in_kernel, use_beta_sigmoid_in_kernel, lower_bound, A_log, dt_bias, state_v_first,
-                    reuse_workspace=reuse_workspace)
+                    reuse_workspace=reuse_workspace, cu_seqlens=cu_seqlens)
 
 
 def kda_bt16_debug(q, k, v, g, beta, scale=None, initial_state=None, output_final_state=False,

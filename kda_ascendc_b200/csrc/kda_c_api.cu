@@ -1,11 +1,15 @@
 // C-ABI layer of libkda_b200.so: argument checks, workspace arithmetic, stage launches.
 // Interface and the reference entry points it stands in for: include/kda_b200.h.
+#include <cstddef>
 #include <cstdio>
 #include <cstring>
 
 #include "../../include/kda_b200.h"
 #include "kda_common.cuh"
 #include "kda_kernels.h"
+
+static_assert(sizeof(KdaFwdArgs) == 312 && offsetof(KdaFwdArgs, chunk_table) == 288,
+              "KdaFwdArgs layout is part of the ABI (bindings mirror it field by field)");
 
 namespace {
 
@@ -24,6 +28,16 @@ int check_common(const KdaFwdArgs* a) {
   if (a->workspace == nullptr) return fail(KDA_ERR_INVALID_ARG, "kda: workspace is NULL%s", "");
   if (reinterpret_cast<uintptr_t>(a->workspace) % 256 != 0)
     return fail(KDA_ERR_INVALID_ARG, "kda: workspace must be 256-byte aligned%s", "");
+  if (a->n_seqs < 0) return fail(KDA_ERR_INVALID_ARG, "kda: n_seqs must not be negative%s", "");
+  if (a->n_seqs > 0) {
+    if (a->B != 1) return fail(KDA_ERR_INVALID_ARG, "kda: packed sequences need B = 1%s (got %lld)", "", a->B);
+    if (a->chunk_table == nullptr || a->seq_table == nullptr || a->n_chunks <= 0)
+      return fail(KDA_ERR_INVALID_ARG, "kda: packed sequences need chunk_table, seq_table and n_chunks%s", "");
+    if (reinterpret_cast<uintptr_t>(a->chunk_table) % 16 != 0 || reinterpret_cast<uintptr_t>(a->seq_table) % 16 != 0)
+      return fail(KDA_ERR_INVALID_ARG, "kda: chunk_table and seq_table must be 16-byte aligned%s", "");
+    if (a->g_out != nullptr || a->ainv_out != nullptr)
+      return fail(KDA_ERR_INVALID_ARG, "kda: the debug outputs are not available with packed sequences%s", "");
+  }
   return KDA_OK;
 }
 
@@ -72,7 +86,7 @@ int check_k2(const KdaFwdArgs* a, bool state_only) {
 void pick_split(const KdaFwdArgs* a, int* vsplit, int* variant) {
   int dev = 0, sms = 148;
   if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-  const long long bh = static_cast<long long>(a->B) * a->H;
+  const long long bh = static_cast<long long>(a->n_seqs > 0 ? a->n_seqs : a->B) * a->H;
   int var = a->k2_variant;
   int vs = a->k2_vsplit;
   if (var == 0) {
@@ -117,6 +131,10 @@ int do_k1(const KdaFwdArgs* a, cudaStream_t st) {
   p.scale = a->scale;
   p.lower_bound = a->lower_bound;
   p.flags = a->flags;
+  if (a->n_seqs > 0) {
+    p.chunk_table = reinterpret_cast<const int4*>(a->chunk_table);
+    p.n_chunks = a->n_chunks;
+  }
   // 2^g may be factored as 2^(g-g_mid) * 2^(g_mid) only while no factor can underflow:
   // 16 tokens * |lower_bound| * RCP_LN2 must stay inside the fp32 exponent range.
   const bool fast_exp = (a->flags & KDA_FLAG_GATE_IN_KERNEL) && (16.0f * -a->lower_bound * kda::RCP_LN2 <= 120.0f);
@@ -141,6 +159,10 @@ int do_k2(const KdaFwdArgs* a, bool state_only, int zero_u, cudaStream_t st) {
   for (int i = 0; i < 3; ++i) p.o_s[i] = a->o_stride[i];
   p.scale = a->scale;
   p.zero_u = zero_u;
+  if (a->n_seqs > 0) {
+    p.seq_table = reinterpret_cast<const int4*>(a->seq_table);
+    p.n_seqs = a->n_seqs;
+  }
   int vsplit = 4, variant = 3;
   pick_split(a, &vsplit, &variant);
   cudaError_t e = (variant == 3) ? kda::launch_k2m(p, vsplit, state_only, st)
@@ -203,6 +225,7 @@ int kda_recurrent_fwd(const KdaFwdArgs* a, void* stream) {
   if (a == nullptr) return fail(KDA_ERR_INVALID_ARG, "kda: args is NULL%s", "");
   if (a->B <= 0 || a->T <= 0 || a->H <= 0)
     return fail(KDA_ERR_INVALID_ARG, "kda: B, T, H must be positive%s (T=%lld, H=%lld)", "", a->T, a->H);
+  if (a->n_seqs != 0) return fail(KDA_ERR_INVALID_ARG, "kda: the recurrent step takes a fixed-length batch%s (n_seqs must be 0)", "");
   if (!a->q || !a->k || !a->v || !a->g || !a->beta || !a->o || !a->A_log)
     return fail(KDA_ERR_INVALID_ARG, "kda: the recurrent step needs q, k, v, g, beta, A_log and o%s", "");
   const uint32_t all = KDA_FLAG_GATE_IN_KERNEL | KDA_FLAG_QK_L2NORM | KDA_FLAG_BETA_SIGMOID;
@@ -238,6 +261,34 @@ int kda_recurrent_fwd(const KdaFwdArgs* a, void* stream) {
   if (e != cudaSuccess) return fail(KDA_ERR_CUDA, "kda: recurrent launch failed: %s", cudaGetErrorString(e));
   ++g_launches;
   return KDA_OK;
+}
+
+int kda_varlen_fill_tables(const int32_t* cu, int32_t n_seqs, int32_t H, int32_t* chunk_table, int32_t* seq_table) {
+  if (cu == nullptr || n_seqs <= 0 || H <= 0)
+    return fail(KDA_ERR_INVALID_ARG, "kda: cu_seqlens, n_seqs and H are required%s", "");
+  if (cu[0] != 0) return fail(KDA_ERR_INVALID_ARG, "kda: cu_seqlens must start at 0%s (got %lld)", "", cu[0]);
+  long long chunks = 0;
+  for (int i = 0; i < n_seqs; ++i) {
+    const long long len = static_cast<long long>(cu[i + 1]) - cu[i];
+    if (len <= 0) return fail(KDA_ERR_INVALID_ARG, "kda: sequence %s%lld is empty or cu_seqlens decreases", "", i);
+    const long long nt = (len + kda::BT - 1) / kda::BT;
+    if ((chunks + nt) * H > 0x7fffffffLL) return fail(KDA_ERR_INVALID_ARG, "kda: too many chunk records%s", "");
+    if (chunk_table != nullptr && seq_table != nullptr) {
+      seq_table[4 * i + 0] = cu[i];
+      seq_table[4 * i + 1] = static_cast<int32_t>(nt);
+      seq_table[4 * i + 2] = static_cast<int32_t>(chunks * H);
+      seq_table[4 * i + 3] = static_cast<int32_t>(len);
+      for (long long n = 0; n < nt; ++n) {
+        int32_t* e = chunk_table + 4 * (chunks + n);
+        e[0] = cu[i] + static_cast<int32_t>(n * kda::BT);
+        e[1] = static_cast<int32_t>(len - n * kda::BT < kda::BT ? len - n * kda::BT : kda::BT);
+        e[2] = static_cast<int32_t>(chunks * H + n);
+        e[3] = static_cast<int32_t>(nt);
+      }
+    }
+    chunks += nt;
+  }
+  return static_cast<int>(chunks);
 }
 
 int kda_fwd_status(const void* workspace, void* stream, int32_t* status_out) {

@@ -74,6 +74,14 @@ __device__ __forceinline__ K1Item k1_item(const K1Params& p, int id) {
   K1Item w;
   const int bn = static_cast<int>(p.div_h.div(id));
   w.h = id - bn * p.H;
+  if (p.chunk_table != nullptr) {   // packed sequences: the chunk's place comes from the table
+    const int4 e = __ldg(p.chunk_table + bn);
+    w.b = 0;
+    w.t0 = e.x;
+    w.nvalid = e.y;
+    w.rec_idx = static_cast<size_t>(e.z) + static_cast<size_t>(w.h) * e.w;
+    return w;
+  }
   w.b = static_cast<int>(p.div_nt.div(bn));
   const int n = bn - w.b * p.NT;
   w.t0 = n * BT;
@@ -93,7 +101,7 @@ __global__ void __launch_bounds__(128, 4) kda_k1_kernel(const __grid_constant__ 
   const int lane = tid & 31;
   const int warp = tid >> 5;
   const int gq = lane >> 2, tq = lane & 3;
-  const int n_items = p.B * p.NT * p.H;
+  const int n_items = (p.chunk_table != nullptr ? p.n_chunks : p.B * p.NT) * p.H;
 
   const uint32_t sbase = smem_u32(smem);
   const uint32_t mbar = sbase + SM::MBAR;
@@ -546,7 +554,7 @@ static cudaError_t launch_k1_t(const K1Params& p, cudaStream_t stream) {
     if (e != cudaSuccess) return e;
     grid_cap[dev] = sms * (per_sm > 0 ? per_sm : 1);   // persistent: one CTA per resident slot
   }
-  const long long n_items = static_cast<long long>(p.B) * p.NT * p.H;
+  const long long n_items = (p.chunk_table != nullptr ? static_cast<long long>(p.n_chunks) : static_cast<long long>(p.B) * p.NT) * p.H;
   const int grid = static_cast<int>(n_items < grid_cap[dev] ? n_items : grid_cap[dev]);
   kda_k1_kernel<G_BF16, FAST_EXP><<<grid, 128, smem_bytes, stream>>>(p);
   return cudaGetLastError();

@@ -71,8 +71,16 @@ __global__ void __launch_bounds__((CW + 1) * 32, 1) kda_k2_kernel(const K2Params
   const int warp = tid >> 5;
   const int bh = blockIdx.x / NV;
   const int vs = blockIdx.x % NV;
-  const int b = bh / p.H, h = bh % p.H;
-  const int NT = p.NT;
+  int b = bh / p.H;
+  const int h = bh % p.H;
+  int NT = p.NT, Tlen = p.T, tok0 = 0;
+  size_t rec_first = static_cast<size_t>(bh) * NT;
+  if (p.seq_table != nullptr) {   // packed sequences: bh = sequence * H + head
+    const int4 e = __ldg(p.seq_table + b);
+    tok0 = e.x; NT = e.y; Tlen = e.w;
+    rec_first = static_cast<size_t>(e.z) + static_cast<size_t>(h) * NT;
+    b = 0;
+  }
 
   const uint32_t sbase = smem_u32(smem);
   const uint32_t full0 = sbase + SM::BARS;
@@ -91,7 +99,7 @@ __global__ void __launch_bounds__((CW + 1) * 32, 1) kda_k2_kernel(const K2Params
   }
   __syncthreads();
 
-  const uint8_t* rec_bh = p.rec + static_cast<size_t>(bh) * NT * REC_BYTES;
+  const uint8_t* rec_bh = p.rec + rec_first * REC_BYTES;
 
   if (warp == CW) {
     // ------------------------------ producer -------------------------------
@@ -147,7 +155,7 @@ __global__ void __launch_bounds__((CW + 1) * 32, 1) kda_k2_kernel(const K2Params
                   "tile bases must keep address bits 5..7 clear");
     const uint32_t a1_lane = swz_off(a1_row, a1_col), a2_lane = swz_off(a2_row, a2_col);
     const uint32_t u_off = REC_SHARED_BYTES + warp * (NVT * REC_U_TILE_BYTES) + lane * 16;
-    __nv_bfloat16* const ob = STATE_ONLY ? nullptr : p.o + b * p.o_s[0] + h * p.o_s[2] + v0 + tq * 2;
+    __nv_bfloat16* const ob = STATE_ONLY ? nullptr : p.o + b * p.o_s[0] + tok0 * p.o_s[1] + h * p.o_s[2] + v0 + tq * 2;
     const bool use_u = !(STATE_ONLY && p.zero_u);
 
     uint32_t aw[8][4], aq[8][4];     // A fragments of w and qg (one per 16-wide k-step)
@@ -320,8 +328,8 @@ __global__ void __launch_bounds__((CW + 1) * 32, 1) kda_k2_kernel(const K2Params
       __nv_bfloat16* op = ob + static_cast<int64_t>(tok) * p.o_s[1];
 #pragma unroll
       for (int nv = 0; nv < NVT; ++nv) {
-        if (tok < p.T) *reinterpret_cast<uint32_t*>(op + nv * 8) = pack_bf16(oa[nv][0], oa[nv][1]);
-        if (tok + 8 < p.T) *reinterpret_cast<uint32_t*>(op + 8 * p.o_s[1] + nv * 8) = pack_bf16(oa[nv][2], oa[nv][3]);
+        if (tok < Tlen) *reinterpret_cast<uint32_t*>(op + nv * 8) = pack_bf16(oa[nv][0], oa[nv][1]);
+        if (tok + 8 < Tlen) *reinterpret_cast<uint32_t*>(op + 8 * p.o_s[1] + nv * 8) = pack_bf16(oa[nv][2], oa[nv][3]);
       }
     }
 
@@ -362,7 +370,7 @@ static cudaError_t launch_k2_t(const K2Params& p, cudaStream_t stream) {
     if (e != cudaSuccess) return e;
     configured[dev] = true;
   }
-  const int nblocks = p.B * p.H * (D / (CW * NVT * 8));
+  const int nblocks = (p.seq_table != nullptr ? p.n_seqs : p.B) * p.H * (D / (CW * NVT * 8));
   kda_k2_kernel<CW, NVT, STATE_ONLY><<<nblocks, (CW + 1) * 32, smem_bytes, stream>>>(p);
   return cudaGetLastError();
 }

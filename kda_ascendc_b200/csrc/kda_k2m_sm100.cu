@@ -47,8 +47,16 @@ __global__ void __launch_bounds__((CW + 1) * 32, MINB) kda_k2m_kernel(const K2Pa
   const int warp = tid >> 5;
   const int bh = blockIdx.x / NV;
   const int vs = blockIdx.x % NV;
-  const int b = bh / p.H, h = bh % p.H;
-  const int NT = p.NT;
+  int b = bh / p.H;
+  const int h = bh % p.H;
+  int NT = p.NT, Tlen = p.T, tok0 = 0;
+  size_t rec_first = static_cast<size_t>(bh) * NT;
+  if (p.seq_table != nullptr) {   // packed sequences: bh = sequence * H + head
+    const int4 e = __ldg(p.seq_table + b);
+    tok0 = e.x; NT = e.y; Tlen = e.w;
+    rec_first = static_cast<size_t>(e.z) + static_cast<size_t>(h) * NT;
+    b = 0;
+  }
 
   const uint32_t sbase = smem_u32(smem);
   const uint32_t full0 = sbase + SM::BARS;
@@ -67,7 +75,7 @@ __global__ void __launch_bounds__((CW + 1) * 32, MINB) kda_k2m_kernel(const K2Pa
   }
   __syncthreads();
 
-  const uint8_t* rec_bh = p.rec + static_cast<size_t>(bh) * NT * REC_BYTES;
+  const uint8_t* rec_bh = p.rec + rec_first * REC_BYTES;
 
   if (warp == CW) {
     // ------------------------------ producer -------------------------------
@@ -118,7 +126,7 @@ __global__ void __launch_bounds__((CW + 1) * 32, MINB) kda_k2m_kernel(const K2Pa
     // u^T fragment of this warp out of the record's [8-column tile][lane][4] blocks (see kda_common.cuh):
     // element (v = vrow0 + gq + 8a, tok = 2tq + j + 8c)  ->  tile 2*warp + a, lane (2tq+j)*4 + gq/2, slot 2c + gq%2
     const uint32_t u_off = REC_SHARED_BYTES + (warp * 2) * REC_U_TILE_BYTES + ((tq * 2) * 4 + (gq >> 1)) * 16 + (gq & 1) * 4;
-    __nv_bfloat16* const ob = STATE_ONLY ? nullptr : p.o + b * p.o_s[0] + h * p.o_s[2] + vrow0 + tq * 2;
+    __nv_bfloat16* const ob = STATE_ONLY ? nullptr : p.o + b * p.o_s[0] + tok0 * p.o_s[1] + h * p.o_s[2] + vrow0 + tq * 2;
     const bool use_u = !(STATE_ONLY && p.zero_u);
 
     // rolling B fragments of P1: two k-steps ahead
@@ -290,11 +298,11 @@ __global__ void __launch_bounds__((CW + 1) * 32, MINB) kda_k2m_kernel(const K2Pa
     if (!STATE_ONLY && !failed) {
       const int tok = (NT - 1) * BT + gq;
       __nv_bfloat16* op = ob + static_cast<int64_t>(tok) * p.o_s[1];
-      if (tok < p.T) {
+      if (tok < Tlen) {
         *reinterpret_cast<uint32_t*>(op) = o_st[0][0];
         *reinterpret_cast<uint32_t*>(op + 8) = o_st[0][1];
       }
-      if (tok + 8 < p.T) {
+      if (tok + 8 < Tlen) {
         *reinterpret_cast<uint32_t*>(op + 8 * p.o_s[1]) = o_st[1][0];
         *reinterpret_cast<uint32_t*>(op + 8 * p.o_s[1] + 8) = o_st[1][1];
       }
@@ -349,7 +357,7 @@ static cudaError_t launch_k2m_c(const K2Params& p, cudaStream_t stream) {
     cudaError_t e = cudaDeviceGetAttribute(&sms[dev], cudaDevAttrMultiProcessorCount, dev);
     if (e != cudaSuccess) return e;
   }
-  const int nblocks = p.B * p.H * (8 / CW);
+  const int nblocks = (p.seq_table != nullptr ? p.n_seqs : p.B) * p.H * (8 / CW);
   if (CW == 4 && nblocks > sms[dev]) return launch_k2m_t<CW, STATE_ONLY, 2>(p, nblocks, stream);
   return launch_k2m_t<CW, STATE_ONLY, 1>(p, nblocks, stream);
 }

@@ -42,6 +42,10 @@ struct K1Params {
   int64_t q_s[3], k_s[3], v_s[3], g_s[3], beta_s[3];  // element strides (batch, token, head)
   float scale, lower_bound;
   uint32_t flags;
+  // packed variable-length input: one entry per chunk (first token, valid tokens, first record,
+  // chunks of its sequence), B == 1; null for a fixed-length batch
+  const int4* chunk_table;
+  int n_chunks;
 };
 
 struct K2Params {
@@ -54,6 +58,10 @@ struct K2Params {
   int64_t o_s[3];
   float scale;
   int zero_u;        // state-only mode: drop the u term
+  // packed variable-length input: one entry per sequence (first token, chunks, first record,
+  // length); the grid then runs over (sequence, head); null for a fixed-length batch
+  const int4* seq_table;
+  int n_seqs;
 };
 
 cudaError_t launch_k1(const K1Params& p, bool g_bf16, bool fast_exp, cudaStream_t stream);

@@ -46,7 +46,9 @@ extern "C" int kda_fwd_static_scratch(const KdaFwdArgs* args, void* stream) {
     kda::set_last_error("kda: args is NULL");
     return KDA_ERR_INVALID_ARG;
   }
-  const size_t need = kda_fwd_workspace_bytes(args->B, args->T, args->H);
+  // packed sequences hold one record per (chunk, head) of their chunk table
+  const size_t need = args->n_seqs > 0 ? kda_fwd_workspace_bytes(1, 16 * args->n_chunks, args->H)
+                                       : kda_fwd_workspace_bytes(args->B, args->T, args->H);
   if (need == 0) {
     kda::set_last_error("kda: B, T, H must be positive");
     return KDA_ERR_INVALID_ARG;

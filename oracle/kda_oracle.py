@@ -275,6 +275,23 @@ def run_chunk_reference(inp, **kw):
                            initial_state=inp["initial_state"], **kw)
 
 
+def run_chunk_reference_varlen(inp, cu_seqlens, **kw):
+    """Packed variable-length input ([1, T, H, 128], cu_seqlens = [0, ..., T]): the chunk forward of
+    every sequence on its own (chunked from its own first token), outputs re-packed; the initial
+    state, if any, is [n_seqs, H, 128, 128].  Returns (o [1, T, H, 128], ht [n_seqs, H, 128, 128])."""
+    cu = [int(x) for x in cu_seqlens]
+    outs, states = [], []
+    for i in range(len(cu) - 1):
+        a, b = cu[i], cu[i + 1]
+        h0 = None if inp["initial_state"] is None else inp["initial_state"][i:i + 1]
+        o, ht = chunk_reference(inp["q"][:, a:b], inp["k"][:, a:b], inp["v"][:, a:b], inp["g"][:, a:b],
+                                inp["beta"][:, a:b], scale=inp["scale"], lower_bound=inp["lower_bound"],
+                                A_log=inp["A_log"], dt_bias=inp["dt_bias"], initial_state=h0, **kw)
+        outs.append(o)
+        states.append(ht)
+    return torch.cat(outs, dim=1), torch.cat(states, dim=0)
+
+
 def run_recurrent_gold(inp):
     return recurrent_gold(inp["q"], inp["k"], inp["v"], inp["g"], inp["beta"], scale=inp["scale"],
                           lower_bound=inp["lower_bound"], A_log=inp["A_log"], dt_bias=inp["dt_bias"],

@@ -1,4 +1,4 @@
-"""The BASELINE workloads at their full sizes.  The CPU oracle cannot walk them whole in
+"""The benchmark configurations of the reference at their full sizes.  The CPU oracle cannot walk them whole in
 reasonable time, so each is checked through properties that do not depend on size
 (determinism, state chaining at a chunk boundary, head shards, the sequence split) plus the
 oracle on a slice of heads / tokens that it finishes in seconds.  Inputs follow the benchmark

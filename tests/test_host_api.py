@@ -33,8 +33,9 @@ def test_library_exports_every_declared_symbol():
 
 
 def test_struct_layout_matches_header():
-    # 13 pointers, 4 int32, 6 x 3 int64, 2 floats, uint32, 3 int32
-    assert ctypes.sizeof(_lib.KdaFwdArgs) == 13 * 8 + 4 * 4 + 18 * 8 + 6 * 4
+    # 13 pointers, 4 int32, 6 x 3 int64, 2 floats, uint32, 3 int32, 2 pointers, int32 + padding
+    assert ctypes.sizeof(_lib.KdaFwdArgs) == 13 * 8 + 4 * 4 + 18 * 8 + 6 * 4 + 2 * 8 + 8
+    assert _lib.KdaFwdArgs.chunk_table.offset == 13 * 8 + 16 + 18 * 8 + 24
     assert _lib.KdaFwdArgs.q_stride.offset == 13 * 8 + 16
     assert _lib.KdaFwdArgs.scale.offset == 13 * 8 + 16 + 18 * 8
 
@@ -120,3 +121,22 @@ def test_record_index_maps_are_permutations():
     # ldmatrix reads 8 rows at one 16-byte column unit: all eight must hit different units
     units = sw.view(16, 128)[:8, 0] % 128 // 8
     assert len(set(units.tolist())) == 8
+
+
+def test_varlen_tables_host_helper():
+    """kda_varlen_fill_tables is host code: chunk and sequence tables from cu_seqlens."""
+    import ctypes
+    lib = _lib.load()
+    cu = (ctypes.c_int32 * 4)(0, 17, 33, 34)
+    n = lib.kda_varlen_fill_tables(cu, 3, 2, None, None)
+    assert n == 2 + 1 + 1
+    ct = (ctypes.c_int32 * (4 * n))()
+    st = (ctypes.c_int32 * 12)()
+    assert lib.kda_varlen_fill_tables(cu, 3, 2, ct, st) == n
+    # chunk: first token, valid tokens, first record, chunks of its sequence (H = 2 records per chunk)
+    assert list(ct) == [0, 16, 0, 2, 16, 1, 1, 2, 17, 16, 4, 1, 33, 1, 6, 1]
+    # sequence: first token, chunks, first record, length
+    assert list(st) == [0, 2, 0, 17, 17, 1, 4, 16, 33, 1, 6, 1]
+    bad = (ctypes.c_int32 * 3)(0, 5, 5)
+    assert lib.kda_varlen_fill_tables(bad, 2, 2, None, None) == -1
+    assert "empty" in _lib.last_error()
