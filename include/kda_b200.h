@@ -92,6 +92,11 @@ typedef struct KdaFwdArgs {
   const int32_t* chunk_table;  /* [n_chunks][4]: first token, valid tokens, first record, chunks of its sequence */
   const int32_t* seq_table;    /* [n_seqs][4]:   first token, chunks, first record, length */
   int32_t n_chunks;
+  /* Grouped value heads (optional; the reference's kernels carry the index arithmetic,
+   * src/kda_bt16/kernels.py:88, but its API rejects HV != H, :729-730): q and k have Hq heads,
+   * everything else (v, g, beta, A_log, dt_bias, o, states, records) has H heads, H a multiple
+   * of Hq, value head h reads q/k head h / (H / Hq).  0 = Hq equals H. */
+  int32_t Hq;
 } KdaFwdArgs;
 
 /* Bytes of K1 -> K2 scratch for a (B, T, H) problem: a 256-byte status block

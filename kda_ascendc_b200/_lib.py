@@ -33,7 +33,7 @@ class KdaFwdArgs(ctypes.Structure):
         ("scale", ctypes.c_float), ("lower_bound", ctypes.c_float), ("flags", ctypes.c_uint32),
         ("k2_vsplit", ctypes.c_int32), ("k2_variant", ctypes.c_int32),
         ("n_seqs", ctypes.c_int32), ("chunk_table", ctypes.c_void_p), ("seq_table", ctypes.c_void_p),
-        ("n_chunks", ctypes.c_int32),
+        ("n_chunks", ctypes.c_int32), ("Hq", ctypes.c_int32),
     ]
 
 

@@ -118,8 +118,11 @@ def _validate_kda_inputs(q, k, v, g, beta, initial_state, use_gate_in_kernel, sa
 
     if K != HEAD_DIM or V != HEAD_DIM:
         raise ValueError(f"prototype targets K=V=128, got K={K}, V={V}")
-    if HV != H:
-        raise ValueError(f"prototype targets MHA (HV == H), got HV={HV}, H={H}")
+    # the reference rejects HV != H outright (src/kda_bt16/kernels.py:729-730); grouped value heads
+    # (HV a multiple of H, value head h reading q/k head h // (HV // H)) are served here
+    if HV % H != 0:
+        raise ValueError(f"prototype targets MHA (HV == H) or grouped value heads (HV a multiple of H), "
+                         f"got HV={HV}, H={H}")
     if use_gate_in_kernel:
         if not safe_gate:
             raise ValueError("use_gate_in_kernel requires safe_gate=True")
@@ -157,13 +160,15 @@ def _ptr(x: Optional[torch.Tensor]):
 def make_args(q, k, v, g, beta, *, scale, lower_bound, A_log, dt_bias, h0, o, ht, workspace,
               flags, g_out=None, ainv_out=None, k2_vsplit=0, k2_variant=0) -> KdaFwdArgs:
     """Fill the C argument block from (possibly strided) tensors; keeps no references."""
-    B, T, H, _ = q.shape
+    B, T, Hq, _ = q.shape
+    H = v.shape[2]          # heads of v, g, beta, o, states; q and k may have fewer (grouped value heads)
     a = KdaFwdArgs()
     a.q, a.k, a.v, a.g, a.beta = _ptr(q), _ptr(k), _ptr(v), _ptr(g), _ptr(beta)
     a.A_log, a.dt_bias, a.h0 = _ptr(A_log), _ptr(dt_bias), _ptr(h0)
     a.o, a.ht, a.workspace = _ptr(o), _ptr(ht), _ptr(workspace)
     a.g_out, a.ainv_out = _ptr(g_out), _ptr(ainv_out)
     a.B, a.T, a.H = B, T, H
+    a.Hq = 0 if Hq == H else Hq
     a.g_dtype = _lib.KDA_G_BF16 if g.dtype == torch.bfloat16 else _lib.KDA_G_FP32
     a.q_stride, a.k_stride, a.v_stride, a.g_stride = _strides3(q), _strides3(k), _strides3(v), _strides3(g)
     a.o_stride = _strides3(o) if o is not None else (ctypes.c_int64 * 3)(0, 0, 0)
@@ -246,7 +251,8 @@ def _forward(q, k, v, g, beta, scale, initial_state, output_final_state, use_qk_
              cu_seqlens=None):
     """Allocate, launch K1 + K2 on the current stream, return (o, ht[, intermediates])."""
     lib = _lib.load()
-    B, T, H, K = q.shape
+    B, T, _, K = q.shape
+    H = v.shape[2]
     dev = q.device
     h0 = initial_state
     if h0 is not None and not state_v_first:
@@ -318,7 +324,8 @@ def kda_recurrent_fwd(q, k, v, g, beta, scale=None, initial_state=None, output_f
         raise ValueError("inplace_state=True needs an initial_state to update")
     if initial_state is not None and not initial_state.is_contiguous():
         raise ValueError("initial_state must be contiguous")
-    B, T, H, K = q.shape
+    B, T, _, K = q.shape
+    H = v.shape[2]
     if scale is None:
         scale = K ** -0.5
     dev = q.device

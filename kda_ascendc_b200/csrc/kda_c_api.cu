@@ -8,7 +8,7 @@
 #include "kda_common.cuh"
 #include "kda_kernels.h"
 
-static_assert(sizeof(KdaFwdArgs) == 312 && offsetof(KdaFwdArgs, chunk_table) == 288,
+static_assert(sizeof(KdaFwdArgs) == 312 && offsetof(KdaFwdArgs, chunk_table) == 288 && offsetof(KdaFwdArgs, Hq) == 308,
               "KdaFwdArgs layout is part of the ABI (bindings mirror it field by field)");
 
 namespace {
@@ -28,6 +28,8 @@ int check_common(const KdaFwdArgs* a) {
   if (a->workspace == nullptr) return fail(KDA_ERR_INVALID_ARG, "kda: workspace is NULL%s", "");
   if (reinterpret_cast<uintptr_t>(a->workspace) % 256 != 0)
     return fail(KDA_ERR_INVALID_ARG, "kda: workspace must be 256-byte aligned%s", "");
+  if (a->Hq < 0 || (a->Hq > 0 && a->H % a->Hq != 0))
+    return fail(KDA_ERR_INVALID_ARG, "kda: H%s (%lld) must be a multiple of Hq (%lld)", "", a->H, a->Hq);
   if (a->n_seqs < 0) return fail(KDA_ERR_INVALID_ARG, "kda: n_seqs must not be negative%s", "");
   if (a->n_seqs > 0) {
     if (a->B != 1) return fail(KDA_ERR_INVALID_ARG, "kda: packed sequences need B = 1%s (got %lld)", "", a->B);
@@ -135,6 +137,8 @@ int do_k1(const KdaFwdArgs* a, cudaStream_t st) {
     p.chunk_table = reinterpret_cast<const int4*>(a->chunk_table);
     p.n_chunks = a->n_chunks;
   }
+  p.Hq = a->Hq > 0 ? a->Hq : a->H;
+  p.div_g.set(static_cast<uint32_t>(p.H / p.Hq));
   // 2^g may be factored as 2^(g-g_mid) * 2^(g_mid) only while no factor can underflow:
   // 16 tokens * |lower_bound| * RCP_LN2 must stay inside the fp32 exponent range.
   const bool fast_exp = (a->flags & KDA_FLAG_GATE_IN_KERNEL) && (16.0f * -a->lower_bound * kda::RCP_LN2 <= 120.0f);
@@ -226,6 +230,8 @@ int kda_recurrent_fwd(const KdaFwdArgs* a, void* stream) {
   if (a->B <= 0 || a->T <= 0 || a->H <= 0)
     return fail(KDA_ERR_INVALID_ARG, "kda: B, T, H must be positive%s (T=%lld, H=%lld)", "", a->T, a->H);
   if (a->n_seqs != 0) return fail(KDA_ERR_INVALID_ARG, "kda: the recurrent step takes a fixed-length batch%s (n_seqs must be 0)", "");
+  if (a->Hq < 0 || (a->Hq > 0 && a->H % a->Hq != 0))
+    return fail(KDA_ERR_INVALID_ARG, "kda: H%s (%lld) must be a multiple of Hq (%lld)", "", a->H, a->Hq);
   if (!a->q || !a->k || !a->v || !a->g || !a->beta || !a->o || !a->A_log)
     return fail(KDA_ERR_INVALID_ARG, "kda: the recurrent step needs q, k, v, g, beta, A_log and o%s", "");
   const uint32_t all = KDA_FLAG_GATE_IN_KERNEL | KDA_FLAG_QK_L2NORM | KDA_FLAG_BETA_SIGMOID;
@@ -249,6 +255,7 @@ int kda_recurrent_fwd(const KdaFwdArgs* a, void* stream) {
   p.g = a->g; p.beta = a->beta; p.A_log = a->A_log; p.dt_bias = a->dt_bias;
   p.h0 = a->h0; p.ht = a->ht; p.o = static_cast<__nv_bfloat16*>(a->o);
   p.B = a->B; p.T = a->T; p.H = a->H;
+  p.group = a->Hq > 0 ? a->H / a->Hq : 1;
   for (int i = 0; i < 3; ++i) {
     p.q_s[i] = a->q_stride[i]; p.k_s[i] = a->k_stride[i]; p.v_s[i] = a->v_stride[i];
     p.g_s[i] = a->g_stride[i]; p.beta_s[i] = a->beta_stride[i]; p.o_s[i] = a->o_stride[i];

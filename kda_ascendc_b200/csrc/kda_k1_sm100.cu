@@ -65,7 +65,7 @@ struct K1Smem {
 #endif
 
 struct K1Item {   // one (batch, head, chunk) work item
-  int b, h, t0, nvalid;
+  int b, h, hq, t0, nvalid;   // hq: the q/k head this (value) head reads
   size_t rec_idx;
 };
 
@@ -74,6 +74,7 @@ __device__ __forceinline__ K1Item k1_item(const K1Params& p, int id) {
   K1Item w;
   const int bn = static_cast<int>(p.div_h.div(id));
   w.h = id - bn * p.H;
+  w.hq = static_cast<int>(p.div_g.div(w.h));
   if (p.chunk_table != nullptr) {   // packed sequences: the chunk's place comes from the table
     const int4 e = __ldg(p.chunk_table + bn);
     w.b = 0;
@@ -130,8 +131,8 @@ __global__ void __launch_bounds__(128, 4) kda_k1_kernel(const __grid_constant__ 
   auto issue_loads = [&](const K1Item& w) {
     if (tid == 0) {
       mbar_arrive_expect_tx(mbar, BT * (3 * ROW_BYTES + G_ROW_BYTES));
-      tma_load_4d(sbase + S_Q, &p.tm_q, 0, w.h, w.t0, w.b, mbar);
-      tma_load_4d(sbase + S_K, &p.tm_k, 0, w.h, w.t0, w.b, mbar);
+      tma_load_4d(sbase + S_Q, &p.tm_q, 0, w.hq, w.t0, w.b, mbar);
+      tma_load_4d(sbase + S_K, &p.tm_k, 0, w.hq, w.t0, w.b, mbar);
       tma_load_4d(sbase + S_V, &p.tm_v, 0, w.h, w.t0, w.b, mbar);
       tma_load_4d(sbase + S_G, &p.tm_g, 0, w.h, w.t0, w.b, mbar);
     }
@@ -589,8 +590,9 @@ cudaError_t k1_encode_tensor_maps(K1Params& p, bool g_bf16, const char** what) {
   for (const T& t : ts) {
     // dims innermost first: (d, head, token, batch); strides in bytes for dims 1..3.  A size-1
     // dimension may come with any stride: give it a legal one (it is never stepped).
-    const cuuint64_t dims[4] = {static_cast<cuuint64_t>(D), static_cast<cuuint64_t>(p.H), static_cast<cuuint64_t>(p.T),
-                                static_cast<cuuint64_t>(p.B)};
+    const bool qk = (t.m == &p.tm_q || t.m == &p.tm_k);
+    const cuuint64_t dims[4] = {static_cast<cuuint64_t>(D), static_cast<cuuint64_t>(qk ? p.Hq : p.H),
+                                static_cast<cuuint64_t>(p.T), static_cast<cuuint64_t>(p.B)};
     cuuint64_t strides[3] = {static_cast<cuuint64_t>(t.s[2]) * t.es, static_cast<cuuint64_t>(t.s[1]) * t.es,
                              static_cast<cuuint64_t>(t.s[0]) * t.es};
     for (int i = 0; i < 3; ++i)

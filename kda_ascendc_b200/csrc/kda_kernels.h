@@ -46,6 +46,9 @@ struct K1Params {
   // chunks of its sequence), B == 1; null for a fixed-length batch
   const int4* chunk_table;
   int n_chunks;
+  // grouped value heads: q and k have Hq heads, head h of everything else reads q/k head h / (H/Hq)
+  int Hq;
+  FastDiv div_g;   // divides by H / Hq
 };
 
 struct K2Params {
@@ -85,6 +88,7 @@ struct RecurrentParams {
   float* ht;                // may be null
   __nv_bfloat16* o;
   int B, T, H;
+  int group;                // value heads per q/k head (1 = plain multi-head)
   int64_t q_s[3], k_s[3], v_s[3], g_s[3], beta_s[3], o_s[3];
   float scale, lower_bound;
 };

@@ -52,8 +52,9 @@ __global__ void __launch_bounds__(REC_WARPS * 32) kda_recurrent_kernel(const Rec
   if (p.dt_bias != nullptr) bias = *reinterpret_cast<const float4*>(p.dt_bias + h * D + k0);
   const float lbr = p.lower_bound * RCP_LN2;
 
-  const __nv_bfloat16* qp = p.q + b * p.q_s[0] + h * p.q_s[2] + k0;
-  const __nv_bfloat16* kp = p.k + b * p.k_s[0] + h * p.k_s[2] + k0;
+  const int hq = h / p.group;   // grouped value heads share a q/k head
+  const __nv_bfloat16* qp = p.q + b * p.q_s[0] + hq * p.q_s[2] + k0;
+  const __nv_bfloat16* kp = p.k + b * p.k_s[0] + hq * p.k_s[2] + k0;
   const __nv_bfloat16* vp = p.v + b * p.v_s[0] + h * p.v_s[2] + v0 + (lane % ROWS);
   const uint8_t* gp = static_cast<const uint8_t*>(p.g) + (b * p.g_s[0] + h * p.g_s[2] + k0) * (G_BF16 ? 2 : 4);
   const float* bp = p.beta + b * p.beta_s[0] + h * p.beta_s[2];

@@ -7,7 +7,7 @@ docs/KDA_ANALYSIS.md:215-229).
 Two layers:
 
 * ``chunk_kda`` / ``fused_recurrent_kda`` here take FLA's keyword set and run the B200 kernels.
-  They serve exactly one configuration -- inference (no autograd), bf16, K = V = 128, HV == H,
+  They serve exactly one configuration -- inference (no autograd), bf16, K = V = 128, HV a multiple of H,
   gate + l2-norm (+ beta sigmoid) fused in the kernel, ``safe_gate`` with a ``lower_bound`` -- and
   raise ``NotImplementedError`` with the reason for anything else.  There is no fallback.
 * ``register()`` adds a backend object to FLA's per-operation registry when FLA is importable, so
@@ -45,8 +45,8 @@ def supports(q, k, v, g, beta, *, use_qk_l2norm_in_kernel=False, use_gate_in_ker
         return False, "q, k, v must be bf16 CUDA tensors"
     if q.ndim != 4 or q.shape[-1] != 128 or v.shape[-1] != 128:
         return False, "K = V = 128 only"
-    if v.shape[2] != q.shape[2]:
-        return False, "grouped value heads (HV != H) are not supported"
+    if v.shape[2] % q.shape[2] != 0:
+        return False, "the value heads must be a multiple of the q/k heads"
     if not (use_qk_l2norm_in_kernel and use_gate_in_kernel):
         return False, "the l2-norm and the gate must be fused in the kernel"
     if not (safe_gate and lower_bound is not None and -11.0 < lower_bound < 0.0):

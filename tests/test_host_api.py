@@ -36,6 +36,7 @@ def test_struct_layout_matches_header():
     # 13 pointers, 4 int32, 6 x 3 int64, 2 floats, uint32, 3 int32, 2 pointers, int32 + padding
     assert ctypes.sizeof(_lib.KdaFwdArgs) == 13 * 8 + 4 * 4 + 18 * 8 + 6 * 4 + 2 * 8 + 8
     assert _lib.KdaFwdArgs.chunk_table.offset == 13 * 8 + 16 + 18 * 8 + 24
+    assert _lib.KdaFwdArgs.Hq.offset == ctypes.sizeof(_lib.KdaFwdArgs) - 4
     assert _lib.KdaFwdArgs.q_stride.offset == 13 * 8 + 16
     assert _lib.KdaFwdArgs.scale.offset == 13 * 8 + 16 + 18 * 8
 
