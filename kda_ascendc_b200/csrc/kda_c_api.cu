@@ -70,7 +70,10 @@ int check_k2(const KdaFwdArgs* a, bool state_only) {
   if (int rc = check_common(a)) return rc;
   if (!state_only && a->o == nullptr) return fail(KDA_ERR_INVALID_ARG, "kda: o is NULL%s", "");
   const int vs = a->k2_vsplit, var = a->k2_variant;
-  if (var < 0 || var > 3) return fail(KDA_ERR_INVALID_ARG, "kda: k2_variant must be 0..3%s (got %lld)", "", var);
+  if (var < 0 || var > 4) return fail(KDA_ERR_INVALID_ARG, "kda: k2_variant must be 0..4%s (got %lld)", "", var);
+  if (var == 4 && state_only)
+    return fail(KDA_ERR_INVALID_ARG, "kda: the tensor-memory K2 (k2_variant 4) has no state-only form%s", "");
+  if (var == 4) return KDA_OK;
   if (vs != 0 && vs != 2 && vs != 4 && vs != 8 && vs != 16)
     return fail(KDA_ERR_INVALID_ARG, "kda: k2_vsplit must be 0, 2, 4, 8 or 16%s (got %lld)", "", vs);
   if (vs != 0 && var != 0 && ((var == 1) ? (vs < 4) : (vs > 8)))
@@ -169,8 +172,14 @@ int do_k2(const KdaFwdArgs* a, bool state_only, int zero_u, cudaStream_t st) {
   }
   int vsplit = 4, variant = 3;
   pick_split(a, &vsplit, &variant);
-  cudaError_t e = (variant == 3) ? kda::launch_k2m(p, vsplit, state_only, st)
-                                 : kda::launch_k2n(p, vsplit, variant, state_only, st);
+  cudaError_t e;
+  if (variant == 4) {
+    const long long n_records = a->n_seqs > 0 ? static_cast<long long>(a->n_chunks) * a->H
+                                              : static_cast<long long>(a->B) * a->H * p.NT;
+    e = kda::launch_k2t(p, n_records, st);
+  } else {
+    e = (variant == 3) ? kda::launch_k2m(p, vsplit, state_only, st) : kda::launch_k2n(p, vsplit, variant, state_only, st);
+  }
   if (e != cudaSuccess) return fail(KDA_ERR_CUDA, "kda: K2 launch failed: %s", cudaGetErrorString(e));
   ++g_launches;
   return KDA_OK;

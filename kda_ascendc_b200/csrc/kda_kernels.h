@@ -78,6 +78,9 @@ cudaError_t k1_encode_tensor_maps(K1Params& p, bool g_bf16, const char** what);
 // vsplit = CTAs per (batch, head).
 cudaError_t launch_k2n(const K2Params& p, int vsplit, int ntile, bool state_only, cudaStream_t stream);
 cudaError_t launch_k2m(const K2Params& p, int vsplit, bool state_only, cudaStream_t stream);
+//   "tc":       the whole 128-row state of a head in tensor memory, tcgen05 MMAs, one CTA per
+//               (batch, head), two CTAs per SM; outputs + final state only              (kda_k2t_sm100.cu)
+cudaError_t launch_k2t(const K2Params& p, long long n_records, cudaStream_t stream);
 
 // Token recurrence (decode / short sequences): no chunking, no workspace (kda_recurrent_sm100.cu).
 struct RecurrentParams {
