@@ -449,7 +449,15 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference", "reference_gpu"])
     ap.add_argument("--kernels-only", action="store_true",
                     help="skip the e2e and CPU-baseline legs (short run for profiler captures)")
+    ap.add_argument("--shape", default=None,
+                    help="B,T,H of another workload for --kernels-only runs (profiler captures of other regimes); "
+                         "the default and every reported line use the headline shape")
     a = ap.parse_args()
+    if a.shape is not None:
+        if not a.kernels_only:
+            ap.error("--shape goes with --kernels-only")
+        global B, T, H
+        B, T, H = (int(x) for x in a.shape.split(","))
     if a.impl == "reference":
         run_reference_arm(a.steps, a.warmup, a.gpus)
     elif a.impl == "reference_gpu":
