@@ -69,6 +69,11 @@ int check_k1(const KdaFwdArgs* a) {
 int check_k2(const KdaFwdArgs* a, bool state_only) {
   if (int rc = check_common(a)) return rc;
   if (!state_only && a->o == nullptr) return fail(KDA_ERR_INVALID_ARG, "kda: o is NULL%s", "");
+  if (!state_only && !row_aligned(a->o, a->o_stride, 2))
+    return fail(KDA_ERR_INVALID_ARG, "kda: o rows must start on 16-byte boundaries%s", "");
+  for (const void* ptr : {static_cast<const void*>(a->h0), static_cast<const void*>(a->ht)})
+    if (ptr != nullptr && reinterpret_cast<uintptr_t>(ptr) % 16 != 0)
+      return fail(KDA_ERR_INVALID_ARG, "kda: h0 and ht must be 16-byte aligned%s", "");
   const int vs = a->k2_vsplit, var = a->k2_variant;
   if (var < 0 || var > 4) return fail(KDA_ERR_INVALID_ARG, "kda: k2_variant must be 0..4%s (got %lld)", "", var);
   if (var == 4 && state_only)
