@@ -48,8 +48,8 @@ struct K1Smem {
   static constexpr int G_BYTES = G_BF16 ? 4096 : 8192;
   static constexpr int SMALL = G + G_BYTES;
   static constexpr int BETA = SMALL;          // fp32 [2][16] activated beta + [2] exp(A_log): this item / next item
-  static constexpr int TOT = BETA + 144;      // fp32 [128]: column sums of rows 0..7, then g[last]
-  static constexpr int GMID = TOT + 512;      // fp32 [128] g[mid] (not needed with FAST_EXP)
+  static constexpr int TOT = BETA + 144;      // fp32 [2][128]: column sums of the gate over rows 0..7 and rows 8..15
+  static constexpr int GMID = TOT + 1024;     // fp32 [128] g[mid] (not needed with FAST_EXP)
   static constexpr int MBAR = GMID + (FAST_EXP ? 0 : 512);
   static constexpr int FLAG = MBAR + 8;
   static constexpr int TOTAL = FLAG + 8;
@@ -110,7 +110,7 @@ __global__ void __launch_bounds__(128, 4) kda_k1_kernel(const __grid_constant__ 
   float* sBetaAll = reinterpret_cast<float*>(smem + SM::BETA);   // [2][16], then expA[2] at +32
   float* sTot = reinterpret_cast<float*>(smem + SM::TOT);
   float* sGmid = reinterpret_cast<float*>(smem + SM::GMID);
-  float* sGlast = sTot;   // the thread that reads sTot[c] is the one that then writes g[last] there
+  float* sTot1 = sTot + D;
   volatile int* sFlag = reinterpret_cast<volatile int*>(smem + SM::FLAG);
 
   const bool use_gate = (p.flags & 1u) != 0;
@@ -187,24 +187,15 @@ __global__ void __launch_bounds__(128, 4) kda_k1_kernel(const __grid_constant__ 
     const float* sBeta = sBetaAll + (it & 1) * 16;
 
     K1_STAMP(8)
-    bool ok = true;
-    if (lane == 0) ok = mbar_wait_bounded(mbar, it & 1, sFlag);
+    // every thread waits for the input copies itself (no CTA barrier here); a thread whose wait runs
+    // out raises the flag, and the whole CTA leaves together behind the barrier that ends phase A
+    const bool ok = mbar_wait_bounded(mbar, it & 1, sFlag);
     K1_STAMP(9)
     if (!ok) *sFlag = 1;
-    __syncthreads();
-    if (*sFlag != 0) {
-      // a copy never completed: report, give in-flight copies one more bounded wait, leave
-      if (tid == 0) {
-        atomicExch(p.status, ST_K1_LOAD_TIMEOUT);
-        mbar_wait_bounded(mbar, it & 1, nullptr);
-      }
-      __syncthreads();
-      return;
-    }
     K1_STAMP(1)
 
     // ---- phase A: l2-normalise q and k in place (8 threads per row, 16 elements each) ----
-    if (use_l2) {
+    if (use_l2 && ok) {
       const int r = tid >> 3, seg = tid & 7;
       uint4 qa[2], ka[2];
       float sq = 0.f, sk = 0.f;
@@ -241,6 +232,15 @@ __global__ void __launch_bounds__(128, 4) kda_k1_kernel(const __grid_constant__ 
       }
     }
     __syncthreads();
+    if (*sFlag != 0) {
+      // a copy never completed: report, give in-flight copies one more bounded wait, leave
+      if (tid == 0) {
+        atomicExch(p.status, ST_K1_LOAD_TIMEOUT);
+        mbar_wait_bounded(mbar, it & 1, nullptr);
+      }
+      __syncthreads();
+      return;
+    }
     K1_STAMP(2)
 
     // ---- phase B: thread = (column pair, row half): gate, cumsum, gated operands ----
@@ -283,23 +283,27 @@ __global__ void __launch_bounds__(128, 4) kda_k1_kernel(const __grid_constant__ 
           gv[i] = run;
           if (r == mid) gm = run;
         }
-        // rows 8..15 need the sum over rows 0..7, all rows need g[centre]
-        if (rh == 0) *reinterpret_cast<float2*>(sTot + c0) = run;
+        // rows 8..15 need the sum over rows 0..7, all rows need g[last] and g[centre]: both halves
+        // publish their column sums (and the half that owns the centre row its running sum there),
+        // one barrier, and every thread completes its own values
+        *reinterpret_cast<float2*>((rh == 0 ? sTot : sTot1) + c0) = run;
+        if (!FAST_EXP && rh == (mid >> 3)) *reinterpret_cast<float2*>(sGmid + c0) = gm;
         // the previous item's bulk stores must have read the qg / kg / Aqk / dec tiles before the
         // operand loop below rewrites them; by now they have had two phases to do so
         if (tid == 0) bulk_wait_read_all();
         __syncthreads();
+        const float2 t0 = *reinterpret_cast<const float2*>(sTot + c0);
+        const float2 t1 = *reinterpret_cast<const float2*>(sTot1 + c0);
         if (rh == 1) {
-          const float2 t = *reinterpret_cast<const float2*>(sTot + c0);
 #pragma unroll
-          for (int i = 0; i < 8; ++i) gv[i] = __fadd2_rn(gv[i], t);
-          gm = __fadd2_rn(gm, t);
-          *reinterpret_cast<float2*>(sGlast + c0) = gv[7];
+          for (int i = 0; i < 8; ++i) gv[i] = __fadd2_rn(gv[i], t0);
         }
-        if (!FAST_EXP && rh == (mid >> 3)) *reinterpret_cast<float2*>(sGmid + c0) = gm;
-        __syncthreads();
-        gmid = FAST_EXP ? make_float2(0.f, 0.f) : *reinterpret_cast<const float2*>(sGmid + c0);
-        glast = *reinterpret_cast<const float2*>(sGlast + c0);
+        glast = __fadd2_rn(t1, t0);
+        gmid = make_float2(0.f, 0.f);
+        if (!FAST_EXP) {
+          gmid = *reinterpret_cast<const float2*>(sGmid + c0);
+          if ((mid >> 3) == 1) gmid = __fadd2_rn(gmid, t0);
+        }
       } else {
         // g already holds the chunk-local log2 cumsum; rows past the end repeat the last valid row
 #pragma unroll
