@@ -54,7 +54,7 @@ K1_FLOPS_PER_CHUNK = 262144.0
 K2_FLOPS_PER_CHUNK = 1638400.0
 # dram__bytes_read.sum + dram__bytes_write.sum of ONE launch on this workload, from the ncu
 # capture summarised in profiles/kda_k1_k2_B1_T8192_H32.md (bytes per launch)
-NCU_TRAFFIC_BYTES = {"kda_k1": 642.42e6, "kda_k2": 489.06e6}
+NCU_TRAFFIC_BYTES = {"kda_k1": 641.80e6, "kda_k2": 488.68e6}
 
 
 def load_peaks():
