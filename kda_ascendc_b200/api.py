@@ -342,6 +342,44 @@ def kda_recurrent_fwd(q, k, v, g, beta, scale=None, initial_state=None, output_f
     return o, ht
 
 
+class RecurrentPlan:
+    """Decode loop without per-step host work: fixed input buffers, in-place state, one C call per step.
+
+    A serving loop writes each new token's ``q, k, v, g, beta`` into the SAME tensors and calls
+    :meth:`step`; validation, output allocation and the argument block are done once here.  ``o``
+    is reused by every step (copy it if it must outlive the next one); ``state`` is updated in
+    place.  Same arithmetic and checks as :func:`kda_recurrent_fwd`.
+    """
+
+    def __init__(self, q, k, v, g, beta, state, *, scale=None, lower_bound=-5.0, A_log=None, dt_bias=None):
+        _validate_kda_inputs(q, k, v, g, beta, state, True, True, lower_bound, A_log, dt_bias, True,
+                             require_contiguous=False)
+        _require_cuda(q)
+        if state is None:
+            raise ValueError("RecurrentPlan needs the state tensor it updates in place")
+        B, T, _, K = q.shape
+        self.device = q.device
+        self.o = torch.empty((B, T, v.shape[2], HEAD_DIM), dtype=torch.bfloat16, device=q.device)
+        self.state = state
+        self._keep = (q, k, v, g, beta, A_log, dt_bias)   # the argument block holds raw pointers
+        self._args = make_args(q, k, v, g, beta, scale=K ** -0.5 if scale is None else scale, lower_bound=lower_bound,
+                               A_log=A_log, dt_bias=dt_bias, h0=state, o=self.o, ht=state, workspace=None,
+                               flags=_flags(True, True, True))
+        self._ref = ctypes.byref(self._args)
+        self._fn = _lib.load().kda_recurrent_fwd
+
+    def step(self, stream: Optional[int] = None):
+        """Apply the tokens currently in the input buffers; returns ``o`` (the plan's own tensor).
+        ``stream``: raw CUDA stream handle; default = the current torch stream of the plan's device."""
+        if stream is None:
+            stream = torch.cuda.current_stream(self.device).cuda_stream
+        rc = self._fn(self._ref, ctypes.c_void_p(stream))
+        if rc != 0:
+            _check(rc)
+        _LAUNCH_COUNTS["kda_recurrent"] += 1
+        return self.o
+
+
 # ---------------------------------------------------------------------------
 # public API, reference signature 1: src/kda_bt16/kernels.py:752-850
 # ---------------------------------------------------------------------------

@@ -153,9 +153,34 @@ int do_k1(const KdaFwdArgs* a, cudaStream_t st) {
   // 2^g may be factored as 2^(g-g_mid) * 2^(g_mid) only while no factor can underflow:
   // 16 tokens * |lower_bound| * RCP_LN2 must stay inside the fp32 exponent range.
   const bool fast_exp = (a->flags & KDA_FLAG_GATE_IN_KERNEL) && (16.0f * -a->lower_bound * kda::RCP_LN2 <= 120.0f);
-  const char* what = "";
-  cudaError_t e = kda::k1_encode_tensor_maps(p, a->g_dtype == KDA_G_BF16, &what);
-  if (e != cudaSuccess) return fail(KDA_ERR_CUDA, "kda: building the TMA descriptor failed for: %s", what);
+  // The four tensor maps depend only on the input pointers, sizes and strides: a loop that calls with
+  // the same buffers (a serving loop, a benchmark) re-uses the maps of its previous call.
+  struct MapKey {
+    const void *q, *k, *v, *g;
+    int32_t B, T, H, Hq, g_dtype;
+    int64_t s[12];
+  };
+  thread_local MapKey last_key;
+  thread_local CUtensorMap last_maps[4];
+  thread_local bool have_maps = false;
+  MapKey key;
+  memset(&key, 0, sizeof(key));
+  key.q = a->q; key.k = a->k; key.v = a->v; key.g = a->g;
+  key.B = a->B; key.T = a->T; key.H = a->H; key.Hq = p.Hq; key.g_dtype = a->g_dtype;
+  for (int i = 0; i < 3; ++i) {
+    key.s[i] = a->q_stride[i]; key.s[3 + i] = a->k_stride[i]; key.s[6 + i] = a->v_stride[i]; key.s[9 + i] = a->g_stride[i];
+  }
+  cudaError_t e = cudaSuccess;
+  if (have_maps && memcmp(&key, &last_key, sizeof(key)) == 0) {
+    p.tm_q = last_maps[0]; p.tm_k = last_maps[1]; p.tm_v = last_maps[2]; p.tm_g = last_maps[3];
+  } else {
+    const char* what = "";
+    e = kda::k1_encode_tensor_maps(p, a->g_dtype == KDA_G_BF16, &what);
+    if (e != cudaSuccess) return fail(KDA_ERR_CUDA, "kda: building the TMA descriptor failed for: %s", what);
+    last_key = key;
+    last_maps[0] = p.tm_q; last_maps[1] = p.tm_k; last_maps[2] = p.tm_v; last_maps[3] = p.tm_g;
+    have_maps = true;
+  }
   e = kda::launch_k1(p, a->g_dtype == KDA_G_BF16, fast_exp, st);
   if (e != cudaSuccess) return fail(KDA_ERR_CUDA, "kda: K1 launch failed: %s", cudaGetErrorString(e));
   ++g_launches;

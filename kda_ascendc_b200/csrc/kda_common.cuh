@@ -195,7 +195,7 @@ __device__ __forceinline__ void mma_bf16(float (&d)[4], const uint32_t (&a)[4], 
 }
 
 // same instruction, but pinned in program order (used where independent loads and stores are
-// deliberately interleaved with a long MMA sequence to fill the tensor pipe's issue gaps)
+// deliberately interleaved with a long MMA sequence so that their latency is covered)
 __device__ __forceinline__ void mma_bf16_v(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
   asm volatile(
       "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"

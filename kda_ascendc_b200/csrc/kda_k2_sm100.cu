@@ -24,11 +24,13 @@
 // with v_new and Aqk (the intra-chunk term dominates o); P1 uses plain bf16 operands.
 // The result does not depend on how the rows are distributed over warps and CTAs.
 //
-// One warp executes its chain in program order, so everything that is not on the chain is
-// placed in the issue gaps of the two long MMA sequences (~6 free issue slots between
-// consecutive MMAs): P1 carries this step's kg fragment loads and the decay of hT; P2
-// carries the next step's [w;qg] / decay / u loads; the previous step's output tile is
-// stored at the start of the next step.
+// One warp executes its chain in program order.  Measured on B200: an mma.sync holds the
+// sub-partition's issue port for its 8 cycles (neither this warp nor another one on the same
+// sub-partition issues meanwhile), so a step costs about 8 cycles per MMA plus 2 per other
+// instruction and what matters is the instruction count.  Loads are still interleaved with the
+// MMA sequences so that their latency is covered: P1 carries this step's kg fragment loads and
+// the decay of hT; P2 carries the next step's [w;qg] / decay / u loads; the previous step's output
+// tile is stored at the start of the next step.
 //
 // A CTA = CW consumer warps (CW*NVT*8 state rows of one (batch, head)) plus one producer warp
 // that streams the chunk records through a ring of shared-memory stages with bulk (TMA)

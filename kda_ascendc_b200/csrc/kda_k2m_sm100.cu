@@ -10,12 +10,13 @@
 // so bf16(h) and v_new feed the next product by a register pack alone.  The shared operands
 // (w, qg, kg, Aqk) are the B side here: a B fragment is half the size of an A fragment, so this
 // organisation reads half as many shared-memory bytes per MMA as the "n8" one, at the price of
-// a chain twice as long per warp (86 MMAs per step).  It is the better choice when a GPU has
-// few heads to work on: two warps per SM keep the shared-memory pipe far from saturation and
-// each warp has a tensor pipe to itself.
+// a chain twice as long per warp (86 MMAs per step).  Per state row it needs fewer instructions
+// (no transposes, operand loads shared by 16 rows), which makes it the better choice once
+// there are more 8-row tiles than SM sub-partitions (more than about 37 (batch, head) chains).
 //
-// Everything that is not on the chain rides in the issue gaps of the MMA sequences
-// (one m16n8k16 per 8 cycles per sub-partition): P1 carries its own rolling B-fragment loads,
+// Loads are interleaved with the MMA sequences so that their latency is covered (an m16n8k16
+// holds the sub-partition's issue port for 8 cycles; the step time is 8 x MMAs + 2 x the other
+// instructions): P1 carries its own rolling B-fragment loads,
 // the decay row and the kg(hi) fragments; P2's first two passes carry kg(lo), its last pass the
 // next step's first fragments; the output tile is transposed in-warp (movmatrix) and stored one
 // step late.  Producer warp, stage ring, bounded waits: as in kda_k2_sm100.cu.

@@ -103,3 +103,27 @@ def test_recurrent_argument_errors():
         K.kda_recurrent_fwd(d["q"], d["k"], d["v"], d["g"], d["beta"], initial_state=None, inplace_state=True, **_kw(d))
     with pytest.raises((ValueError, TypeError)):
         K.kda_recurrent_fwd(d["q"], d["k"], d["v"], d["g"], d["beta"], scale=d["scale"], A_log=None, dt_bias=d["dt_bias"])
+
+
+def test_recurrent_plan_matches_stepwise_calls():
+    import kda_ascendc_b200 as K
+    B, H, n_tok = 3, 4, 6
+    inp = O.make_inputs(B, n_tok, H, seed0=8, h0_std=0.2)
+    d = _dev(inp)
+    # reference: one call per token
+    state = d["initial_state"].clone()
+    outs = []
+    for t in range(n_tok):
+        o_t, state = K.kda_recurrent_fwd(*(d[n][:, t:t + 1] for n in ("q", "k", "v", "g", "beta")), initial_state=state,
+                                         inplace_state=True, **_kw(d))
+        outs.append(o_t.clone())
+    # plan: fixed one-token buffers refilled in place
+    buf = {n: d[n][:, :1].clone() for n in ("q", "k", "v", "g", "beta")}
+    st2 = d["initial_state"].clone()
+    plan = K.RecurrentPlan(buf["q"], buf["k"], buf["v"], buf["g"], buf["beta"], st2, **_kw(d))
+    for t in range(n_tok):
+        for n in buf:
+            buf[n].copy_(d[n][:, t:t + 1])
+        o_t = plan.step()
+        assert torch.equal(o_t, outs[t])
+    assert torch.equal(st2, state) and plan.state is st2
