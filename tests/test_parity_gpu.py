@@ -268,3 +268,35 @@ def test_strided_head_view_needs_no_copy(cuda_device):
     o, ht = api._forward(q, k, v, g, beta, d["scale"], d["initial_state"][:, sl].contiguous(), True, True, True, True,
                          d["lower_bound"], d["A_log"][sl].contiguous(), d["dt_bias"].view(4, 128)[sl].contiguous().view(-1), True)
     assert torch.equal(o, o_full[:, :, sl]) and torch.equal(ht, h_full[:, sl])
+
+
+def test_two_streams_with_their_own_workspaces_do_not_interfere():
+    """The library keeps no per-call global state: forwards issued alternately on two streams (each
+    call allocates its own scratch) give the results of running them one after the other."""
+    import kda_ascendc_b200 as K
+    dev = torch.device("cuda", 0)
+    problems = []
+    for seed, (B, T, H) in enumerate([(1, 2048, 8), (2, 777, 5)]):
+        inp = O.make_inputs(B, T, H, seed0=100 + seed, h0_std=0.05)
+        problems.append({k: (v.to(dev) if torch.is_tensor(v) else v) for k, v in inp.items()})
+
+    def fwd(d):
+        return K.kda_bt16_fwd(d["q"], d["k"], d["v"], d["g"], d["beta"], scale=d["scale"], initial_state=d["initial_state"],
+                              output_final_state=True, use_qk_l2norm_in_kernel=True, use_gate_in_kernel=True,
+                              use_beta_sigmoid_in_kernel=True, lower_bound=d["lower_bound"], A_log=d["A_log"],
+                              dt_bias=d["dt_bias"])
+
+    ref = [fwd(d) for d in problems]
+    torch.cuda.synchronize()
+    streams = [torch.cuda.Stream(device=dev) for _ in problems]
+    for s_ in streams:
+        s_.wait_stream(torch.cuda.current_stream(dev))
+    outs = [[], []]
+    for rep in range(6):
+        for i, d in enumerate(problems):
+            with torch.cuda.stream(streams[i]):
+                outs[i].append(fwd(d))
+    torch.cuda.synchronize()
+    for i in range(2):
+        for o, ht in outs[i]:
+            assert torch.equal(o, ref[i][0]) and torch.equal(ht, ref[i][1])
