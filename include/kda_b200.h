@@ -135,6 +135,13 @@ int kda_recurrent_fwd(const KdaFwdArgs* args, void* stream);
 int kda_varlen_fill_tables(const int32_t* cu_seqlens, int32_t n_seqs, int32_t H, int32_t* chunk_table,
                            int32_t* seq_table);
 
+/* Self-test of the failure path (no reference counterpart): launches a one-warp kernel that waits,
+ * with the same bounded wait every kernel of the library uses, on a barrier nothing arrives on.  The
+ * wait gives up after its limit (one second), the kernel writes status code 100 into the status word
+ * at the start of `workspace` (at least 256 bytes of device memory) and returns normally;
+ * kda_fwd_status then reports KDA_ERR_DEVICE_STATUS, and the GPU context stays usable. */
+int kda_selftest_bounded_wait(void* workspace, void* stream);
+
 /* Whole forward with the K1 -> K2 scratch taken from a fixed array inside the library instead
  * of args->workspace (which is ignored).  It has no counterpart in the reference, whose host
  * code always allocates its intermediates itself.  It exists for callers that cannot obtain
