@@ -2,7 +2,8 @@
 
 Drop-in for the forward path of the reference project: ``kda_bt16_fwd`` /
 ``kda_bt16_debug`` (its Triton package) and ``kda_bt16_fwd_ascendc`` (its second
-backend).  The device code is two hand-written sm_100a CUDA kernels behind a C ABI
+backend).  The device code is hand-written sm_100a CUDA (K1, three organisations of K2, a
+token-recurrence step) behind a C ABI
 (``include/kda_b200.h``); there is no other backend and no CPU fallback.
 """
 from .api import (CHUNK, PERSISTENT_LOOP, RecurrentPlan, get_last_profile, kda_bt16_debug, kda_bt16_fwd,
