@@ -99,3 +99,16 @@ def test_config4_b1_t131072_h16_sequence_split(cuda_device):
     omax, hmax = o.float().abs().max().item(), ht.abs().max().item()
     assert (o8.float() - o.float()).abs().max().item() <= 1e-2 * omax
     assert (h8 - ht).abs().max().item() <= 1e-2 * hmax
+
+
+def test_many_chains_b8_t2048_h32_tensor_memory_k2(cuda_device):
+    """256 (batch, head) chains: more chains than SMs, so K2 runs in its tcgen05 form (two CTAs per
+    SM).  Same size-independent properties; the oracle walks four heads of one batch entry."""
+    d = _inputs(cuda_device, 8, 2048, 32, seed=105, h0_std=0.02)
+    o, ht = _check_properties(d, [0, 9, 22, 31], 512)
+    # the 16-row mma.sync organisation on the same records agrees to rounding
+    from kda_ascendc_b200 import api
+    o_m, ht_m = api._forward(d["q"], d["k"], d["v"], d["g"], d["beta"], d["scale"], d["initial_state"], True, True, True,
+                             True, d["lower_bound"], d["A_log"], d["dt_bias"], True, k2_variant=3)
+    assert (o.float() - o_m.float()).abs().max().item() <= 5e-3 * o.float().abs().max().item()
+    assert (ht - ht_m).abs().max().item() <= 1e-4
