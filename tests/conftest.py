@@ -16,6 +16,14 @@ def pytest_configure(config):
     config.addinivalue_line("markers", "gpu: needs a CUDA device (run with -m gpu on a B200)")
 
 
+@pytest.fixture(scope="session", autouse=True)
+def _library_is_built():
+    """Build libkda_b200.so once if a fresh checkout has none (it is not part of the history)."""
+    from kda_ascendc_b200 import build as kda_build
+    if not kda_build.LIB_PATH.exists():
+        kda_build.build()
+
+
 def golden_cases():
     return sorted(p.stem for p in GOLDEN_DIR.glob("*.pt"))
 
