@@ -27,6 +27,32 @@ __device__ __forceinline__ float warp_sum(float x) {
   return x;
 }
 
+// Sums N per-lane values over the warp at once: each exchange halves the number of values a lane
+// still carries (the upper half of the lanes keeps the upper half of the rows), so N values cost
+// N - 1 + (5 - log2 N) shuffles instead of 5 N.  Afterwards the lanes l with l >> (5 - log2 N) == r
+// hold the total of value r.
+template <int N> struct Log2 { static constexpr int v = 1 + Log2<N / 2>::v; };
+template <> struct Log2<1> { static constexpr int v = 0; };
+template <int N>
+__device__ __forceinline__ float warp_sum_rows(float (&p)[N], int lane) {
+  constexpr int LG = Log2<N>::v;
+#pragma unroll
+  for (int lv = 0; lv < LG; ++lv) {
+    const int half = N >> (lv + 1), mask = 16 >> lv;
+    const bool up = (lane & mask) != 0;
+#pragma unroll
+    for (int i = 0; i < half; ++i) {
+      const float send = up ? p[i] : p[i + half];
+      const float keep = up ? p[i + half] : p[i];
+      p[i] = keep + __shfl_xor_sync(0xffffffffu, send, mask);
+    }
+  }
+  float x = p[0];
+#pragma unroll
+  for (int lv = LG; lv < 5; ++lv) x += __shfl_xor_sync(0xffffffffu, x, 16 >> lv);
+  return x;
+}
+
 template <int ROWS, bool G_BF16>
 __global__ void __launch_bounds__(REC_WARPS * 32) kda_recurrent_kernel(const RecurrentParams p) {
   constexpr int ROWS_PER_CTA = ROWS * REC_WARPS;
@@ -55,7 +81,7 @@ __global__ void __launch_bounds__(REC_WARPS * 32) kda_recurrent_kernel(const Rec
   const int hq = h / p.group;   // grouped value heads share a q/k head
   const __nv_bfloat16* qp = p.q + b * p.q_s[0] + hq * p.q_s[2] + k0;
   const __nv_bfloat16* kp = p.k + b * p.k_s[0] + hq * p.k_s[2] + k0;
-  const __nv_bfloat16* vp = p.v + b * p.v_s[0] + h * p.v_s[2] + v0 + (lane % ROWS);
+  const __nv_bfloat16* vp = p.v + b * p.v_s[0] + h * p.v_s[2] + v0 + (lane >> (5 - Log2<ROWS>::v));   // v of the row this lane reduces
   const uint8_t* gp = static_cast<const uint8_t*>(p.g) + (b * p.g_s[0] + h * p.g_s[2] + k0) * (G_BF16 ? 2 : 4);
   const float* bp = p.beta + b * p.beta_s[0] + h * p.beta_s[2];
   __nv_bfloat16* op = p.o + b * p.o_s[0] + h * p.o_s[2] + v0;
@@ -71,7 +97,7 @@ __global__ void __launch_bounds__(REC_WARPS * 32) kda_recurrent_kernel(const Rec
     float4 gr;
     if (G_BF16) gr = load4(reinterpret_cast<const __nv_bfloat16*>(gp + t * p.g_s[1] * 2));
     else gr = *reinterpret_cast<const float4*>(gp + t * p.g_s[1] * 4);
-    const float vmine = __bfloat162float(vp[t * p.v_s[1]]);   // lane l holds v of row l % ROWS
+    const float vmine = __bfloat162float(vp[t * p.v_s[1]]);
     float beta = bp[t * p.beta_s[1]];
     beta = 1.0f / (1.0f + __expf(-beta));
 
@@ -88,19 +114,26 @@ __global__ void __launch_bounds__(REC_WARPS * 32) kda_recurrent_kernel(const Rec
     };
     const float4 dc = make_float4(dec1(gr.x, bias.x), dec1(gr.y, bias.y), dec1(gr.z, bias.z), dec1(gr.w, bias.w));
 
-    float oacc = 0.f;   // lane r keeps o of row r
+    // the ROWS predictions h khat are reduced together; the lanes that end up with row r's total are
+    // the ones that loaded v of row r (lane >> SH == r)
+    constexpr int SH = 5 - Log2<ROWS>::v;
+    float part[ROWS];
 #pragma unroll
     for (int r = 0; r < ROWS; ++r) {
       s[r].x *= dc.x; s[r].y *= dc.y; s[r].z *= dc.z; s[r].w *= dc.w;
-      const float pred = warp_sum(s[r].x * kn.x + s[r].y * kn.y + s[r].z * kn.z + s[r].w * kn.w);
-      const float vr = __shfl_sync(0xffffffffu, vmine, r);
-      const float vn = beta * (vr - pred);
+      part[r] = s[r].x * kn.x + s[r].y * kn.y + s[r].z * kn.z + s[r].w * kn.w;
+    }
+    const float pred = warp_sum_rows<ROWS>(part, lane);
+    const float vn_mine = beta * (vmine - pred);          // v' of row lane >> SH
+#pragma unroll
+    for (int r = 0; r < ROWS; ++r) {
+      const float vn = __shfl_sync(0xffffffffu, vn_mine, r << SH);
       s[r].x = fmaf(vn, kn.x, s[r].x); s[r].y = fmaf(vn, kn.y, s[r].y);
       s[r].z = fmaf(vn, kn.z, s[r].z); s[r].w = fmaf(vn, kn.w, s[r].w);
-      const float od = warp_sum(s[r].x * qn.x + s[r].y * qn.y + s[r].z * qn.z + s[r].w * qn.w);
-      if (lane == r) oacc = od;
+      part[r] = s[r].x * qn.x + s[r].y * qn.y + s[r].z * qn.z + s[r].w * qn.w;
     }
-    if (lane < ROWS) op[t * p.o_s[1] + lane] = __float2bfloat16(p.scale * oacc);
+    const float od = warp_sum_rows<ROWS>(part, lane);     // o of row lane >> SH
+    if ((lane & ((1 << SH) - 1)) == 0) op[t * p.o_s[1] + (lane >> SH)] = __float2bfloat16(p.scale * od);
   }
 
   if (p.ht != nullptr) {
