@@ -33,6 +33,7 @@ WS_HEADER_BYTES = 256
 
 _WORKSPACE_CACHE: dict[tuple, torch.Tensor] = {}
 _LAST_PROFILE: dict[str, object] = {}
+RECURRENT_MAX_TOKENS = 8   # kda_recurrent_fwd hands longer calls to the chunk kernels
 _LAUNCH_COUNTS = {"kda_k1": 0, "kda_k2": 0, "kda_recurrent": 0}
 
 
@@ -309,8 +310,9 @@ def kda_recurrent_fwd(q, k, v, g, beta, scale=None, initial_state=None, output_f
     """Token-by-token KDA recurrence for decode steps and short sequences.
 
     Same tensors as :func:`kda_bt16_fwd` with the in-kernel gate, l2-norm and beta sigmoid
-    (``g`` raw, ``beta`` logits, ``A_log`` required), any ``T >= 1`` (meant for one to a few dozen
-    tokens), V-first fp32 state ``[B, H, 128, 128]``.  Returns ``(o, state)``; with
+    (``g`` raw, ``beta`` logits, ``A_log`` required), any ``T >= 1`` (calls of more than
+    ``RECURRENT_MAX_TOKENS`` tokens run on the chunk kernels, which are faster from there on), V-first fp32
+    state ``[B, H, 128, 128]``.  Returns ``(o, state)``; with
     ``inplace_state=True`` the new state overwrites ``initial_state`` (which is returned).
     The reference has no decode function; the arithmetic is the token recurrence its tests use
     as the gold (``fused_recurrent_kda``, ``tests/test_kda_bt16.py:26-39`` of the reference) with
@@ -334,10 +336,16 @@ def kda_recurrent_fwd(q, k, v, g, beta, scale=None, initial_state=None, output_f
         ht = initial_state
     else:
         ht = torch.empty((B, H, HEAD_DIM, HEAD_DIM), dtype=torch.float32, device=dev) if output_final_state else None
+    # Beyond RECURRENT_MAX_TOKENS tokens per call the chunk kernels are faster (measured on B200, B64 H32:
+    # 8 tokens 151 us token by token against 155 us as one chunk, 16 tokens 279 us against 156 us); each K2
+    # CTA reads its rows of the state before it writes them, so the in-place update carries over.
+    chunked = T > RECURRENT_MAX_TOKENS
+    ws = _get_workspace(dev, B, T, H, True) if chunked else None
     args = make_args(q, k, v, g, beta, scale=scale, lower_bound=lower_bound, A_log=A_log, dt_bias=dt_bias,
-                     h0=initial_state, o=o, ht=ht, workspace=None, flags=_flags(True, True, True))
+                     h0=initial_state, o=o, ht=ht, workspace=ws, flags=_flags(True, True, True))
+    lib = _lib.load()
     with torch.cuda.device(dev):
-        _check(_lib.load().kda_recurrent_fwd(ctypes.byref(args), _stream_handle()))
+        _check((lib.kda_fwd if chunked else lib.kda_recurrent_fwd)(ctypes.byref(args), _stream_handle()))
     _LAUNCH_COUNTS["kda_recurrent"] += 1
     return o, ht
 

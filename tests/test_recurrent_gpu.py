@@ -127,3 +127,18 @@ def test_recurrent_plan_matches_stepwise_calls():
         o_t = plan.step()
         assert torch.equal(o_t, outs[t])
     assert torch.equal(st2, state) and plan.state is st2
+
+
+def test_long_calls_run_on_the_chunk_kernels_and_keep_the_in_place_contract():
+    import kda_ascendc_b200 as K
+    from kda_ascendc_b200 import api
+    B, T, H = 2, api.RECURRENT_MAX_TOKENS + 12, 5
+    inp = O.make_inputs(B, T, H, seed0=14, h0_std=0.2)
+    d = _dev(inp)
+    o_ref, ht_ref = K.kda_recurrent_fwd(d["q"], d["k"], d["v"], d["g"], d["beta"], initial_state=d["initial_state"], **_kw(d))
+    st = d["initial_state"].clone()
+    o_ip, st2 = K.kda_recurrent_fwd(d["q"], d["k"], d["v"], d["g"], d["beta"], initial_state=st, inplace_state=True, **_kw(d))
+    assert st2.data_ptr() == st.data_ptr() and torch.equal(o_ip, o_ref) and torch.equal(st, ht_ref)
+    o_g, ht_g = O.run_recurrent_gold(inp)
+    assert (o_ref.float().cpu() - o_g.float()).abs().max().item() <= 1e-3 * max(1.0, o_g.abs().max().item() / 0.06)
+    assert (ht_ref.cpu() - ht_g.float()).abs().max().item() <= 2e-3 * max(1.0, ht_g.abs().max().item())
