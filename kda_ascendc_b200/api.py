@@ -33,7 +33,7 @@ WS_HEADER_BYTES = 256
 
 _WORKSPACE_CACHE: dict[tuple, torch.Tensor] = {}
 _LAST_PROFILE: dict[str, object] = {}
-RECURRENT_MAX_TOKENS = 8   # kda_recurrent_fwd hands longer calls to the chunk kernels
+RECURRENT_MAX_TOKENS = 4   # kda_recurrent_fwd hands longer calls to the chunk kernels
 _LAUNCH_COUNTS = {"kda_k1": 0, "kda_k2": 0, "kda_recurrent": 0}
 
 
@@ -337,8 +337,9 @@ def kda_recurrent_fwd(q, k, v, g, beta, scale=None, initial_state=None, output_f
     else:
         ht = torch.empty((B, H, HEAD_DIM, HEAD_DIM), dtype=torch.float32, device=dev) if output_final_state else None
     # Beyond RECURRENT_MAX_TOKENS tokens per call the chunk kernels are faster (measured on B200, B64 H32:
-    # 8 tokens 151 us token by token against 155 us as one chunk, 16 tokens 279 us against 156 us); each K2
-    # CTA reads its rows of the state before it writes them, so the in-place update carries over.
+    # 4 tokens 88 us token by token against 104 us as one chunk, 8 tokens 151 us against 105 us, 16 tokens
+    # 279 us against 107 us); each K2 CTA reads its rows of the state before it writes them, so the in-place
+    # update carries over.
     chunked = T > RECURRENT_MAX_TOKENS
     ws = _get_workspace(dev, B, T, H, True) if chunked else None
     args = make_args(q, k, v, g, beta, scale=scale, lower_bound=lower_bound, A_log=A_log, dt_bias=dt_bias,
