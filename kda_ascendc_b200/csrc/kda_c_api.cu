@@ -112,7 +112,7 @@ void pick_split(const KdaFwdArgs* a, bool state_only, int* vsplit, int* variant)
     else var = (bh * 4 <= sms) ? 1 : 3;
   }
   if (vs == 0) {
-    if (var == 1) vs = (bh * 8 <= sms) ? 8 : 4;
+    if (var == 1) vs = (bh * 16 <= sms) ? 16 : (bh * 8 <= sms) ? 8 : 4;
     else vs = (bh * 4 <= sms) ? 4 : 2;
   }
   if (var == 1 && vs < 4) vs = 4;
