@@ -127,15 +127,23 @@ class _Segment:
         self.args.ht = ctypes.c_void_p(ht.data_ptr())
 
     def transforms(self):
-        """(M_seg, Q_seg): two state-only passes over the records."""
+        """(M_seg, Q_seg): two state-only passes over the records.  They are independent (same records,
+        different entry state), and one pass leaves most of the GPU idle (a chain per head), so the second
+        runs beside the first on a side stream."""
         eye = torch.eye(D, device=self.dev, dtype=torch.float32).expand(self.B, self.H, D, D).contiguous()
         M = torch.empty_like(eye)
         Q = torch.empty_like(eye)
+        cur = torch.cuda.current_stream(self.dev)
+        side = torch.cuda.Stream(device=self.dev)
+        args_m = _lib.KdaFwdArgs.from_buffer_copy(self.args)
+        args_m.h0 = ctypes.c_void_p(eye.data_ptr())
+        args_m.ht = ctypes.c_void_p(M.data_ptr())
         with torch.cuda.device(self.dev):
+            side.wait_stream(cur)                      # K1's records (and eye) are ready
+            api._check(self.lib.kda_fwd_k2_state(ctypes.byref(args_m), 1, ctypes.c_void_p(side.cuda_stream)))
             self._with_state(None, Q)
-            api._check(self.lib.kda_fwd_k2_state(ctypes.byref(self.args), 0, self.stream))
-            self._with_state(eye, M)
-            api._check(self.lib.kda_fwd_k2_state(ctypes.byref(self.args), 1, self.stream))
+            api._check(self.lib.kda_fwd_k2_state(ctypes.byref(self.args), 0, ctypes.c_void_p(cur.cuda_stream)))
+            cur.wait_stream(side)
         self._eye = eye   # stays alive until the launches that read it have been ordered
         return M, Q
 
