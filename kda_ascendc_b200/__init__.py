@@ -6,12 +6,12 @@ backend).  The device code is hand-written sm_100a CUDA (K1, three organisations
 token-recurrence step) behind a C ABI
 (``include/kda_b200.h``); there is no other backend and no CPU fallback.
 """
-from .api import (CHUNK, PERSISTENT_LOOP, RecurrentPlan, get_last_profile, kda_bt16_debug, kda_bt16_fwd,
+from .api import (CHUNK, PERSISTENT_LOOP, ForwardPlan, RecurrentPlan, get_last_profile, kda_bt16_debug, kda_bt16_fwd,
                   kda_bt16_fwd_ascendc, kda_recurrent_fwd, workspace_bytes)
 from .layout import pack_tokens, unpack_tokens
 
 __all__ = [
-    "CHUNK", "PERSISTENT_LOOP", "RecurrentPlan", "get_last_profile", "kda_bt16_debug", "kda_bt16_fwd",
+    "CHUNK", "PERSISTENT_LOOP", "ForwardPlan", "RecurrentPlan", "get_last_profile", "kda_bt16_debug", "kda_bt16_fwd",
     "kda_bt16_fwd_ascendc", "kda_recurrent_fwd", "pack_tokens", "unpack_tokens", "workspace_bytes",
 ]
 __version__ = "0.1.0"

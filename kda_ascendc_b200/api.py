@@ -351,6 +351,55 @@ def kda_recurrent_fwd(q, k, v, g, beta, scale=None, initial_state=None, output_f
     return o, ht
 
 
+class ForwardPlan:
+    """The chunk forward on fixed buffers without per-call host work: validation, outputs, scratch
+    and the argument block are made once, :meth:`run` is one C call (K1 + K2 on the current stream).
+
+    For loops that refill the same input tensors (serving with static shapes, benchmarks).  ``o`` and
+    ``final_state`` belong to the plan and are overwritten by every run.  In-kernel gate, l2-norm and
+    beta sigmoid, V-first state; ``cu_seqlens`` as in :func:`kda_bt16_fwd`.
+    """
+
+    def __init__(self, q, k, v, g, beta, *, scale=None, initial_state=None, output_final_state=True,
+                 lower_bound=-5.0, A_log=None, dt_bias=None, cu_seqlens=None):
+        n_states = None if cu_seqlens is None else len(cu_seqlens) - 1
+        if cu_seqlens is not None and q.ndim == 4 and q.shape[0] != 1:
+            raise ValueError(f"cu_seqlens needs a packed batch of size 1, got B={q.shape[0]}")
+        _validate_kda_inputs(q, k, v, g, beta, initial_state, True, True, lower_bound, A_log, dt_bias, True,
+                             n_states=n_states)
+        _require_cuda(q)
+        B, T, _, K = q.shape
+        H = v.shape[2]
+        self.device = q.device
+        tables = None if cu_seqlens is None else _varlen_tables(cu_seqlens, T, H, q.device)
+        ns = B if tables is None else tables[0]
+        self.o = torch.empty((B, T, H, HEAD_DIM), dtype=torch.bfloat16, device=q.device)
+        self.final_state = (torch.empty((ns, H, HEAD_DIM, HEAD_DIM), dtype=torch.float32, device=q.device)
+                            if output_final_state else None)
+        self._ws = torch.empty(workspace_bytes(B, T if tables is None else BT * tables[1], H), dtype=torch.uint8,
+                               device=q.device)
+        self._keep = (q, k, v, g, beta, A_log, dt_bias, initial_state, tables)   # the argument block holds raw pointers
+        self._args = make_args(q, k, v, g, beta, scale=K ** -0.5 if scale is None else scale, lower_bound=lower_bound,
+                               A_log=A_log, dt_bias=dt_bias, h0=initial_state, o=self.o, ht=self.final_state,
+                               workspace=self._ws, flags=_flags(True, True, True))
+        if tables is not None:
+            self._args.n_seqs, self._args.n_chunks = tables[0], tables[1]
+            self._args.chunk_table, self._args.seq_table = _ptr(tables[2]), _ptr(tables[3])
+        self._ref = ctypes.byref(self._args)
+        self._fn = _lib.load().kda_fwd
+
+    def run(self, stream: Optional[int] = None):
+        """One forward over the current contents of the input buffers; returns ``(o, final_state)``."""
+        if stream is None:
+            stream = torch.cuda.current_stream(self.device).cuda_stream
+        rc = self._fn(self._ref, ctypes.c_void_p(stream))
+        if rc != 0:
+            _check(rc)
+        _LAUNCH_COUNTS["kda_k1"] += 1
+        _LAUNCH_COUNTS["kda_k2"] += 1
+        return self.o, self.final_state
+
+
 class RecurrentPlan:
     """Decode loop without per-step host work: fixed input buffers, in-place state, one C call per step.
 

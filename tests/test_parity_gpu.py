@@ -300,3 +300,25 @@ def test_two_streams_with_their_own_workspaces_do_not_interfere():
     for i in range(2):
         for o, ht in outs[i]:
             assert torch.equal(o, ref[i][0]) and torch.equal(ht, ref[i][1])
+
+
+def test_forward_plan_matches_the_function_on_refilled_buffers():
+    dev = torch.device("cuda", 0)
+    runs = []
+    for seed in (200, 201):
+        inp = O.make_inputs(2, 300, 3, seed0=seed, h0_std=0.05)
+        runs.append({k: (v.to(dev) if torch.is_tensor(v) else v) for k, v in inp.items()})
+    buf = {n: runs[0][n].clone() for n in ("q", "k", "v", "g", "beta", "initial_state")}
+    plan = K.ForwardPlan(buf["q"], buf["k"], buf["v"], buf["g"], buf["beta"], scale=runs[0]["scale"],
+                         initial_state=buf["initial_state"], lower_bound=runs[0]["lower_bound"], A_log=runs[0]["A_log"],
+                         dt_bias=runs[0]["dt_bias"])
+    for d in runs:                       # same A_log / dt_bias distribution seeds differ: refill them too
+        for n in buf:
+            buf[n].copy_(d[n])
+        runs[0]["A_log"].copy_(d["A_log"]); runs[0]["dt_bias"].copy_(d["dt_bias"])
+        o, ht = plan.run()
+        o_f, ht_f = K.kda_bt16_fwd(d["q"], d["k"], d["v"], d["g"], d["beta"], scale=d["scale"],
+                                   initial_state=d["initial_state"], output_final_state=True,
+                                   use_qk_l2norm_in_kernel=True, use_gate_in_kernel=True, use_beta_sigmoid_in_kernel=True,
+                                   lower_bound=d["lower_bound"], A_log=d["A_log"], dt_bias=d["dt_bias"])
+        assert torch.equal(o, o_f) and torch.equal(ht, ht_f)
