@@ -93,10 +93,12 @@ int check_k2(const KdaFwdArgs* a, bool state_only) {
 // up to ~37 (batch x head) chains the 8-rows-per-warp "n8" form wins (two warps per SM while
 // chains x 8 CTAs fit the SMs, else four); beyond that the 16-rows-per-warp "m16" form with four
 // warps per CTA, which reads half the shared-memory bytes per MMA.  With more chains than SMs the
-// tensor-memory form (one CTA per chain, two per SM, tcgen05) is 10-20 % faster still, provided the
-// chains are at least 16 chunks long (its set-up -- TMEM allocation, the state in and out through
-// registers -- costs about as much as ten steps; 2,048 chains x 1 chunk: 131 us against 80 us,
-// x 16 chunks: 321 us against 343 us); it has no state-only variant.
+// tensor-memory form (one CTA per chain, two per SM, tcgen05) is 10-25 % faster still once the
+// chains are a few chunks long: its set-up (TMEM allocation, the state in and out through
+// registers) costs about as much as two steps.  2,048 chains x 1 chunk: 82 us against 80 us,
+// x 4: 127 against 135, x 8: 169 against 205, x 16: 266 against 343; 256 chains x 4: 17 against
+// 21, 512 chains x 4: 41 against 40 -- hence from four chunks per chain on.  It has no state-only
+// variant.
 void pick_split(const KdaFwdArgs* a, bool state_only, int* vsplit, int* variant) {
   int dev = 0, sms = 148;
   if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
@@ -108,7 +110,7 @@ void pick_split(const KdaFwdArgs* a, bool state_only, int* vsplit, int* variant)
   if (var == 0) {
     if (vs == 16) var = 1;
     else if (vs == 2) var = 3;
-    else if (bh > sms && !state_only && vs == 0 && steps >= 16) var = 4;
+    else if (bh > sms && !state_only && vs == 0 && steps >= 4) var = 4;
     else var = (bh * 4 <= sms) ? 1 : 3;
   }
   if (vs == 0) {

@@ -118,6 +118,37 @@ __device__ __forceinline__ void tmem_st16(uint32_t a, const uint32_t (&r)[16]) {
       "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
       : "memory");
 }
+// 16-lane shapes: thread (g = lane / 4, t = lane % 4) of the warp holds, per repeat n, the fp32 pairs
+// (row g, columns 8n + 2t, 8n + 2t + 1) and (row g + 8, same columns) -- the mma.sync accumulator layout,
+// whose rows are 32-byte pieces of memory rows: the state moves between global memory and TMEM with
+// fully used sectors.  The 128-bit shape is the same with one 32-bit column per thread and repeat.
+__device__ __forceinline__ void tmem_st_16x256b_x8(uint32_t a, const uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.16x256b.x8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,"
+      "%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};" ::"r"(a),
+      "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
+      "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]), "r"(r[18]),
+      "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]),
+      "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+      : "memory");
+}
+__device__ __forceinline__ void tmem_ld_16x256b_x8(uint32_t a, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.16x256b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+      "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(a));
+}
+__device__ __forceinline__ void tmem_st_16x128b_x8(uint32_t a, const uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.16x128b.x8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};" ::"r"(a),
+      "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
+      "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+      : "memory");
+}
 __device__ __forceinline__ void tma_load_5d(uint32_t dst_smem, const void* tmap, int c0, int c1, int c2, int c3, int c4,
                                             uint32_t bar) {
   asm volatile(
@@ -259,7 +290,6 @@ __global__ void __launch_bounds__(KT_THREADS, 2) kda_k2t_kernel(const __grid_con
     const int quad = warp & 3, half = warp >> 2;
     const int v = quad * 32 + lane;                       // state row = TMEM lane
     const uint32_t tl = tbase + (static_cast<uint32_t>(quad * 32) << 16);
-    const float* h0row = p.h0 != nullptr ? p.h0 + (static_cast<size_t>(bh) * D + v) * D + half * 64 : nullptr;
     // u[tok = 8 half + j][v] in the record's fragment order
     const uint32_t u_off = T_U + (v >> 3) * 512 + ((v & 7) >> 1) * 16 + (half * 2 + (v & 1)) * 4;
     bool ok = true;
@@ -267,21 +297,27 @@ __global__ void __launch_bounds__(KT_THREADS, 2) kda_k2t_kernel(const __grid_con
     // initial state: TMEM <- h0 * dec(chunk 0); bf16(h0) as the first A operand
     ok = mbar_wait_bounded(full(0), 0, sAbort);
     if (ok) {
+      // this warp's 32 rows x 64 columns in two 16-row halves, through the 16-lane access shapes
       const float* dec0 = reinterpret_cast<const float*>(smem + T_AQ + (REC_DEC - REC_AQK)) + half * 64;
+      const int g4 = lane >> 2, t4 = lane & 3;
+#pragma unroll 1
+      for (int hh = 0; hh < 2; ++hh) {
+        const int r0 = quad * 32 + hh * 16 + g4;
+        const float* src = p.h0 != nullptr ? p.h0 + (static_cast<size_t>(bh) * D + r0) * D + half * 64 + t4 * 2 : nullptr;
+        uint32_t sr[32], ar[16];
 #pragma unroll
-      for (int cc = 0; cc < 4; ++cc) {
-        uint32_t sr[16], ar[8];
-#pragma unroll
-        for (int j4 = 0; j4 < 4; ++j4) {
-          const float4 x = h0row != nullptr ? *reinterpret_cast<const float4*>(h0row + cc * 16 + j4 * 4) : make_float4(0, 0, 0, 0);
-          const float4 dd = *reinterpret_cast<const float4*>(dec0 + cc * 16 + j4 * 4);
-          ar[j4 * 2] = pack_bf16(x.x, x.y);
-          ar[j4 * 2 + 1] = pack_bf16(x.z, x.w);
-          sr[j4 * 4 + 0] = __float_as_uint(x.x * dd.x); sr[j4 * 4 + 1] = __float_as_uint(x.y * dd.y);
-          sr[j4 * 4 + 2] = __float_as_uint(x.z * dd.z); sr[j4 * 4 + 3] = __float_as_uint(x.w * dd.w);
+        for (int n8 = 0; n8 < 8; ++n8) {
+          const float2 x = src != nullptr ? *reinterpret_cast<const float2*>(src + n8 * 8) : make_float2(0.f, 0.f);
+          const float2 y = src != nullptr ? *reinterpret_cast<const float2*>(src + 8 * D + n8 * 8) : make_float2(0.f, 0.f);
+          const float2 dd = *reinterpret_cast<const float2*>(dec0 + n8 * 8 + t4 * 2);
+          ar[n8 * 2] = pack_bf16(x.x, x.y);
+          ar[n8 * 2 + 1] = pack_bf16(y.x, y.y);
+          sr[n8 * 4 + 0] = __float_as_uint(x.x * dd.x); sr[n8 * 4 + 1] = __float_as_uint(x.y * dd.y);
+          sr[n8 * 4 + 2] = __float_as_uint(y.x * dd.x); sr[n8 * 4 + 3] = __float_as_uint(y.y * dd.y);
         }
-        tmem_st16(tl + C_S + half * 64 + cc * 16, sr);
-        tmem_st8(tl + C_AS + half * 32 + cc * 8, ar);
+        const uint32_t th = tbase + (static_cast<uint32_t>(quad * 32 + hh * 16) << 16);
+        tmem_st_16x256b_x8(th + C_S + half * 64, sr);
+        tmem_st_16x128b_x8(th + C_AS + half * 32, ar);
       }
       tc_wait_st();
       tc_fence_before();
@@ -370,10 +406,6 @@ __global__ void __launch_bounds__(KT_THREADS, 2) kda_k2t_kernel(const __grid_con
       if (tid == 0) mbar_arrive(empty(s));   // every operand of this stage has been consumed
       // dec of the next chunk (its stage was waited for in prepare)
       const float* decn = reinterpret_cast<const float*>(smem + ((n + 1) % KT_STAGES) * T_STAGE + T_AQ + (REC_DEC - REC_AQK)) + half * 64;
-      float* htrow = (!more && p.ht != nullptr) ? p.ht + (static_cast<size_t>(bh) * D + v) * D + half * 64 : nullptr;
-#ifdef KDA_K2T_PROFILE
-      htrow = nullptr;   // ht holds clock stamps
-#endif
       // TMEM loads are issued one chunk ahead of their use; the output operands (which must leave
       // TMEM before the next P1 / P3 overwrite them) travel with the first one
       uint32_t sr[2][16];
@@ -409,12 +441,6 @@ __global__ void __launch_bounds__(KT_THREADS, 2) kda_k2t_kernel(const __grid_con
           }
           tmem_st16(tl + C_S + half * 64 + cc * 16, cur);
           tmem_st8(tl + C_AS + half * 32 + cc * 8, ar);
-        } else if (htrow != nullptr) {
-#pragma unroll
-          for (int j4 = 0; j4 < 4; ++j4)
-            *reinterpret_cast<float4*>(htrow + cc * 16 + j4 * 4) =
-                make_float4(__uint_as_float(cur[j4 * 4]), __uint_as_float(cur[j4 * 4 + 1]), __uint_as_float(cur[j4 * 4 + 2]),
-                            __uint_as_float(cur[j4 * 4 + 3]));
         }
         if (cc < 3) {
           tc_wait_ld();
@@ -429,6 +455,28 @@ __global__ void __launch_bounds__(KT_THREADS, 2) kda_k2t_kernel(const __grid_con
       }
       KT_STAMP(4)
     }
+#ifndef KDA_K2T_PROFILE
+    if (ok && p.ht != nullptr) {
+      // final state: TMEM -> global through the 16-lane shape (32-byte pieces of the state's rows);
+      // every element-wise thread has seen the last P2 complete
+      const int g4 = lane >> 2, t4 = lane & 3;
+#pragma unroll 1
+      for (int hh = 0; hh < 2; ++hh) {
+        uint32_t fr[32];
+        tmem_ld_16x256b_x8(tbase + (static_cast<uint32_t>(quad * 32 + hh * 16) << 16) + C_S + half * 64, fr);
+        tc_wait_ld();
+        pin16(reinterpret_cast<uint32_t (&)[16]>(fr[0]));
+        pin16(reinterpret_cast<uint32_t (&)[16]>(fr[16]));
+        float* dst = p.ht + (static_cast<size_t>(bh) * D + quad * 32 + hh * 16 + g4) * D + half * 64 + t4 * 2;
+#pragma unroll
+        for (int n8 = 0; n8 < 8; ++n8) {
+          *reinterpret_cast<float2*>(dst + n8 * 8) = make_float2(__uint_as_float(fr[n8 * 4]), __uint_as_float(fr[n8 * 4 + 1]));
+          *reinterpret_cast<float2*>(dst + 8 * D + n8 * 8) =
+              make_float2(__uint_as_float(fr[n8 * 4 + 2]), __uint_as_float(fr[n8 * 4 + 3]));
+        }
+      }
+    }
+#endif
     if (ok && NT > 0) ok = store_o(NT - 1);
     if (!ok) give_up();
   }
