@@ -160,6 +160,14 @@ int kda_fwd_static_scratch(const KdaFwdArgs* args, void* stream);
  * wait inside the kernels completed). */
 int kda_fwd_status(const void* workspace, void* stream, int32_t* status_out);
 
+/* Which organisation of K2 a call with these arguments runs, without running it: k2_variant
+ * (1 n8, 3 m16, 4 tc) and k2_vsplit (CTAs per chain; 1 for tc) as kda_fwd / kda_fwd_k2 (state_only = 0) or kda_fwd_k2_state
+ * (state_only = 1) resolve the zeros ("automatic") in args.  Reads B, T, H, n_seqs, n_chunks,
+ * k2_variant and k2_vsplit only; no pointer in args is touched and no CUDA work is issued.
+ * sm_count = 0 takes the SM count of the current device (148 without one).  No reference
+ * counterpart: the reference has one K2 (src/kda_bt16/kernels.py:188-318). */
+int kda_fwd_k2_choice(const KdaFwdArgs* args, int state_only, int sm_count, int32_t* variant_out, int32_t* vsplit_out);
+
 /* Number of kernels the last kda_fwd* call on this thread launched. */
 int kda_last_launch_count(void);
 

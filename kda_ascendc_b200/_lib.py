@@ -17,7 +17,7 @@ FLAG_GATE, FLAG_L2NORM, FLAG_BETA_SIGMOID = 1, 2, 4
 EXPORTS = (
     "kda_fwd_workspace_bytes", "kda_fwd", "kda_fwd_k1", "kda_fwd_k2", "kda_fwd_k2_state", "kda_recurrent_fwd",
     "kda_varlen_fill_tables", "kda_selftest_bounded_wait", "kda_fwd_static_scratch",
-    "kda_fwd_status", "kda_last_launch_count", "kda_last_error", "kda_version",
+    "kda_fwd_status", "kda_fwd_k2_choice", "kda_last_launch_count", "kda_last_error", "kda_version",
 )
 
 
@@ -63,6 +63,9 @@ def load() -> ctypes.CDLL:
     lib.kda_varlen_fill_tables.restype = ctypes.c_int
     lib.kda_varlen_fill_tables.argtypes = [ctypes.POINTER(ctypes.c_int32), ctypes.c_int32, ctypes.c_int32,
                                            ctypes.POINTER(ctypes.c_int32), ctypes.POINTER(ctypes.c_int32)]
+    lib.kda_fwd_k2_choice.restype = ctypes.c_int
+    lib.kda_fwd_k2_choice.argtypes = [ctypes.POINTER(KdaFwdArgs), ctypes.c_int, ctypes.c_int,
+                                      ctypes.POINTER(ctypes.c_int32), ctypes.POINTER(ctypes.c_int32)]
     lib.kda_fwd_status.restype = ctypes.c_int
     lib.kda_fwd_status.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.POINTER(ctypes.c_int32)]
     lib.kda_last_launch_count.restype = ctypes.c_int

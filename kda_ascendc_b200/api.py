@@ -202,6 +202,21 @@ def check_device_status(workspace: torch.Tensor) -> int:
     return st.value
 
 
+K2_FORMS = {1: "n8", 3: "m16", 4: "tc"}
+
+
+def k2_choice(B: int, T: int, H: int, *, state_only: bool = False, n_seqs: int = 0, n_chunks: int = 0,
+              sm_count: int = 0) -> tuple[str, int]:
+    """(organisation, CTAs per chain) of K2 for a problem, as the library's automatic choice
+    resolves it: "n8" / "m16" (``mma.sync``, 8 / 16 state rows per warp) or "tc" (tcgen05, the
+    state in tensor memory).  Host logic only; ``sm_count=0`` takes the current device's."""
+    a = _lib.KdaFwdArgs()
+    a.B, a.T, a.H, a.n_seqs, a.n_chunks = B, T, H, n_seqs, n_chunks
+    var, vs = ctypes.c_int32(0), ctypes.c_int32(0)
+    _check(_lib.load().kda_fwd_k2_choice(ctypes.byref(a), int(state_only), sm_count, ctypes.byref(var), ctypes.byref(vs)))
+    return K2_FORMS[var.value], vs.value
+
+
 def _get_workspace(device, B, T, H, reuse: bool) -> torch.Tensor:
     nbytes = workspace_bytes(B, T, H)
     if reuse:

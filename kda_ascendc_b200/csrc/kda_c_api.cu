@@ -99,9 +99,12 @@ int check_k2(const KdaFwdArgs* a, bool state_only) {
 // x 4: 127 against 135, x 8: 169 against 205, x 16: 266 against 343; 256 chains x 4: 17 against
 // 21, 512 chains x 4: 41 against 40 -- hence from four chunks per chain on.  It has no state-only
 // variant.
-void pick_split(const KdaFwdArgs* a, bool state_only, int* vsplit, int* variant) {
-  int dev = 0, sms = 148;
-  if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+void pick_split(const KdaFwdArgs* a, bool state_only, int* vsplit, int* variant, int sms = 0) {
+  if (sms <= 0) {   // the current device's SM count
+    int dev = 0;
+    sms = 148;
+    if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  }
   const long long bh = static_cast<long long>(a->n_seqs > 0 ? a->n_seqs : a->B) * a->H;
   // chunks per chain (the mean, for packed sequences)
   const long long steps = a->n_seqs > 0 ? a->n_chunks / a->n_seqs : (a->T + kda::BT - 1) / kda::BT;
@@ -356,6 +359,18 @@ int kda_fwd_status(const void* workspace, void* stream, int32_t* status_out) {
   if (e != cudaSuccess) return fail(KDA_ERR_CUDA, "kda: status read failed: %s", cudaGetErrorString(e));
   *status_out = v;
   if (v != 0) return fail(KDA_ERR_DEVICE_STATUS, "kda: a bounded device-side wait gave up%s (status %lld)", "", v);
+  return KDA_OK;
+}
+
+int kda_fwd_k2_choice(const KdaFwdArgs* args, int state_only, int sm_count, int32_t* variant_out, int32_t* vsplit_out) {
+  if (args == nullptr || variant_out == nullptr || vsplit_out == nullptr)
+    return fail(KDA_ERR_INVALID_ARG, "kda: null pointer%s", "");
+  if (args->k2_variant < 0 || args->k2_variant > 4)
+    return fail(KDA_ERR_INVALID_ARG, "kda: k2_variant%s %lld is not one of 0..4", "", static_cast<long long>(args->k2_variant));
+  int vs = 0, var = 0;
+  pick_split(args, state_only != 0, &vs, &var, sm_count);
+  *variant_out = var;
+  *vsplit_out = (var == 4) ? 1 : vs;   // the tensor-memory form runs one CTA per chain
   return KDA_OK;
 }
 

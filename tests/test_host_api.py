@@ -141,3 +141,39 @@ def test_varlen_tables_host_helper():
     bad = (ctypes.c_int32 * 3)(0, 5, 5)
     assert lib.kda_varlen_fill_tables(bad, 2, 2, None, None) == -1
     assert "empty" in _lib.last_error()
+
+
+def test_k2_choice_table():
+    """Which organisation of K2 the library picks (host logic only; 148 SMs given explicitly)."""
+    lib = _lib.load()
+
+    def choice(B, T, H, state_only=0, variant=0, vsplit=0, n_seqs=0, n_chunks=0):
+        a = _lib.KdaFwdArgs()
+        a.B, a.T, a.H, a.k2_variant, a.k2_vsplit, a.n_seqs, a.n_chunks = B, T, H, variant, vsplit, n_seqs, n_chunks
+        var, vs = ctypes.c_int32(-1), ctypes.c_int32(-1)
+        assert lib.kda_fwd_k2_choice(ctypes.byref(a), state_only, 148, ctypes.byref(var), ctypes.byref(vs)) == 0
+        return var.value, vs.value
+
+    N8, M16, TC = 1, 3, 4
+    assert choice(1, 8192, 32) == (N8, 4)            # the headline shape: 32 chains, one warp per SM sub-partition
+    assert choice(1, 8192, 4) == (N8, 16)            # a handful of chains: sixteen CTAs per chain
+    assert choice(1, 8192, 16) == (N8, 8)
+    assert choice(1, 8192, 96) == (M16, 2)           # more than 37 chains, fewer than SMs
+    assert choice(2, 4096, 16) == (N8, 4)
+    assert choice(1, 4096, 37) == (N8, 4) and choice(1, 4096, 38) == (M16, 2)
+    assert choice(8, 2048, 32) == (TC, 1)            # more chains than SMs, long enough chains
+    assert choice(8, 48, 32) == (M16, 2)             # three chunks per chain: set-up not amortised
+    assert choice(8, 64, 32) == (TC, 1)
+    assert choice(8, 2048, 32, state_only=1) == (M16, 2)   # no state-only form in tensor memory
+    assert choice(8, 2048, 32, vsplit=2) == (M16, 2)       # an explicit split keeps the mma.sync forms
+    assert choice(8, 2048, 32, variant=M16) == (M16, 2)
+    assert choice(1, 8192, 32, variant=TC) == (TC, 1)
+    # packed sequences: chains = sequences x heads, steps = the mean chunk count
+    assert choice(1, 4096, 32, n_seqs=8, n_chunks=8 * 32) == (TC, 1)
+    assert choice(1, 4096, 32, n_seqs=8, n_chunks=8 * 2) == (M16, 2)
+    assert choice(1, 4096, 32, n_seqs=2, n_chunks=256) == (M16, 2)
+    a = _lib.KdaFwdArgs()
+    a.B, a.T, a.H, a.k2_variant = 1, 16, 1, 9
+    var, vs = ctypes.c_int32(), ctypes.c_int32()
+    assert lib.kda_fwd_k2_choice(ctypes.byref(a), 0, 148, ctypes.byref(var), ctypes.byref(vs)) != 0
+    assert "k2_variant" in _lib.last_error()
