@@ -43,8 +43,15 @@ constexpr int T_AQ = 24576;    // Aqk hi, Aqk lo, dec as in the record (1536 B)
 constexpr int T_AQF = 26112;   // Aqk hi / lo re-laid as 8x8 core matrices (2 x 512 B)
 constexpr int T_STAGE = 27648;
 constexpr int T_BARS = KT_STAGES * T_STAGE;
-// barriers: full[S], empty[S], p1, v, p2, s, o
-constexpr int T_NBARS = 2 * KT_STAGES + 5;
+// The state snapshot reaches the MMA thread in KT_PG column groups, so that the first k-steps of the
+// next P1 are issued while the element-wise warps still convert the rest of the state.
+#ifndef KDA_K2T_P1_GROUPS
+#define KDA_K2T_P1_GROUPS 2
+#endif
+constexpr int KT_PG = KDA_K2T_P1_GROUPS;
+static_assert(KT_PG == 1 || KT_PG == 2 || KT_PG == 4, "column groups of the snapshot");
+// barriers: full[S], empty[S], p1, v, p2, o, s[KT_PG]
+constexpr int T_NBARS = 2 * KT_STAGES + 4 + KT_PG;
 constexpr int T_SLOT = T_BARS + T_NBARS * 8;      // TMEM base address, abort flag, issued count
 constexpr int T_OST = (T_SLOT + 32 + 15) / 16 * 16;                // two [16 tok][128 v] bf16 output staging tiles
 constexpr int T_TOTAL = T_OST + 2 * TILE_BYTES;
@@ -196,8 +203,8 @@ __global__ void __launch_bounds__(KT_THREADS, 2) kda_k2t_kernel(const __grid_con
   auto full = [&](int s) { return bar0 + s * 8; };
   auto empty = [&](int s) { return bar0 + (KT_STAGES + s) * 8; };
   const uint32_t bar_p1 = bar0 + (2 * KT_STAGES + 0) * 8, bar_v = bar0 + (2 * KT_STAGES + 1) * 8;
-  const uint32_t bar_p2 = bar0 + (2 * KT_STAGES + 2) * 8, bar_s = bar0 + (2 * KT_STAGES + 3) * 8;
-  const uint32_t bar_o = bar0 + (2 * KT_STAGES + 4) * 8;
+  const uint32_t bar_p2 = bar0 + (2 * KT_STAGES + 2) * 8, bar_o = bar0 + (2 * KT_STAGES + 3) * 8;
+  auto bar_s = [&](int q) { return bar0 + (2 * KT_STAGES + 4 + q) * 8; };
   uint32_t* slot = reinterpret_cast<uint32_t*>(smem + T_SLOT);
   volatile int* sAbort = reinterpret_cast<volatile int*>(smem + T_SLOT + 4);
   volatile int* sIssued = sAbort + 1;
@@ -207,7 +214,7 @@ __global__ void __launch_bounds__(KT_THREADS, 2) kda_k2t_kernel(const __grid_con
     mbar_init(bar_p1, 1);
     mbar_init(bar_v, KT_EPI_WARPS);    // one arrival per element-wise warp (lane 0, after __syncwarp)
     mbar_init(bar_p2, 1);
-    mbar_init(bar_s, KT_EPI_WARPS);
+    for (int q = 0; q < KT_PG; ++q) mbar_init(bar_s(q), KT_EPI_WARPS);
     mbar_init(bar_o, KT_EPI_WARPS);
     *sAbort = 0;
     *sIssued = 0;
@@ -259,14 +266,24 @@ __global__ void __launch_bounds__(KT_THREADS, 2) kda_k2t_kernel(const __grid_con
         const uint32_t st = sbase + s * T_STAGE;
         if (!mbar_wait_bounded(full(s), (n / KT_STAGES) & 1, sAbort)) { give_up(); break; }
         KT_STAMP(8)
-        if (!mbar_wait_bounded(bar_s, n & 1, sAbort)) { give_up(); break; }     // bf16(h) and decayed h are in TMEM
-        tc_fence_after();
-        KT_STAMP(9)
         const uint64_t dwq = smem_desc(st + T_WQ, 16, 1024, 2);   // k-step ks: start address + atom * 4096 + (ks % 4) * 32 bytes
+        bool ready = true;
 #pragma unroll
-        for (int ks = 0; ks < 8; ++ks)
-          umma_ts(tbase + C_D1, tbase + C_AS + ks * 8, dwq + static_cast<uint64_t>(((ks >> 2) * 4096 + (ks & 3) * 32) >> 4),
-                  ID_P1, ks > 0);
+        for (int q = 0; q < KT_PG; ++q) {
+          // column group q of both halves of bf16(h) is in TMEM (with the last group: the decayed h too)
+          if (!mbar_wait_bounded(bar_s(q), n & 1, sAbort)) { ready = false; break; }
+          tc_fence_after();
+          if (q == 0) { KT_STAMP(9) }
+#pragma unroll
+          for (int cc = q * (4 / KT_PG); cc < (q + 1) * (4 / KT_PG); ++cc)
+#pragma unroll
+            for (int hf = 0; hf < 2; ++hf) {
+              const int ks = hf * 4 + cc;
+              umma_ts(tbase + C_D1, tbase + C_AS + ks * 8, dwq + static_cast<uint64_t>((hf * 4096 + cc * 32) >> 4), ID_P1,
+                      !(cc == 0 && hf == 0));
+            }
+        }
+        if (!ready) { give_up(); break; }
         umma_commit(bar_p1);
         KT_STAMP(10)
         if (!mbar_wait_bounded(bar_v, n & 1, sAbort)) { give_up(); break; }     // v_new hi/lo are in TMEM
@@ -322,7 +339,8 @@ __global__ void __launch_bounds__(KT_THREADS, 2) kda_k2t_kernel(const __grid_con
       tc_wait_st();
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(bar_s);
+      if (lane == 0)
+        for (int q = 0; q < KT_PG; ++q) mbar_arrive(bar_s(q));
     } else {
       give_up();
     }
@@ -442,16 +460,16 @@ __global__ void __launch_bounds__(KT_THREADS, 2) kda_k2t_kernel(const __grid_con
           tmem_st16(tl + C_S + half * 64 + cc * 16, cur);
           tmem_st8(tl + C_AS + half * 32 + cc * 8, ar);
         }
+        if (more && (cc + 1) % (4 / KT_PG) == 0) {   // a column group of the snapshot is complete
+          tc_wait_st();
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(bar_s((cc + 1) / (4 / KT_PG) - 1));
+        }
         if (cc < 3) {
           tc_wait_ld();
           pin16(sr[(cc + 1) & 1]);
         }
-      }
-      if (more) {
-        tc_wait_st();
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(bar_s);
       }
       KT_STAMP(4)
     }
