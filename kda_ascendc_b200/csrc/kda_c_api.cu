@@ -95,8 +95,8 @@ int check_k2(const KdaFwdArgs* a, bool state_only) {
 // warps per CTA, which reads half the shared-memory bytes per MMA.  With more chains than SMs the
 // tensor-memory form (one CTA per chain, two per SM, tcgen05) is 10-25 % faster still once the
 // chains are a few chunks long: its set-up (TMEM allocation, the state in and out through
-// registers) costs about as much as two steps.  2,048 chains x 1 chunk: 82 us against 80 us,
-// x 4: 127 against 135, x 8: 169 against 205, x 16: 266 against 343; 256 chains x 4: 17 against
+// registers) costs about as much as two steps.  2,048 chains x 1 chunk: 81 us against 80 us,
+// x 4: 126 against 134, x 8: 162 against 205, x 16: 253 against 343; 256 chains x 4: 17 against
 // 21, 512 chains x 4: 41 against 40 -- hence from four chunks per chain on.  It has no state-only
 // variant.
 void pick_split(const KdaFwdArgs* a, bool state_only, int* vsplit, int* variant, int sms = 0) {

@@ -50,8 +50,8 @@ constexpr int T_BARS = KT_STAGES * T_STAGE;
 #endif
 constexpr int KT_PG = KDA_K2T_P1_GROUPS;
 static_assert(KT_PG == 1 || KT_PG == 2 || KT_PG == 4, "column groups of the snapshot");
-// barriers: full[S], empty[S], p1, v, p2, o, s[KT_PG]
-constexpr int T_NBARS = 2 * KT_STAGES + 4 + KT_PG;
+// barriers: full[S], empty[S], p1, v, p2, o, p3, s[KT_PG]
+constexpr int T_NBARS = 2 * KT_STAGES + 5 + KT_PG;
 constexpr int T_SLOT = T_BARS + T_NBARS * 8;      // TMEM base address, abort flag, issued count
 constexpr int T_OST = (T_SLOT + 32 + 15) / 16 * 16;                // two [16 tok][128 v] bf16 output staging tiles
 constexpr int T_TOTAL = T_OST + 2 * TILE_BYTES;
@@ -204,7 +204,8 @@ __global__ void __launch_bounds__(KT_THREADS, 2) kda_k2t_kernel(const __grid_con
   auto empty = [&](int s) { return bar0 + (KT_STAGES + s) * 8; };
   const uint32_t bar_p1 = bar0 + (2 * KT_STAGES + 0) * 8, bar_v = bar0 + (2 * KT_STAGES + 1) * 8;
   const uint32_t bar_p2 = bar0 + (2 * KT_STAGES + 2) * 8, bar_o = bar0 + (2 * KT_STAGES + 3) * 8;
-  auto bar_s = [&](int q) { return bar0 + (2 * KT_STAGES + 4 + q) * 8; };
+  const uint32_t bar_p3 = bar0 + (2 * KT_STAGES + 4) * 8;
+  auto bar_s = [&](int q) { return bar0 + (2 * KT_STAGES + 5 + q) * 8; };
   uint32_t* slot = reinterpret_cast<uint32_t*>(smem + T_SLOT);
   volatile int* sAbort = reinterpret_cast<volatile int*>(smem + T_SLOT + 4);
   volatile int* sIssued = sAbort + 1;
@@ -214,6 +215,7 @@ __global__ void __launch_bounds__(KT_THREADS, 2) kda_k2t_kernel(const __grid_con
     mbar_init(bar_p1, 1);
     mbar_init(bar_v, KT_EPI_WARPS);    // one arrival per element-wise warp (lane 0, after __syncwarp)
     mbar_init(bar_p2, 1);
+    mbar_init(bar_p3, 1);
     for (int q = 0; q < KT_PG; ++q) mbar_init(bar_s(q), KT_EPI_WARPS);
     mbar_init(bar_o, KT_EPI_WARPS);
     *sAbort = 0;
@@ -293,11 +295,12 @@ __global__ void __launch_bounds__(KT_THREADS, 2) kda_k2t_kernel(const __grid_con
         umma_ts(tbase + C_S, tbase + C_VH, dkh, ID_P2, 1);
         umma_ts(tbase + C_S, tbase + C_VL, dkh, ID_P2, 1);
         umma_ts(tbase + C_S, tbase + C_VH, dkl, ID_P2, 1);
+        umma_commit(bar_p2);   // the state pass of the element-wise warps starts while P3 runs
         const uint64_t dah = smem_desc(st + T_AQF, 128, 256, 0), dal = smem_desc(st + T_AQF + 512, 128, 256, 0);
         umma_ts(tbase + C_D3, tbase + C_VH, dah, ID_P3, 0);
         umma_ts(tbase + C_D3, tbase + C_VL, dah, ID_P3, 1);
         umma_ts(tbase + C_D3, tbase + C_VH, dal, ID_P3, 1);
-        umma_commit(bar_p2);
+        umma_commit(bar_p3);
         KT_STAMP(12)
       }
     }
@@ -346,6 +349,7 @@ __global__ void __launch_bounds__(KT_THREADS, 2) kda_k2t_kernel(const __grid_con
     }
 
     float oq[8], o3[8], uv[8];
+    uint32_t aq[8];
     __nv_bfloat16* const orow = p.o + b * p.o_s[0] + tok0 * p.o_s[1] + h * p.o_s[2];
 
     // State-independent operands of chunk n1: this thread's eight u values and, by warp 0, Aqk hi / lo
@@ -397,8 +401,10 @@ __global__ void __launch_bounds__(KT_THREADS, 2) kda_k2t_kernel(const __grid_con
       {
         uint32_t d1[8];
         tmem_ld8(tl + C_D1 + half * 8, d1);
+        tmem_ld8(tl + C_D1 + 16 + half * 8, aq);   // qg h^T of this chunk: it must leave TMEM before the next P1
         tc_wait_ld();
         pin8(d1);
+        pin8(aq);
         uint32_t vh[4], vl[4];
 #pragma unroll
         for (int c = 0; c < 4; ++c)
@@ -414,6 +420,8 @@ __global__ void __launch_bounds__(KT_THREADS, 2) kda_k2t_kernel(const __grid_con
 
       // while P2 / P3 run: the previous chunk's outputs, the next chunk's operands
       if (n > 0 && !store_o(n - 1)) { ok = false; break; }
+#pragma unroll
+      for (int j = 0; j < 8; ++j) oq[j] = __uint_as_float(aq[j]);
       if (more && !prepare(n + 1)) { ok = false; break; }
       KT_STAMP(5)
 
@@ -421,24 +429,13 @@ __global__ void __launch_bounds__(KT_THREADS, 2) kda_k2t_kernel(const __grid_con
       if (!mbar_wait_bounded(bar_p2, n & 1, sAbort)) { ok = false; break; }
       tc_fence_after();
       KT_STAMP(3)
-      if (tid == 0) mbar_arrive(empty(s));   // every operand of this stage has been consumed
       // dec of the next chunk (its stage was waited for in prepare)
       const float* decn = reinterpret_cast<const float*>(smem + ((n + 1) % KT_STAGES) * T_STAGE + T_AQ + (REC_DEC - REC_AQK)) + half * 64;
-      // TMEM loads are issued one chunk ahead of their use; the output operands (which must leave
-      // TMEM before the next P1 / P3 overwrite them) travel with the first one
+      // the TMEM loads of the state are issued one 16-column step ahead of their use
       uint32_t sr[2][16];
-      {
-        uint32_t a[8], c3[8];
-        tmem_ld8(tl + C_D1 + 16 + half * 8, a);
-        tmem_ld8(tl + C_D3 + half * 8, c3);
-        tmem_ld16(tl + C_S + half * 64, sr[0]);
-        tc_wait_ld();
-        pin8(a);
-        pin8(c3);
-        pin16(sr[0]);
-#pragma unroll
-        for (int j = 0; j < 8; ++j) { oq[j] = __uint_as_float(a[j]); o3[j] = __uint_as_float(c3[j]); }
-      }
+      tmem_ld16(tl + C_S + half * 64, sr[0]);
+      tc_wait_ld();
+      pin16(sr[0]);
 #pragma unroll
       for (int cc = 0; cc < 4; ++cc) {
         uint32_t (&cur)[16] = sr[cc & 1];
@@ -470,6 +467,18 @@ __global__ void __launch_bounds__(KT_THREADS, 2) kda_k2t_kernel(const __grid_con
           tc_wait_ld();
           pin16(sr[(cc + 1) & 1]);
         }
+      }
+      // Aqk v_new of this chunk (P3 was committed after P2; it must leave TMEM before the next P3)
+      if (!mbar_wait_bounded(bar_p3, n & 1, sAbort)) { ok = false; break; }
+      tc_fence_after();
+      if (tid == 0) mbar_arrive(empty(s));   // every operand of this stage has been consumed
+      {
+        uint32_t c3[8];
+        tmem_ld8(tl + C_D3 + half * 8, c3);
+        tc_wait_ld();
+        pin8(c3);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) o3[j] = __uint_as_float(c3[j]);
       }
       KT_STAMP(4)
     }
