@@ -93,12 +93,14 @@ int check_k2(const KdaFwdArgs* a, bool state_only) {
 // up to ~37 (batch x head) chains the 8-rows-per-warp "n8" form wins (two warps per SM while
 // chains x 8 CTAs fit the SMs, else four); beyond that the 16-rows-per-warp "m16" form with four
 // warps per CTA, which reads half the shared-memory bytes per MMA.  With more chains than SMs the
-// tensor-memory form (one CTA per chain, two per SM, tcgen05) is 10-25 % faster still once the
+// tensor-memory form (one CTA per chain, two per SM, tcgen05) is 10-35 % faster still once the
 // chains are a few chunks long: its set-up (TMEM allocation, the state in and out through
 // registers) costs about as much as two steps.  2,048 chains x 1 chunk: 81 us against 80 us,
-// x 4: 126 against 134, x 8: 162 against 205, x 16: 253 against 343; 256 chains x 4: 17 against
-// 21, 512 chains x 4: 41 against 40 -- hence from four chunks per chain on.  It has no state-only
-// variant.
+// x 4: 126 against 134, x 16: 243 against 343; 1,024 chains x 64: 404 against 601; 256 chains
+// x 4: 17 against 21 -- hence from four chunks per chain on.  Between half as many chains as SMs and as many
+// (where the 16-row form needs two CTAs per chain and so more than one CTA per SM) it wins from
+// about 32 chunks per chain: 96 chains x 64 chunks 85 us against 92, x 16 equal.  It has no
+// state-only variant.
 void pick_split(const KdaFwdArgs* a, bool state_only, int* vsplit, int* variant, int sms = 0) {
   if (sms <= 0) {   // the current device's SM count
     int dev = 0;
@@ -113,7 +115,7 @@ void pick_split(const KdaFwdArgs* a, bool state_only, int* vsplit, int* variant,
   if (var == 0) {
     if (vs == 16) var = 1;
     else if (vs == 2) var = 3;
-    else if (bh > sms && !state_only && vs == 0 && steps >= 4) var = 4;
+    else if (!state_only && vs == 0 && ((bh > sms && steps >= 4) || (bh * 2 > sms && steps >= 32))) var = 4;
     else var = (bh * 4 <= sms) ? 1 : 3;
   }
   if (vs == 0) {

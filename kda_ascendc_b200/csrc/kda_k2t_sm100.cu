@@ -418,8 +418,7 @@ __global__ void __launch_bounds__(KT_THREADS, 2) kda_k2t_kernel(const __grid_con
       if (lane == 0) mbar_arrive(bar_v);
       KT_STAMP(2)
 
-      // while P2 / P3 run: the previous chunk's outputs, the next chunk's operands
-      if (n > 0 && !store_o(n - 1)) { ok = false; break; }
+      // while P2 runs: the next chunk's operands
 #pragma unroll
       for (int j = 0; j < 8; ++j) oq[j] = __uint_as_float(aq[j]);
       if (more && !prepare(n + 1)) { ok = false; break; }
@@ -480,6 +479,7 @@ __global__ void __launch_bounds__(KT_THREADS, 2) kda_k2t_kernel(const __grid_con
 #pragma unroll
         for (int j = 0; j < 8; ++j) o3[j] = __uint_as_float(c3[j]);
       }
+      if (!store_o(n)) { ok = false; break; }   // while the next P1 runs
       KT_STAMP(4)
     }
 #ifndef KDA_K2T_PROFILE
@@ -504,7 +504,6 @@ __global__ void __launch_bounds__(KT_THREADS, 2) kda_k2t_kernel(const __grid_con
       }
     }
 #endif
-    if (ok && NT > 0) ok = store_o(NT - 1);
     if (!ok) give_up();
   }
 

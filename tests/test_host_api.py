@@ -158,7 +158,10 @@ def test_k2_choice_table():
     assert choice(1, 8192, 32) == (N8, 4)            # the headline shape: 32 chains, one warp per SM sub-partition
     assert choice(1, 8192, 4) == (N8, 16)            # a handful of chains: sixteen CTAs per chain
     assert choice(1, 8192, 16) == (N8, 8)
-    assert choice(1, 8192, 96) == (M16, 2)           # more than 37 chains, fewer than SMs
+    assert choice(1, 8192, 64) == (M16, 2)           # more than 37 chains, at most half as many as SMs
+    assert choice(1, 8192, 74) == (M16, 2) and choice(1, 8192, 75) == (TC, 1)
+    assert choice(1, 8192, 96) == (TC, 1)            # two CTAs per chain no longer fit one per SM
+    assert choice(1, 256, 96) == (M16, 2)            # ... but only for long chains
     assert choice(2, 4096, 16) == (N8, 4)
     assert choice(1, 4096, 37) == (N8, 4) and choice(1, 4096, 38) == (M16, 2)
     assert choice(8, 2048, 32) == (TC, 1)            # more chains than SMs, long enough chains
