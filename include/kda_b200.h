@@ -161,7 +161,8 @@ int kda_fwd_static_scratch(const KdaFwdArgs* args, void* stream);
 int kda_fwd_status(const void* workspace, void* stream, int32_t* status_out);
 
 /* Which organisation of K2 a call with these arguments runs, without running it: k2_variant
- * (1 n8, 3 m16, 4 tc) and k2_vsplit (CTAs per chain; 1 for tc) as kda_fwd / kda_fwd_k2 (state_only = 0) or kda_fwd_k2_state
+ * (1 n8, 3 m16, 4 tc; with tc chosen automatically, a last partial wave of at most SMs/2 chains runs in
+ * the m16 form as a second launch) and k2_vsplit (CTAs per chain; 1 for tc) as kda_fwd / kda_fwd_k2 (state_only = 0) or kda_fwd_k2_state
  * (state_only = 1) resolve the zeros ("automatic") in args.  Reads B, T, H, n_seqs, n_chunks,
  * k2_variant and k2_vsplit only; no pointer in args is touched and no CUDA work is issued.
  * sm_count = 0 takes the SM count of the current device (148 without one).  No reference

@@ -220,7 +220,27 @@ int do_k2(const KdaFwdArgs* a, bool state_only, int zero_u, cudaStream_t st) {
   if (variant == 4) {
     const long long n_records = a->n_seqs > 0 ? static_cast<long long>(a->n_chunks) * a->H
                                               : static_cast<long long>(a->B) * a->H * p.NT;
-    e = kda::launch_k2t(p, n_records, st);
+    // Tail wave.  The tensor-memory form holds two chains per SM at once; when the chains left over
+    // after the full waves are at most half as many as SMs, they run faster in the 16-row form
+    // (two CTAs per chain, one per SM: 0.8 us per step against 1.3 us for a lone tensor-memory CTA),
+    // launched behind the full waves.  Only for the automatic choice.
+    int dev = 0, sms = 148;
+    if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    const long long bh = static_cast<long long>(a->n_seqs > 0 ? a->n_seqs : a->B) * a->H;
+    const long long tail = bh % (2LL * sms);
+    if (a->k2_variant == 0 && bh > 2LL * sms && tail > 0 && tail * 2 <= sms) {
+      p.chain0 = 0;
+      p.n_chains = static_cast<int>(bh - tail);
+      e = kda::launch_k2t(p, n_records, st);
+      if (e == cudaSuccess) {
+        ++g_launches;
+        p.chain0 = static_cast<int>(bh - tail);
+        p.n_chains = static_cast<int>(tail);
+        e = kda::launch_k2m(p, 2, false, st);
+      }
+    } else {
+      e = kda::launch_k2t(p, n_records, st);
+    }
   } else {
     e = (variant == 3) ? kda::launch_k2m(p, vsplit, state_only, st) : kda::launch_k2n(p, vsplit, variant, state_only, st);
   }

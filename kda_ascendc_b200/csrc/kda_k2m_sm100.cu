@@ -46,7 +46,7 @@ __global__ void __launch_bounds__((CW + 1) * 32, MINB) kda_k2m_kernel(const K2Pa
   const int tid = threadIdx.x;
   const int lane = tid & 31;
   const int warp = tid >> 5;
-  const int bh = blockIdx.x / NV;
+  const int bh = blockIdx.x / NV + p.chain0;
   const int vs = blockIdx.x % NV;
   int b = bh / p.H;
   const int h = bh % p.H;
@@ -358,7 +358,7 @@ static cudaError_t launch_k2m_c(const K2Params& p, cudaStream_t stream) {
     cudaError_t e = cudaDeviceGetAttribute(&sms[dev], cudaDevAttrMultiProcessorCount, dev);
     if (e != cudaSuccess) return e;
   }
-  const int nblocks = (p.seq_table != nullptr ? p.n_seqs : p.B) * p.H * (8 / CW);
+  const int nblocks = (p.n_chains > 0 ? p.n_chains : (p.seq_table != nullptr ? p.n_seqs : p.B) * p.H) * (8 / CW);
   if (CW == 4 && nblocks > sms[dev]) return launch_k2m_t<CW, STATE_ONLY, 2>(p, nblocks, stream);
   return launch_k2m_t<CW, STATE_ONLY, 1>(p, nblocks, stream);
 }

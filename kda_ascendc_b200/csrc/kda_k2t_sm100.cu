@@ -186,7 +186,7 @@ __global__ void __launch_bounds__(KT_THREADS, 2) kda_k2t_kernel(const __grid_con
   extern __shared__ __align__(1024) uint8_t smem[];
   const K2Params& p = pp.k;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const int bh = blockIdx.x;
+  const int bh = blockIdx.x + p.chain0;
   int b = bh / p.H;
   const int h = bh % p.H;
   int NT = p.NT, Tlen = p.T, tok0 = 0;
@@ -563,7 +563,7 @@ cudaError_t launch_k2t(const K2Params& p, long long n_records, cudaStream_t stre
     if (e != cudaSuccess) return e;
     configured[dev] = true;
   }
-  const int nblocks = (p.seq_table != nullptr ? p.n_seqs : p.B) * p.H;
+  const int nblocks = p.n_chains > 0 ? p.n_chains : (p.seq_table != nullptr ? p.n_seqs : p.B) * p.H;
   kda_k2t_kernel<<<nblocks, KT_THREADS, T_TOTAL, stream>>>(pp);
   return cudaGetLastError();
 }

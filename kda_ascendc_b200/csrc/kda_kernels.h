@@ -65,6 +65,8 @@ struct K2Params {
   // length); the grid then runs over (sequence, head); null for a fixed-length batch
   const int4* seq_table;
   int n_seqs;
+  // a launch may cover a sub-range of the (batch, head) chains: first chain and count (0 = all)
+  int chain0, n_chains;
 };
 
 cudaError_t launch_k1(const K1Params& p, bool g_bf16, bool fast_exp, cudaStream_t stream);

@@ -55,3 +55,26 @@ def test_tensor_memory_k2_packed_sequences():
     o_r, ht_r = O.run_chunk_reference_varlen(inp, cu)
     assert (o - o_r.float()).abs().max().item() <= 1e-3
     assert (ht - ht_r).abs().max().item() <= 2e-3
+
+
+def test_tail_wave_runs_in_the_16_row_form():
+    """320 chains on 148 SMs: 296 fill one wave of the tensor-memory form, the other 24 follow in
+    the 16-row form (a second K2 launch on the chains' sub-range).  Both halves against the oracle."""
+    from kda_ascendc_b200 import _lib
+    sms = torch.cuda.get_device_properties(0).multi_processor_count
+    B, T, H = 10, 72, 32
+    inp = O.make_inputs(B, T, H, seed0=31, h0_std=0.02)
+    o, ht = _run(inp, 0)
+    launches = _lib.load().kda_last_launch_count()
+    tail = (B * H) % (2 * sms)
+    if B * H > 2 * sms and 0 < tail * 2 <= sms:
+        assert launches == 3     # K1, K2 on tcgen05 for the full waves, K2 m16 for the tail
+    o_r, ht_r = O.run_chunk_reference(inp)
+    assert (o - o_r.float()).abs().max().item() <= 1e-3
+    assert (ht - ht_r).abs().max().item() <= 2e-3
+    o3, ht3 = _run(inp, 3)
+    assert (o - o3).abs().max().item() <= 2.5e-4
+    assert (ht - ht3).abs().max().item() <= 2e-5
+    # the tail chains are the last ones: bit-identical to the 16-row form there
+    first_tail = B * H - tail
+    assert torch.equal(ht.reshape(B * H, 128, 128)[first_tail:], ht3.reshape(B * H, 128, 128)[first_tail:])
