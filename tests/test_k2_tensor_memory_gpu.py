@@ -78,3 +78,23 @@ def test_tail_wave_runs_in_the_16_row_form():
     # the tail chains are the last ones: bit-identical to the 16-row form there
     first_tail = B * H - tail
     assert torch.equal(ht.reshape(B * H, 128, 128)[first_tail:], ht3.reshape(B * H, 128, 128)[first_tail:])
+
+
+def test_tail_wave_with_packed_sequences():
+    """20 packed sequences x 16 heads = 320 chains: the automatic choice (tensor memory + tail in the
+    16-row form) against the 16-row form alone."""
+    lengths = [64 + 7 * i for i in range(20)]
+    T, H = sum(lengths), 16
+    inp = O.make_inputs(1, T, H, seed0=37, h0_std=None)
+    g = torch.Generator().manual_seed(7)
+    inp["initial_state"] = torch.randn(len(lengths), H, 128, 128, generator=g) * 0.05
+    cu = [0]
+    for L in lengths:
+        cu.append(cu[-1] + L)
+    o, ht = _run(inp, 0, cu=cu)
+    o3, ht3 = _run(inp, 3, cu=cu)
+    assert (o - o3).abs().max().item() <= 2.5e-4
+    assert (ht - ht3).abs().max().item() <= 2e-5
+    o_r, ht_r = O.run_chunk_reference_varlen(inp, cu)
+    assert (o - o_r.float()).abs().max().item() <= 1e-3
+    assert (ht - ht_r).abs().max().item() <= 2e-3
