@@ -221,9 +221,10 @@ int do_k2(const KdaFwdArgs* a, bool state_only, int zero_u, cudaStream_t st) {
     const long long n_records = a->n_seqs > 0 ? static_cast<long long>(a->n_chunks) * a->H
                                               : static_cast<long long>(a->B) * a->H * p.NT;
     // Tail wave.  The tensor-memory form holds two chains per SM at once; when the chains left over
-    // after the full waves are at most half as many as SMs, they run faster in the 16-row form
-    // (two CTAs per chain, one per SM: 0.8 us per step against 1.3 us for a lone tensor-memory CTA),
-    // launched behind the full waves.  Only for the automatic choice.
+    // after the full waves are at most half as many as SMs, they run faster in an mma.sync form
+    // (16-row: two CTAs per chain, one per SM, 0.8 us per step; 8-row for at most SMs/4 chains,
+    // 0.55 us per step; against 1.3 us for a lone tensor-memory CTA), launched behind the full
+    // waves.  Only for the automatic choice.
     int dev = 0, sms = 148;
     if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     const long long bh = static_cast<long long>(a->n_seqs > 0 ? a->n_seqs : a->B) * a->H;
@@ -236,7 +237,9 @@ int do_k2(const KdaFwdArgs* a, bool state_only, int zero_u, cudaStream_t st) {
         ++g_launches;
         p.chain0 = static_cast<int>(bh - tail);
         p.n_chains = static_cast<int>(tail);
-        e = kda::launch_k2m(p, 2, false, st);
+        // the few-chain rule of pick_split applied to the tail alone
+        if (tail * 4 <= sms) e = kda::launch_k2n(p, tail * 16 <= sms ? 16 : tail * 8 <= sms ? 8 : 4, 1, false, st);
+        else e = kda::launch_k2m(p, 2, false, st);
       }
     } else {
       e = kda::launch_k2t(p, n_records, st);

@@ -71,7 +71,7 @@ __global__ void __launch_bounds__((CW + 1) * 32, 1) kda_k2_kernel(const K2Params
   const int tid = threadIdx.x;
   const int lane = tid & 31;
   const int warp = tid >> 5;
-  const int bh = blockIdx.x / NV;
+  const int bh = blockIdx.x / NV + p.chain0;
   const int vs = blockIdx.x % NV;
   int b = bh / p.H;
   const int h = bh % p.H;
@@ -372,7 +372,7 @@ static cudaError_t launch_k2_t(const K2Params& p, cudaStream_t stream) {
     if (e != cudaSuccess) return e;
     configured[dev] = true;
   }
-  const int nblocks = (p.seq_table != nullptr ? p.n_seqs : p.B) * p.H * (D / (CW * NVT * 8));
+  const int nblocks = (p.n_chains > 0 ? p.n_chains : (p.seq_table != nullptr ? p.n_seqs : p.B) * p.H) * (D / (CW * NVT * 8));
   kda_k2_kernel<CW, NVT, STATE_ONLY><<<nblocks, (CW + 1) * 32, smem_bytes, stream>>>(p);
   return cudaGetLastError();
 }
