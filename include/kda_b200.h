@@ -19,8 +19,11 @@
  *   kda_last_error     <- the launcher's exception text
  *                         (aclab/launcher/launcher.cpp:35-39)
  *
- * Conventions: the library allocates nothing; the caller owns every buffer and
- * passes raw device pointers (NULL = tensor absent).  All launches are
+ * Conventions: the library never calls an allocation routine; the caller owns every
+ * buffer and passes raw device pointers (NULL = tensor absent).  What the library holds by
+ * itself: a thread-local error string and tensor-map cache, per-device one-time kernel
+ * attribute set-up, and the fixed KDA_STATIC_SCRATCH_BYTES device array (with its cached
+ * address per device) behind kda_fwd_static_scratch.  All launches are
  * asynchronous on the given stream (a cudaStream_t passed as void*), exactly as
  * the reference launches on the caller's current stream.  Functions return 0 on
  * success and a negative KDA_ERR_* code otherwise; kda_last_error() returns the
@@ -80,8 +83,7 @@ typedef struct KdaFwdArgs {
   uint32_t flags;
   int32_t k2_vsplit;    /* 0 = choose; else CTAs per (batch, head) that share the rows of its state */
   int32_t k2_variant;   /* 0 = choose; how K2 maps state rows to warps:
-                           1 "n8":  8 rows per warp  (k2_vsplit 4, 8 or 16)
-                           2 "n16": 16 rows per warp (k2_vsplit 2, 4 or 8), rows on the MMA N dimension
+                           1 "n8":  8 rows per warp  (k2_vsplit 4, 8 or 16), rows on the MMA N dimension
                            3 "m16": 16 rows per warp (k2_vsplit 2, 4 or 8), rows on the MMA M dimension
                            4 "tc":  all 128 rows of a head in tensor memory, tcgen05 MMAs (k2_vsplit ignored;
                                     not for kda_fwd_k2_state) */
@@ -155,6 +157,12 @@ int kda_selftest_bounded_wait(void* workspace, void* stream);
  * capture.  No allocation routine is called. */
 #define KDA_STATIC_SCRATCH_BYTES (32 * 1024 * 1024)
 int kda_fwd_static_scratch(const KdaFwdArgs* args, void* stream);
+
+/* Synchronising read of the status word that kda_fwd_static_scratch's kernels report through (it
+ * sits at the start of the library's own array on the current device, whose address no caller
+ * has): 0 = every bounded device-side wait of the last call completed; otherwise the code is
+ * stored and KDA_ERR_DEVICE_STATUS returned, as by kda_fwd_status.  No reference counterpart. */
+int kda_fwd_static_scratch_status(void* stream, int32_t* status_out);
 
 /* Synchronising read of the device status word of a workspace (0 = every bounded
  * wait inside the kernels completed). */

@@ -17,6 +17,7 @@ FLAG_GATE, FLAG_L2NORM, FLAG_BETA_SIGMOID = 1, 2, 4
 EXPORTS = (
     "kda_fwd_workspace_bytes", "kda_fwd", "kda_fwd_k1", "kda_fwd_k2", "kda_fwd_k2_state", "kda_recurrent_fwd",
     "kda_varlen_fill_tables", "kda_selftest_bounded_wait", "kda_fwd_static_scratch",
+    "kda_fwd_static_scratch_status",
     "kda_fwd_status", "kda_fwd_k2_choice", "kda_last_launch_count", "kda_last_error", "kda_version",
 )
 
@@ -68,6 +69,8 @@ def load() -> ctypes.CDLL:
                                       ctypes.POINTER(ctypes.c_int32), ctypes.POINTER(ctypes.c_int32)]
     lib.kda_fwd_status.restype = ctypes.c_int
     lib.kda_fwd_status.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.POINTER(ctypes.c_int32)]
+    lib.kda_fwd_static_scratch_status.restype = ctypes.c_int
+    lib.kda_fwd_static_scratch_status.argtypes = [ctypes.c_void_p, ctypes.POINTER(ctypes.c_int32)]
     lib.kda_last_launch_count.restype = ctypes.c_int
     lib.kda_last_error.restype = ctypes.c_char_p
     lib.kda_version.restype = ctypes.c_char_p

@@ -407,12 +407,22 @@ class ForwardPlan:
         """One forward over the current contents of the input buffers; returns ``(o, final_state)``."""
         if stream is None:
             stream = torch.cuda.current_stream(self.device).cuda_stream
-        rc = self._fn(self._ref, ctypes.c_void_p(stream))
+        rc = _call_on_device(self.device, self._fn, self._ref, ctypes.c_void_p(stream))
         if rc != 0:
             _check(rc)
         _LAUNCH_COUNTS["kda_k1"] += 1
         _LAUNCH_COUNTS["kda_k2"] += 1
         return self.o, self.final_state
+
+
+def _call_on_device(device, fn, *args):
+    """Call a C entry point with ``device`` current.  The library sizes grids, caches kernel
+    attributes and resolves tensor maps for the CURRENT device, so a process that drives several
+    GPUs must not run a plan built for one of them while another is current."""
+    if torch.cuda.current_device() == device.index:
+        return fn(*args)
+    with torch.cuda.device(device):
+        return fn(*args)
 
 
 class RecurrentPlan:
@@ -446,7 +456,7 @@ class RecurrentPlan:
         ``stream``: raw CUDA stream handle; default = the current torch stream of the plan's device."""
         if stream is None:
             stream = torch.cuda.current_stream(self.device).cuda_stream
-        rc = self._fn(self._ref, ctypes.c_void_p(stream))
+        rc = _call_on_device(self.device, self._fn, self._ref, ctypes.c_void_p(stream))
         if rc != 0:
             _check(rc)
         _LAUNCH_COUNTS["kda_recurrent"] += 1

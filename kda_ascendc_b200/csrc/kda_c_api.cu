@@ -63,6 +63,17 @@ int check_k1(const KdaFwdArgs* a) {
   if (!row_aligned(a->q, a->q_stride, 2) || !row_aligned(a->k, a->k_stride, 2) || !row_aligned(a->v, a->v_stride, 2) ||
       !row_aligned(a->g, a->g_stride, a->g_dtype == KDA_G_BF16 ? 2 : 4))
     return fail(KDA_ERR_INVALID_ARG, "kda: q/k/v/g rows must start on 16-byte boundaries%s", "");
+  // an expanded view (stride 0 on a dimension larger than 1) cannot be described to the TMA unit
+  const int hq = a->Hq > 0 ? a->Hq : a->H;
+  const struct { const int64_t* s; int heads; const char* name; } views[4] = {
+      {a->q_stride, hq, "q"}, {a->k_stride, hq, "k"}, {a->v_stride, a->H, "v"}, {a->g_stride, a->H, "g"}};
+  for (const auto& v : views) {
+    const int sizes[3] = {a->B, a->T, v.heads};
+    for (int i = 0; i < 3; ++i)
+      if (sizes[i] > 1 && v.s[i] <= 0)
+        return fail(KDA_ERR_INVALID_ARG, "kda: %s has a zero or negative stride on a dimension of size %lld (expanded views are not supported)",
+                    v.name, sizes[i]);
+  }
   return KDA_OK;
 }
 
@@ -75,7 +86,8 @@ int check_k2(const KdaFwdArgs* a, bool state_only) {
     if (ptr != nullptr && reinterpret_cast<uintptr_t>(ptr) % 16 != 0)
       return fail(KDA_ERR_INVALID_ARG, "kda: h0 and ht must be 16-byte aligned%s", "");
   const int vs = a->k2_vsplit, var = a->k2_variant;
-  if (var < 0 || var > 4) return fail(KDA_ERR_INVALID_ARG, "kda: k2_variant must be 0..4%s (got %lld)", "", var);
+  if (var < 0 || var > 4 || var == 2)
+    return fail(KDA_ERR_INVALID_ARG, "kda: k2_variant must be 0, 1, 3 or 4%s (got %lld)", "", var);
   if (var == 4 && state_only)
     return fail(KDA_ERR_INVALID_ARG, "kda: the tensor-memory K2 (k2_variant 4) has no state-only form%s", "");
   if (var == 4) return KDA_OK;
@@ -245,7 +257,7 @@ int do_k2(const KdaFwdArgs* a, bool state_only, int zero_u, cudaStream_t st) {
       e = kda::launch_k2t(p, n_records, st);
     }
   } else {
-    e = (variant == 3) ? kda::launch_k2m(p, vsplit, state_only, st) : kda::launch_k2n(p, vsplit, variant, state_only, st);
+    e = (variant == 3) ? kda::launch_k2m(p, vsplit, state_only, st) : kda::launch_k2n(p, vsplit, 1, state_only, st);
   }
   if (e != cudaSuccess) return fail(KDA_ERR_CUDA, "kda: K2 launch failed: %s", cudaGetErrorString(e));
   ++g_launches;
@@ -390,8 +402,8 @@ int kda_fwd_status(const void* workspace, void* stream, int32_t* status_out) {
 int kda_fwd_k2_choice(const KdaFwdArgs* args, int state_only, int sm_count, int32_t* variant_out, int32_t* vsplit_out) {
   if (args == nullptr || variant_out == nullptr || vsplit_out == nullptr)
     return fail(KDA_ERR_INVALID_ARG, "kda: null pointer%s", "");
-  if (args->k2_variant < 0 || args->k2_variant > 4)
-    return fail(KDA_ERR_INVALID_ARG, "kda: k2_variant%s %lld is not one of 0..4", "", static_cast<long long>(args->k2_variant));
+  if (args->k2_variant < 0 || args->k2_variant > 4 || args->k2_variant == 2)
+    return fail(KDA_ERR_INVALID_ARG, "kda: k2_variant%s %lld is not one of 0, 1, 3, 4", "", static_cast<long long>(args->k2_variant));
   int vs = 0, var = 0;
   pick_split(args, state_only != 0, &vs, &var, sm_count);
   *variant_out = var;

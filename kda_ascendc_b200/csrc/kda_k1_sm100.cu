@@ -55,15 +55,6 @@ struct K1Smem {
   static constexpr int TOTAL = FLAG + 8;
 };
 
-// Developer facility: with -DKDA_K1_PROFILE thread 0 of CTA 77 writes clock() stamps of the
-// phases of its chunks to K1Params::ainv_out (which then is NOT the inverse) -- 16 per chunk.
-#ifdef KDA_K1_PROFILE
-#define K1_STAMP(i) \
-  if (tid == 0 && blockIdx.x == 77 && it < 16) reinterpret_cast<unsigned*>(p.ainv_out)[it * 16 + (i)] = (unsigned)clock();
-#else
-#define K1_STAMP(i)
-#endif
-
 struct K1Item {   // one (batch, head, chunk) work item
   int b, h, hq, t0, nvalid;   // hq: the q/k head this (value) head reads
   size_t rec_idx;
@@ -175,7 +166,6 @@ __global__ void __launch_bounds__(128, 4) kda_k1_kernel(const __grid_constant__ 
   }
 
   for (int it = 0; id < n_items; ++it, id += gridDim.x) {
-    K1_STAMP(0)
     const int b = cur.b, h = cur.h, t0 = cur.t0, nvalid = cur.nvalid;
     uint8_t* rec = p.rec + cur.rec_idx * REC_BYTES;
     const bool has_next = id + static_cast<int>(gridDim.x) < n_items;
@@ -186,13 +176,10 @@ __global__ void __launch_bounds__(128, 4) kda_k1_kernel(const __grid_constant__ 
     const float bias0 = par.bias0, bias1 = par.bias1;
     const float* sBeta = sBetaAll + (it & 1) * 16;
 
-    K1_STAMP(8)
     // every thread waits for the input copies itself (no CTA barrier here); a thread whose wait runs
     // out raises the flag, and the whole CTA leaves together behind the barrier that ends phase A
     const bool ok = mbar_wait_bounded(mbar, it & 1, sFlag);
-    K1_STAMP(9)
     if (!ok) *sFlag = 1;
-    K1_STAMP(1)
 
     // ---- phase A: l2-normalise q and k in place (8 threads per row, 16 elements each) ----
     if (use_l2 && ok) {
@@ -241,7 +228,6 @@ __global__ void __launch_bounds__(128, 4) kda_k1_kernel(const __grid_constant__ 
       __syncthreads();
       return;
     }
-    K1_STAMP(2)
 
     // ---- phase B: thread = (column pair, row half): gate, cumsum, gated operands ----
     // Two adjacent columns per thread: every bf16 conversion is the packed cvt.rn.bf16x2
@@ -322,7 +308,6 @@ __global__ void __launch_bounds__(128, 4) kda_k1_kernel(const __grid_constant__ 
           if (r0 + i < nvalid)
             *reinterpret_cast<float2*>(p.g_out + ((static_cast<size_t>(b) * p.T + t0 + r0 + i) * p.H + h) * D + c0) = gv[i];
       }
-      K1_STAMP(3)
 
       const float2 centre = FAST_EXP ? glast : gmid;
       const float2 ncentre = make_float2(-centre.x, -centre.y);
@@ -368,14 +353,12 @@ __global__ void __launch_bounds__(128, 4) kda_k1_kernel(const __grid_constant__ 
       }
     }
     __syncthreads();  // every thread has read its q/k/v/g elements: the input tiles are free
-    K1_STAMP(4)
 
     // ---- prefetch: the next item's inputs go into the same tiles while this one finishes ----
     if (has_next) {
       if (tid == 0) fence_proxy_async();   // order the earlier generic accesses (made visible by the barrier) before the async writes
       issue_loads(nxt);
     }
-    K1_STAMP(10)
 
     // ---- phase C: Grams on the tensor cores (one 16x8 output tile per warp) ----
     {
@@ -426,7 +409,6 @@ __global__ void __launch_bounds__(128, 4) kda_k1_kernel(const __grid_constant__ 
       }
     }
     __syncthreads();   // Grams done: their A tiles are free, -Akk is visible
-    K1_STAMP(5)
 
     // B operands of w and u take the place of the Gram A tiles
 #pragma unroll
@@ -464,17 +446,14 @@ __global__ void __launch_bounds__(128, 4) kda_k1_kernel(const __grid_constant__ 
         *reinterpret_cast<unsigned short*>(smem + S_XH + (i * 16 + lane) * 2) = bf16_bits(hi);
         *reinterpret_cast<unsigned short*>(smem + S_XL + (i * 16 + lane) * 2) = bf16_bits(x[i] - hi);
       }
-#ifndef KDA_K1_PROFILE
       if (p.ainv_out != nullptr) {
 #pragma unroll
         for (int i = 0; i < BT; ++i)
           if (i < nvalid) p.ainv_out[((static_cast<size_t>(b) * p.T + t0 + i) * p.H + h) * BT + lane] = x[i];
       }
-#endif
     }
     fence_proxy_async();   // qg / kg / Aqk / dec tiles were written with plain stores
     __syncthreads();
-    K1_STAMP(6)
 
     // the finished tiles leave while phase E runs
     if (tid == 0) {
@@ -531,7 +510,6 @@ __global__ void __launch_bounds__(128, 4) kda_k1_kernel(const __grid_constant__ 
       bulk_s2g(rec + REC_W, sbase + S_WST, TILE_BYTES);
       bulk_commit();
     }
-    K1_STAMP(7)
     cur = nxt;
     par = par_next;
   }
@@ -593,14 +571,15 @@ cudaError_t k1_encode_tensor_maps(K1Params& p, bool g_bf16, const char** what) {
       {&p.tm_g, p.g, p.g_s, g_bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32, g_bf16 ? 2 : 4, "g"}};
   for (const T& t : ts) {
     // dims innermost first: (d, head, token, batch); strides in bytes for dims 1..3.  A size-1
-    // dimension may come with any stride: give it a legal one (it is never stepped).
+    // dimension may come with any stride: give it a legal one (it is never stepped).  A zero
+    // stride on a larger dimension (an expanded view) is refused by the argument check.
     const bool qk = (t.m == &p.tm_q || t.m == &p.tm_k);
     const cuuint64_t dims[4] = {static_cast<cuuint64_t>(D), static_cast<cuuint64_t>(qk ? p.Hq : p.H),
                                 static_cast<cuuint64_t>(p.T), static_cast<cuuint64_t>(p.B)};
     cuuint64_t strides[3] = {static_cast<cuuint64_t>(t.s[2]) * t.es, static_cast<cuuint64_t>(t.s[1]) * t.es,
                              static_cast<cuuint64_t>(t.s[0]) * t.es};
     for (int i = 0; i < 3; ++i)
-      if (dims[i + 1] == 1 || strides[i] == 0) strides[i] = static_cast<cuuint64_t>(D) * t.es;
+      if (dims[i + 1] == 1) strides[i] = static_cast<cuuint64_t>(D) * t.es;
     const cuuint32_t box[4] = {static_cast<cuuint32_t>(D), 1, static_cast<cuuint32_t>(BT), 1};
     const cuuint32_t estr[4] = {1, 1, 1, 1};
     CUresult r = enc(t.m, t.dt, 4, const_cast<void*>(t.ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,

@@ -40,19 +40,7 @@
 
 namespace kda {
 
-#ifndef KDA_K2_STAGES
-#define KDA_K2_STAGES 4
-#endif
-constexpr int K2_STAGES = KDA_K2_STAGES;
-
-// Developer facility: with -DKDA_K2_PROFILE the first consumer warp of CTA 0 writes clock()
-// stamps of every step's phases to K2Params::ht (which then is NOT a state) -- 8 stamps/step.
-#ifdef KDA_K2_PROFILE
-#define K2_STAMP(i)                                                                              \
-  if (blockIdx.x == 0 && warp == 0 && lane == 0) reinterpret_cast<unsigned*>(p.ht)[n * 8 + (i)] = (unsigned)clock();
-#else
-#define K2_STAMP(i)
-#endif
+constexpr int K2_STAGES = 4;
 
 template <int CW, int NVT>
 struct K2Smem {
@@ -187,10 +175,8 @@ __global__ void __launch_bounds__((CW + 1) * 32, 1) kda_k2_kernel(const K2Params
       const int s = n % K2_STAGES;
       const uint32_t sp = sbase + s * SM::STAGE;
       const uint32_t t2 = sp + a2_lane;
-      K2_STAMP(0)
 
       // the previous step's output tile (always a full chunk)
-#ifndef KDA_K2_NO_OSTORE
       if (!STATE_ONLY && n > 0) {
         __nv_bfloat16* op = ob + static_cast<int64_t>((n - 1) * BT + gq) * p.o_s[1];
 #pragma unroll
@@ -199,7 +185,6 @@ __global__ void __launch_bounds__((CW + 1) * 32, 1) kda_k2_kernel(const K2Params
           *reinterpret_cast<uint32_t*>(op + 8 * p.o_s[1] + nv * 8) = pack_bf16(oa[nv][2], oa[nv][3]);
         }
       }
-#endif
 
       // B fragments of bf16(hT) (pre-chunk state): accumulator fragment -> pack -> 8x8 transpose
       uint32_t bh[8][NVT][2];
@@ -237,7 +222,6 @@ __global__ void __launch_bounds__((CW + 1) * 32, 1) kda_k2_kernel(const K2Params
         ldsm_x4(sp + a3_off, ah3[0], ah3[1], ah3[2], ah3[3]);
         ldsm_x4(sp + a3_off + (REC_AQL - REC_AQK), al3[0], al3[1], al3[2], al3[3]);
       }
-      K2_STAMP(1)
 
       // v_new (fp32, accumulator layout: rows tok, cols v) and its hi/lo B fragments
       uint32_t bvh[NVT][2], bvl[NVT][2];
@@ -274,7 +258,6 @@ __global__ void __launch_bounds__((CW + 1) * 32, 1) kda_k2_kernel(const K2Params
           break;
         }
       }
-      K2_STAMP(2)
 
       // P2: hT += kg^T v_new  (hi*hi, then hi*lo(v), then lo(kg)*hi: three passes over independent
       // tiles), carrying the next step's operand loads
@@ -300,7 +283,6 @@ __global__ void __launch_bounds__((CW + 1) * 32, 1) kda_k2_kernel(const K2Params
         if (!STATE_ONLY && more)
           ldsm_x4((t1n ^ (m << 5)) + REC_QG, aq[m][0], aq[m][1], aq[m][2], aq[m][3]);
       }
-      K2_STAMP(3)
 
       // P3: o = scale * (qg hT) + Aqk v_new
       if (!STATE_ONLY) {
@@ -318,10 +300,6 @@ __global__ void __launch_bounds__((CW + 1) * 32, 1) kda_k2_kernel(const K2Params
         for (int nv = 0; nv < NVT; ++nv)
           u[nv] = use_u ? *reinterpret_cast<const float4*>(spg1 + u_off + nv * REC_U_TILE_BYTES) : make_float4(0, 0, 0, 0);
       }
-      K2_STAMP(4)
-      K2_STAMP(5)
-      K2_STAMP(6)
-      K2_STAMP(7)
     }
 
     // the last chunk's output tile (it may be a partial chunk)
@@ -335,9 +313,6 @@ __global__ void __launch_bounds__((CW + 1) * 32, 1) kda_k2_kernel(const K2Params
       }
     }
 
-#ifdef KDA_K2_PROFILE
-    failed = true;   // ht holds clock stamps
-#endif
     if (!failed && p.ht != nullptr) {
       float* ht = p.ht + static_cast<size_t>(bh) * D * D;
 #pragma unroll
@@ -386,9 +361,6 @@ cudaError_t launch_k2n(const K2Params& p, int vsplit, int ntile, bool state_only
   KDA_K2_CASE(4, 1, 4)
   KDA_K2_CASE(8, 1, 2)
   KDA_K2_CASE(16, 1, 1)
-  KDA_K2_CASE(2, 2, 4)
-  KDA_K2_CASE(4, 2, 2)
-  KDA_K2_CASE(8, 2, 1)
 #undef KDA_K2_CASE
   return cudaErrorInvalidValue;
 }

@@ -45,10 +45,7 @@ constexpr int T_STAGE = 27648;
 constexpr int T_BARS = KT_STAGES * T_STAGE;
 // The state snapshot reaches the MMA thread in KT_PG column groups, so that the first k-steps of the
 // next P1 are issued while the element-wise warps still convert the rest of the state.
-#ifndef KDA_K2T_P1_GROUPS
-#define KDA_K2T_P1_GROUPS 2
-#endif
-constexpr int KT_PG = KDA_K2T_P1_GROUPS;
+constexpr int KT_PG = 2;
 static_assert(KT_PG == 1 || KT_PG == 2 || KT_PG == 4, "column groups of the snapshot");
 // barriers: full[S], empty[S], p1, v, p2, o, p3, s[KT_PG]
 constexpr int T_NBARS = 2 * KT_STAGES + 5 + KT_PG;
@@ -60,14 +57,6 @@ static_assert(T_OST % 16 == 0, "staging tiles are read 16 bytes at a time");
 constexpr uint32_t C_S = 0, C_D1 = 128, C_D3 = 160, C_AS = 176, C_VH = 240, C_VL = 248, C_TOTAL = 256;
 
 constexpr int ST_K2T_TIMEOUT = 4;
-
-// Developer facility: with -DKDA_K2T_PROFILE CTA 0 writes clock() stamps of every step to
-// K2Params::ht (which then is NOT a state): slots 0..7 by thread 0, 8..15 by the MMA thread.
-#ifdef KDA_K2T_PROFILE
-#define KT_STAMP(i) if (blockIdx.x == 0 && lane == 0 && (warp == 0 || warp == KT_EPI_WARPS + 1)) reinterpret_cast<unsigned*>(p.ht)[n * 16 + (i)] = (unsigned)clock();
-#else
-#define KT_STAMP(i)
-#endif
 
 // ---- tcgen05 wrappers ------------------------------------------------------------------------
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
@@ -267,7 +256,6 @@ __global__ void __launch_bounds__(KT_THREADS, 2) kda_k2t_kernel(const __grid_con
       for (int n = 0; n < NT; ++n, s = (s + 1 == KT_STAGES) ? 0 : s + 1) {
         const uint32_t st = sbase + s * T_STAGE;
         if (!mbar_wait_bounded(full(s), (n / KT_STAGES) & 1, sAbort)) { give_up(); break; }
-        KT_STAMP(8)
         const uint64_t dwq = smem_desc(st + T_WQ, 16, 1024, 2);   // k-step ks: start address + atom * 4096 + (ks % 4) * 32 bytes
         bool ready = true;
 #pragma unroll
@@ -275,7 +263,6 @@ __global__ void __launch_bounds__(KT_THREADS, 2) kda_k2t_kernel(const __grid_con
           // column group q of both halves of bf16(h) is in TMEM (with the last group: the decayed h too)
           if (!mbar_wait_bounded(bar_s(q), n & 1, sAbort)) { ready = false; break; }
           tc_fence_after();
-          if (q == 0) { KT_STAMP(9) }
 #pragma unroll
           for (int cc = q * (4 / KT_PG); cc < (q + 1) * (4 / KT_PG); ++cc)
 #pragma unroll
@@ -287,10 +274,8 @@ __global__ void __launch_bounds__(KT_THREADS, 2) kda_k2t_kernel(const __grid_con
         }
         if (!ready) { give_up(); break; }
         umma_commit(bar_p1);
-        KT_STAMP(10)
         if (!mbar_wait_bounded(bar_v, n & 1, sAbort)) { give_up(); break; }     // v_new hi/lo are in TMEM
         tc_fence_after();
-        KT_STAMP(11)
         const uint64_t dkh = smem_desc(st + T_KGH, 2048, 1024, 2), dkl = smem_desc(st + T_KGL, 2048, 1024, 2);
         umma_ts(tbase + C_S, tbase + C_VH, dkh, ID_P2, 1);
         umma_ts(tbase + C_S, tbase + C_VL, dkh, ID_P2, 1);
@@ -301,7 +286,6 @@ __global__ void __launch_bounds__(KT_THREADS, 2) kda_k2t_kernel(const __grid_con
         umma_ts(tbase + C_D3, tbase + C_VL, dah, ID_P3, 1);
         umma_ts(tbase + C_D3, tbase + C_VH, dal, ID_P3, 1);
         umma_commit(bar_p3);
-        KT_STAMP(12)
       }
     }
     __syncwarp();
@@ -394,10 +378,8 @@ __global__ void __launch_bounds__(KT_THREADS, 2) kda_k2t_kernel(const __grid_con
       const bool more = n + 1 < NT;
 
       // ---- E1: v_new = u - w h^T for this thread's row and eight tokens ----
-      KT_STAMP(0)
       if (!mbar_wait_bounded(bar_p1, n & 1, sAbort)) { ok = false; break; }
       tc_fence_after();
-      KT_STAMP(1)
       {
         uint32_t d1[8];
         tmem_ld8(tl + C_D1 + half * 8, d1);
@@ -416,18 +398,15 @@ __global__ void __launch_bounds__(KT_THREADS, 2) kda_k2t_kernel(const __grid_con
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(bar_v);
-      KT_STAMP(2)
 
       // while P2 runs: the next chunk's operands
 #pragma unroll
       for (int j = 0; j < 8; ++j) oq[j] = __uint_as_float(aq[j]);
       if (more && !prepare(n + 1)) { ok = false; break; }
-      KT_STAMP(5)
 
       // ---- E2: after P2 / P3 ----
       if (!mbar_wait_bounded(bar_p2, n & 1, sAbort)) { ok = false; break; }
       tc_fence_after();
-      KT_STAMP(3)
       // dec of the next chunk (its stage was waited for in prepare)
       const float* decn = reinterpret_cast<const float*>(smem + ((n + 1) % KT_STAGES) * T_STAGE + T_AQ + (REC_DEC - REC_AQK)) + half * 64;
       // the TMEM loads of the state are issued one 16-column step ahead of their use
@@ -480,9 +459,7 @@ __global__ void __launch_bounds__(KT_THREADS, 2) kda_k2t_kernel(const __grid_con
         for (int j = 0; j < 8; ++j) o3[j] = __uint_as_float(c3[j]);
       }
       if (!store_o(n)) { ok = false; break; }   // while the next P1 runs
-      KT_STAMP(4)
     }
-#ifndef KDA_K2T_PROFILE
     if (ok && p.ht != nullptr) {
       // final state: TMEM -> global through the 16-lane shape (32-byte pieces of the state's rows);
       // every element-wise thread has seen the last P2 complete
@@ -503,7 +480,6 @@ __global__ void __launch_bounds__(KT_THREADS, 2) kda_k2t_kernel(const __grid_con
         }
       }
     }
-#endif
     if (!ok) give_up();
   }
 

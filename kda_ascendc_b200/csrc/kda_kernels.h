@@ -73,8 +73,8 @@ cudaError_t launch_k1(const K1Params& p, bool g_bf16, bool fast_exp, cudaStream_
 // Fills the four tensor maps of p from its pointers, sizes and strides (host, no device work).
 cudaError_t k1_encode_tensor_maps(K1Params& p, bool g_bf16, const char** what);
 // Two organisations of K2 (same arithmetic, bit-identical results within one organisation):
-//   "n8"/"n16": state rows on the MMA N dimension, ntile (1 or 2) 8-row tiles per warp,
-//               16 / (vsplit * ntile) in {1, 2, 4} consumer warps per CTA      (kda_k2_sm100.cu)
+//   "n8":       state rows on the MMA N dimension, ntile = 1 tile of 8 rows per warp,
+//               16 / vsplit in {1, 2, 4} consumer warps per CTA                 (kda_k2_sm100.cu)
 //   "m16":      state rows on the MMA M dimension, 16 rows per warp,
 //               8 / vsplit in {1, 2, 4} consumer warps per CTA                 (kda_k2m_sm100.cu)
 // vsplit = CTAs per (batch, head).

@@ -20,8 +20,12 @@
 //     one stream, or otherwise ordered, are fine.  What a call left behind stays in the array:
 //     the status block at its start is cleared by every call, and the chunk records are always
 //     written by K1 before K2 reads them, so stale contents are never consumed.
+//   * A bounded device-side wait that gave up leaves its code in the status word at the start of
+//     the array; since the array's address never leaves the library, kda_fwd_static_scratch_status
+//     reads that word for the current device (kda_fwd_status needs a caller-owned workspace).
 //   * Neither this function nor anything it calls uses cudaMalloc, cudaFree, or an allocating
 //     library routine.
+#include <atomic>
 #include <cstdio>
 
 #include "../../include/kda_b200.h"
@@ -36,7 +40,36 @@ namespace {
 static __device__ __align__(256) unsigned char g_kda_scratch[KDA_STATIC_SCRATCH_BYTES];
 
 constexpr int kMaxDevices = 64;
-void* g_scratch_addr[kMaxDevices] = {};   // device address of g_kda_scratch, per device ordinal
+// device address of g_kda_scratch, per device ordinal.  Two host threads that make their first
+// call on one device at the same time both resolve the same address; the atomic only makes that
+// race well defined.
+std::atomic<void*> g_scratch_addr[kMaxDevices];
+
+// Address of the array on the current device (resolved once per device, with that device
+// current), or nullptr after setting the error text.
+void* scratch_on_current_device(int* rc) {
+  char msg[256];
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess || dev < 0 || dev >= kMaxDevices) {
+    kda::set_last_error("kda: cannot determine the current CUDA device");
+    *rc = KDA_ERR_CUDA;
+    return nullptr;
+  }
+  void* ptr = g_scratch_addr[dev].load(std::memory_order_acquire);
+  if (ptr == nullptr) {
+    // turn the host-side handle into the address the kernels can use
+    e = cudaGetSymbolAddress(&ptr, g_kda_scratch);
+    if (e != cudaSuccess || ptr == nullptr) {
+      snprintf(msg, sizeof(msg), "kda: cudaGetSymbolAddress(static scratch) failed: %s", cudaGetErrorString(e));
+      kda::set_last_error(msg);
+      *rc = KDA_ERR_CUDA;
+      return nullptr;
+    }
+    g_scratch_addr[dev].store(ptr, std::memory_order_release);
+  }
+  return ptr;
+}
 
 }  // namespace
 
@@ -46,40 +79,53 @@ extern "C" int kda_fwd_static_scratch(const KdaFwdArgs* args, void* stream) {
     kda::set_last_error("kda: args is NULL");
     return KDA_ERR_INVALID_ARG;
   }
-  // packed sequences hold one record per (chunk, head) of their chunk table
-  const size_t need = args->n_seqs > 0 ? kda_fwd_workspace_bytes(1, 16 * args->n_chunks, args->H)
-                                       : kda_fwd_workspace_bytes(args->B, args->T, args->H);
-  if (need == 0) {
-    kda::set_last_error("kda: B, T, H must be positive");
+  // The number of chunk records, in 64 bits: packed sequences hold one record per (chunk, head) of
+  // their chunk table, a fixed-length batch one per (batch, head, 16-token chunk).
+  unsigned long long chunks = 0;
+  if (args->n_seqs < 0) {
+    kda::set_last_error("kda: n_seqs must not be negative");
     return KDA_ERR_INVALID_ARG;
   }
-  if (need > static_cast<size_t>(KDA_STATIC_SCRATCH_BYTES)) {
+  if (args->n_seqs > 0) {
+    if (args->n_chunks <= 0 || args->H <= 0) {
+      kda::set_last_error("kda: packed sequences need positive n_chunks and H");
+      return KDA_ERR_INVALID_ARG;
+    }
+    chunks = static_cast<unsigned long long>(args->n_chunks);
+  } else {
+    if (args->B <= 0 || args->T <= 0 || args->H <= 0) {
+      kda::set_last_error("kda: B, T, H must be positive");
+      return KDA_ERR_INVALID_ARG;
+    }
+    chunks = static_cast<unsigned long long>(args->B) * ((static_cast<unsigned long long>(args->T) + kda::BT - 1) / kda::BT);
+  }
+  constexpr unsigned long long kMaxRecords =
+      (static_cast<unsigned long long>(KDA_STATIC_SCRATCH_BYTES) - kda::WS_HEADER_BYTES) / kda::REC_BYTES;
+  // chunks < 2^58 and H < 2^31 here; comparing chunks first keeps the product below 2^64
+  if (chunks > kMaxRecords || chunks * static_cast<unsigned long long>(args->H) > kMaxRecords) {
     snprintf(msg, sizeof(msg),
-             "kda: kda_fwd_static_scratch holds %lld bytes of scratch, this problem (B=%d T=%d H=%d) needs %lld; "
-             "use kda_fwd with a caller-provided workspace",
-             static_cast<long long>(KDA_STATIC_SCRATCH_BYTES), args->B, args->T, args->H, static_cast<long long>(need));
+             "kda: kda_fwd_static_scratch holds %lld bytes of scratch (%llu chunk records), this problem "
+             "(B=%d T=%d H=%d n_chunks=%d) needs %llu x %d records; use kda_fwd with a caller-provided workspace",
+             static_cast<long long>(KDA_STATIC_SCRATCH_BYTES), kMaxRecords, args->B, args->T, args->H, args->n_chunks,
+             chunks, args->H);
     kda::set_last_error(msg);
     return KDA_ERR_INVALID_ARG;
   }
-  int dev = 0;
-  cudaError_t e = cudaGetDevice(&dev);
-  if (e != cudaSuccess || dev < 0 || dev >= kMaxDevices) {
-    kda::set_last_error("kda: cannot determine the current CUDA device");
-    return KDA_ERR_CUDA;
+  int rc = KDA_OK;
+  void* scratch = scratch_on_current_device(&rc);
+  if (scratch == nullptr) return rc;
+  KdaFwdArgs local = *args;          // the caller's block is left untouched
+  local.workspace = scratch;         // whatever the caller put there is ignored
+  return kda_fwd(&local, stream);    // clears the status block, then K1 and K2
+}
+
+extern "C" int kda_fwd_static_scratch_status(void* stream, int32_t* status_out) {
+  if (status_out == nullptr) {
+    kda::set_last_error("kda: status_out is required");
+    return KDA_ERR_INVALID_ARG;
   }
-  if (g_scratch_addr[dev] == nullptr) {
-    // once per device, with that device current: turn the host-side handle into the address
-    // the kernels can use
-    void* ptr = nullptr;
-    e = cudaGetSymbolAddress(&ptr, g_kda_scratch);
-    if (e != cudaSuccess || ptr == nullptr) {
-      snprintf(msg, sizeof(msg), "kda: cudaGetSymbolAddress(static scratch) failed: %s", cudaGetErrorString(e));
-      kda::set_last_error(msg);
-      return KDA_ERR_CUDA;
-    }
-    g_scratch_addr[dev] = ptr;
-  }
-  KdaFwdArgs local = *args;                  // the caller's block is left untouched
-  local.workspace = g_scratch_addr[dev];     // whatever the caller put there is ignored
-  return kda_fwd(&local, stream);            // clears the status block, then K1 and K2
+  int rc = KDA_OK;
+  void* scratch = scratch_on_current_device(&rc);
+  if (scratch == nullptr) return rc;
+  return kda_fwd_status(scratch, stream, status_out);
 }

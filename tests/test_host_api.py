@@ -180,3 +180,37 @@ def test_k2_choice_table():
     var, vs = ctypes.c_int32(), ctypes.c_int32()
     assert lib.kda_fwd_k2_choice(ctypes.byref(a), 0, 148, ctypes.byref(var), ctypes.byref(vs)) != 0
     assert "k2_variant" in _lib.last_error()
+
+
+def test_static_scratch_argument_checks_are_host_only():
+    """kda_fwd_static_scratch sizes its request in 64 bits and refuses before touching CUDA."""
+    lib = _lib.load()
+    a = _lib.KdaFwdArgs()
+    a.B, a.T, a.H = 1, 16, 1
+    a.n_seqs, a.n_chunks = 1, 2 ** 27            # 16 * n_chunks would wrap a 32-bit T
+    assert lib.kda_fwd_static_scratch(ctypes.byref(a), None) == -1
+    assert "records" in _lib.last_error() and "use kda_fwd" in _lib.last_error()
+    a.n_chunks = 0
+    assert lib.kda_fwd_static_scratch(ctypes.byref(a), None) == -1
+    assert "n_chunks" in _lib.last_error()
+    a.n_seqs, a.B, a.T, a.H = 0, 2 ** 30, 2 ** 30, 2 ** 30
+    assert lib.kda_fwd_static_scratch(ctypes.byref(a), None) == -1
+    assert "use kda_fwd" in _lib.last_error()
+    a.n_seqs = -1
+    assert lib.kda_fwd_static_scratch(ctypes.byref(a), None) == -1
+    assert lib.kda_fwd_static_scratch_status(None, None) == -1
+    assert "status_out" in _lib.last_error()
+
+
+def test_expanded_views_are_refused():
+    """A zero stride on a dimension larger than one (q.expand(B, ...)) must not be read as dense."""
+    lib = _lib.load()
+    a = _lib.KdaFwdArgs()
+    a.B, a.T, a.H, a.g_dtype = 2, 16, 1, _lib.KDA_G_BF16
+    fake = ctypes.c_void_p(256 * 4096)            # never dereferenced: the checks are host-only
+    a.q = a.k = a.v = a.g = a.beta = a.workspace = fake
+    for f in ("q_stride", "k_stride", "v_stride", "g_stride"):
+        getattr(a, f)[0], getattr(a, f)[1], getattr(a, f)[2] = 16 * 128, 128, 128
+    a.q_stride[0] = 0                              # batch-expanded q
+    assert lib.kda_fwd_k1(ctypes.byref(a), None) == -1
+    assert "expanded" in _lib.last_error() and "q has" in _lib.last_error()

@@ -172,13 +172,12 @@ def test_all_state_slicings_agree(cuda_device):
 
     o_r, h_r = O.run_chunk_reference(inp)
     ref = {}
-    for var, vss in ((1, (4, 8, 16)), (2, (2, 4, 8)), (3, (2, 4, 8))):
+    for var, vss in ((1, (4, 8, 16)), (3, (2, 4, 8))):
         outs = [run(vs, var) for vs in vss]
         for o, ht in outs[1:]:
             assert torch.equal(o, outs[0][0]) and torch.equal(ht, outs[0][1]), (var, vss)
         ref[var] = outs[0]
         assert (outs[0][1].cpu() - h_r).abs().max().item() <= HT_TOL
-    assert torch.equal(ref[1][0], ref[2][0]) and torch.equal(ref[1][1], ref[2][1])      # n8 == n16
     assert (ref[3][0].float() - ref[1][0].float()).abs().max().item() <= 5e-3 * o_r.float().abs().max().item()
     assert (ref[3][1] - ref[1][1]).abs().max().item() <= 1e-4
     auto = run(0, 0)

@@ -59,6 +59,10 @@ def test_static_scratch_matches_kda_fwd_on_two_calls_in_a_row(cuda_device):
         # same kernels on the same inputs: the tolerance of the parity tests is met with zero error
         assert torch.equal(o_new, o_ref)
         assert torch.equal(h_new, h_ref)
+        # no bounded device-side wait gave up: the status word inside the library's array is clear
+        status = ctypes.c_int32(-1)
+        assert lib.kda_fwd_static_scratch_status(stream, ctypes.byref(status)) == 0, _lib.last_error()
+        assert status.value == 0
     # and the result is right, not just equal
     inp = O.make_inputs(2, 100, 2, seed0=52, regime="carry", h0_std=0.1)
     o_r, h_r = O.run_chunk_reference(inp)
