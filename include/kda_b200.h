@@ -116,9 +116,25 @@ int kda_fwd_k1(const KdaFwdArgs* args, void* stream);
 int kda_fwd_k2(const KdaFwdArgs* args, void* stream);
 
 /* State-only K2 pass for the sequence-parallel split: walks the records and
- * returns only the final state.  With zero_u != 0 the u term is dropped, so that
- * feeding h0 = I yields the segment's transition matrix. */
+ * returns only the final state.  zero_u = 0: the ordinary recurrence from h0.  zero_u = 1: the u
+ * term is dropped, so that feeding h0 = I yields the segment's transition matrix.  zero_u = 2:
+ * both transforms of the segment in ONE launch -- h0 is not read, ht is
+ * [B*H][2][128][128]: for every (batch, head) the transition matrix M (identity entry state, u
+ * dropped) followed by the offset Q (zero entry state), the layout kda_state_fold reads. */
 int kda_fwd_k2_state(const KdaFwdArgs* args, int zero_u, void* stream);
+
+/* Exchange step of the sequence split: walks the affine transforms S_out = S_in * M_j + Q_j of the
+ * n_seg segments of each of n_chains (batch, head) chains, in fp32:
+ *   S = h0[c] (zeros when h0 is NULL);  for j = 0..n_seg-1: s_in[j][c] = S;  S = S * M_j[c] + Q_j[c];
+ *   s_in[n_seg][c] = S
+ * mq: M_j[c] = 128 x 128 floats at mq + j * seg_stride + c * chain_stride, Q_j[c] directly behind it
+ * (strides in floats, so the buffer of an all-gather or of an all-to-all is read in place);
+ * s_in: [n_seg + 1][n_chains][128][128] fp32 contiguous; h0: [n_chains][128][128] or NULL.
+ * M_j is what kda_fwd_k2_state(zero_u = 1) returns from an identity entry state, Q_j what
+ * kda_fwd_k2_state(zero_u = 0) returns from a zero one.  No reference kernel: the reference only
+ * analyses the route (tools/probe_segment_affine.py:100-125, docs/SEGMENT_SCAN_ROUTE_A_EVAL.md:92-118). */
+int kda_state_fold(const float* mq, int64_t seg_stride, int64_t chain_stride, const float* h0, float* s_in,
+                   int32_t n_chains, int32_t n_seg, void* stream);
 
 /* Token-by-token recurrence for decode steps and short sequences (T of one to a few dozen
  * tokens): reads the state from args->h0 (NULL = zeros), applies args->T tokens, writes the

@@ -17,7 +17,7 @@ FLAG_GATE, FLAG_L2NORM, FLAG_BETA_SIGMOID = 1, 2, 4
 EXPORTS = (
     "kda_fwd_workspace_bytes", "kda_fwd", "kda_fwd_k1", "kda_fwd_k2", "kda_fwd_k2_state", "kda_recurrent_fwd",
     "kda_varlen_fill_tables", "kda_selftest_bounded_wait", "kda_fwd_static_scratch",
-    "kda_fwd_static_scratch_status",
+    "kda_fwd_static_scratch_status", "kda_state_fold",
     "kda_fwd_status", "kda_fwd_k2_choice", "kda_last_launch_count", "kda_last_error", "kda_version",
 )
 
@@ -59,6 +59,9 @@ def load() -> ctypes.CDLL:
         fn.argtypes = [ctypes.POINTER(KdaFwdArgs), ctypes.c_void_p]
     lib.kda_fwd_k2_state.restype = ctypes.c_int
     lib.kda_fwd_k2_state.argtypes = [ctypes.POINTER(KdaFwdArgs), ctypes.c_int, ctypes.c_void_p]
+    lib.kda_state_fold.restype = ctypes.c_int
+    lib.kda_state_fold.argtypes = [ctypes.c_void_p, ctypes.c_int64, ctypes.c_int64, ctypes.c_void_p, ctypes.c_void_p,
+                                   ctypes.c_int32, ctypes.c_int32, ctypes.c_void_p]
     lib.kda_selftest_bounded_wait.restype = ctypes.c_int
     lib.kda_selftest_bounded_wait.argtypes = [ctypes.c_void_p, ctypes.c_void_p]
     lib.kda_varlen_fill_tables.restype = ctypes.c_int

@@ -113,13 +113,13 @@ int check_k2(const KdaFwdArgs* a, bool state_only) {
 // (where the 16-row form needs two CTAs per chain and so more than one CTA per SM) it wins from
 // about 32 chunks per chain: 96 chains x 64 chunks 85 us against 92, x 16 equal.  It has no
 // state-only variant.
-void pick_split(const KdaFwdArgs* a, bool state_only, int* vsplit, int* variant, int sms = 0) {
+void pick_split(const KdaFwdArgs* a, bool state_only, int* vsplit, int* variant, int sms = 0, int chain_mult = 1) {
   if (sms <= 0) {   // the current device's SM count
     int dev = 0;
     sms = 148;
     if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   }
-  const long long bh = static_cast<long long>(a->n_seqs > 0 ? a->n_seqs : a->B) * a->H;
+  const long long bh = static_cast<long long>(a->n_seqs > 0 ? a->n_seqs : a->B) * a->H * chain_mult;
   // chunks per chain (the mean, for packed sequences)
   const long long steps = a->n_seqs > 0 ? a->n_chunks / a->n_seqs : (a->T + kda::BT - 1) / kda::BT;
   int var = a->k2_variant;
@@ -221,13 +221,19 @@ int do_k2(const KdaFwdArgs* a, bool state_only, int zero_u, cudaStream_t st) {
   p.B = a->B; p.T = a->T; p.H = a->H; p.NT = (a->T + kda::BT - 1) / kda::BT;
   for (int i = 0; i < 3; ++i) p.o_s[i] = a->o_stride[i];
   p.scale = a->scale;
-  p.zero_u = zero_u;
+  p.zero_u = zero_u == 1;
+  p.pair_mode = (state_only && zero_u == 2) ? 1 : 0;
   if (a->n_seqs > 0) {
     p.seq_table = reinterpret_cast<const int4*>(a->seq_table);
     p.n_seqs = a->n_seqs;
   }
+  if (p.pair_mode) {   // two chains per (batch, head): transition matrix and offset
+    const long long bh2 = 2LL * (a->n_seqs > 0 ? a->n_seqs : a->B) * a->H;
+    if (bh2 > 0x3fffffffLL) return fail(KDA_ERR_INVALID_ARG, "kda: too many chains%s", "");
+    p.n_chains = static_cast<int>(bh2);
+  }
   int vsplit = 4, variant = 3;
-  pick_split(a, state_only, &vsplit, &variant);
+  pick_split(a, state_only, &vsplit, &variant, 0, p.pair_mode ? 2 : 1);
   cudaError_t e;
   if (variant == 4) {
     const long long n_records = a->n_seqs > 0 ? static_cast<long long>(a->n_chunks) * a->H
@@ -309,6 +315,7 @@ int kda_fwd_k2_state(const KdaFwdArgs* a, int zero_u, void* stream) {
   g_launches = 0;
   if (int rc = check_k2(a, true)) return rc;
   if (a->ht == nullptr) return fail(KDA_ERR_INVALID_ARG, "kda: the state-only pass needs ht%s", "");
+  if (zero_u < 0 || zero_u > 2) return fail(KDA_ERR_INVALID_ARG, "kda: zero_u must be 0, 1 or 2%s (got %lld)", "", zero_u);
   return do_k2(a, true, zero_u, static_cast<cudaStream_t>(stream));
 }
 
@@ -354,6 +361,27 @@ int kda_recurrent_fwd(const KdaFwdArgs* a, void* stream) {
   if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   cudaError_t e = kda::launch_recurrent(p, a->g_dtype == KDA_G_BF16, sms, static_cast<cudaStream_t>(stream));
   if (e != cudaSuccess) return fail(KDA_ERR_CUDA, "kda: recurrent launch failed: %s", cudaGetErrorString(e));
+  ++g_launches;
+  return KDA_OK;
+}
+
+int kda_state_fold(const float* mq, int64_t seg_stride, int64_t chain_stride, const float* h0, float* s_in,
+                   int32_t n_chains, int32_t n_seg, void* stream) {
+  g_launches = 0;
+  if (mq == nullptr || s_in == nullptr) return fail(KDA_ERR_INVALID_ARG, "kda: the fold needs mq and s_in%s", "");
+  if (n_chains <= 0 || n_seg < 0)
+    return fail(KDA_ERR_INVALID_ARG, "kda: the fold needs n_chains > 0 and n_seg >= 0%s (got %lld, %lld)", "", n_chains, n_seg);
+  const int64_t pair = 2LL * kda::D * kda::D;
+  if (n_seg > 0 && (chain_stride < pair || (n_seg > 1 && seg_stride < pair)))
+    return fail(KDA_ERR_INVALID_ARG, "kda: the fold's strides must span an (M, Q) pair of 2 x 128 x 128 floats%s", "");
+  for (const void* ptr : {static_cast<const void*>(mq), static_cast<const void*>(h0), static_cast<const void*>(s_in)})
+    if (ptr != nullptr && reinterpret_cast<uintptr_t>(ptr) % 16 != 0)
+      return fail(KDA_ERR_INVALID_ARG, "kda: mq, h0 and s_in must be 16-byte aligned%s", "");
+  if (static_cast<long long>(n_chains) * (kda::D / 4) > 0x7fffffffLL)
+    return fail(KDA_ERR_INVALID_ARG, "kda: too many chains for one fold launch%s", "");
+  cudaError_t e = kda::launch_state_fold(mq, seg_stride, chain_stride, h0, s_in, n_chains, n_seg,
+                                         static_cast<cudaStream_t>(stream));
+  if (e != cudaSuccess) return fail(KDA_ERR_CUDA, "kda: fold launch failed: %s", cudaGetErrorString(e));
   ++g_launches;
   return KDA_OK;
 }

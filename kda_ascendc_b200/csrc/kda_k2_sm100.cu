@@ -59,7 +59,10 @@ __global__ void __launch_bounds__((CW + 1) * 32, 1) kda_k2_kernel(const K2Params
   const int tid = threadIdx.x;
   const int lane = tid & 31;
   const int warp = tid >> 5;
-  const int bh = blockIdx.x / NV + p.chain0;
+  const int chain = blockIdx.x / NV + p.chain0;
+  const bool pair = STATE_ONLY && p.pair_mode != 0;
+  const int bh = pair ? (chain >> 1) : chain;      // the (batch, head) whose records are walked
+  const int plane = pair ? (chain & 1) : 1;        // pair mode: 0 = transition matrix, 1 = offset
   const int vs = blockIdx.x % NV;
   int b = bh / p.H;
   const int h = bh % p.H;
@@ -118,7 +121,15 @@ __global__ void __launch_bounds__((CW + 1) * 32, 1) kda_k2_kernel(const K2Params
     const int v0 = vs * VCOLS + warp * (NVT * 8);   // first state row of this warp
     // hT[m][nv][e]: k = 16m + gq (+8 for e >= 2), v = v0 + 8nv + 2tq + (e & 1)
     float hT[8][NVT][4];
-    if (p.h0 != nullptr) {
+    if (pair) {
+#pragma unroll
+      for (int m = 0; m < 8; ++m)
+#pragma unroll
+        for (int nv = 0; nv < NVT; ++nv)
+#pragma unroll
+          for (int e = 0; e < 4; ++e)
+            hT[m][nv][e] = (plane == 0 && (v0 + nv * 8 + tq * 2 + (e & 1)) == (m * 16 + gq + (e >> 1) * 8)) ? 1.f : 0.f;
+    } else if (p.h0 != nullptr) {
       const float* h0 = p.h0 + static_cast<size_t>(bh) * D * D;
 #pragma unroll
       for (int m = 0; m < 8; ++m)
@@ -146,7 +157,7 @@ __global__ void __launch_bounds__((CW + 1) * 32, 1) kda_k2_kernel(const K2Params
     const uint32_t a1_lane = swz_off(a1_row, a1_col), a2_lane = swz_off(a2_row, a2_col);
     const uint32_t u_off = REC_SHARED_BYTES + warp * (NVT * REC_U_TILE_BYTES) + lane * 16;
     __nv_bfloat16* const ob = STATE_ONLY ? nullptr : p.o + b * p.o_s[0] + tok0 * p.o_s[1] + h * p.o_s[2] + v0 + tq * 2;
-    const bool use_u = !(STATE_ONLY && p.zero_u);
+    const bool use_u = pair ? (plane == 1) : !(STATE_ONLY && p.zero_u);
 
     uint32_t aw[8][4], aq[8][4];     // A fragments of w and qg (one per 16-wide k-step)
     float dk[8][2];                  // decay of the rows k = 16m+gq and 16m+gq+8
@@ -314,7 +325,7 @@ __global__ void __launch_bounds__((CW + 1) * 32, 1) kda_k2_kernel(const K2Params
     }
 
     if (!failed && p.ht != nullptr) {
-      float* ht = p.ht + static_cast<size_t>(bh) * D * D;
+      float* ht = p.ht + static_cast<size_t>(chain) * D * D;
 #pragma unroll
       for (int m = 0; m < 8; ++m)
 #pragma unroll

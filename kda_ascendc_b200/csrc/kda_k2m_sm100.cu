@@ -46,7 +46,10 @@ __global__ void __launch_bounds__((CW + 1) * 32, MINB) kda_k2m_kernel(const K2Pa
   const int tid = threadIdx.x;
   const int lane = tid & 31;
   const int warp = tid >> 5;
-  const int bh = blockIdx.x / NV + p.chain0;
+  const int chain = blockIdx.x / NV + p.chain0;
+  const bool pair = STATE_ONLY && p.pair_mode != 0;
+  const int bh = pair ? (chain >> 1) : chain;      // the (batch, head) whose records are walked
+  const int plane = pair ? (chain & 1) : 1;        // pair mode: 0 = transition matrix, 1 = offset
   const int vs = blockIdx.x % NV;
   int b = bh / p.H;
   const int h = bh % p.H;
@@ -105,7 +108,13 @@ __global__ void __launch_bounds__((CW + 1) * 32, MINB) kda_k2m_kernel(const K2Pa
     const int vrow0 = (vs * CW + warp) * 16;
     // hs[nt][e]: v = vrow0 + gq (+8 for e >= 2), k = 8nt + 2tq + (e & 1)
     float hs[16][4];
-    if (p.h0 != nullptr) {
+    if (pair) {
+#pragma unroll
+      for (int nt = 0; nt < 16; ++nt)
+#pragma unroll
+        for (int e = 0; e < 4; ++e)
+          hs[nt][e] = (plane == 0 && (vrow0 + gq + (e >> 1) * 8) == (nt * 8 + tq * 2 + (e & 1))) ? 1.f : 0.f;
+    } else if (p.h0 != nullptr) {
       const float* h0 = p.h0 + static_cast<size_t>(bh) * D * D;
 #pragma unroll
       for (int nt = 0; nt < 16; ++nt) {
@@ -128,7 +137,7 @@ __global__ void __launch_bounds__((CW + 1) * 32, MINB) kda_k2m_kernel(const K2Pa
     // element (v = vrow0 + gq + 8a, tok = 2tq + j + 8c)  ->  tile 2*warp + a, lane (2tq+j)*4 + gq/2, slot 2c + gq%2
     const uint32_t u_off = REC_SHARED_BYTES + (warp * 2) * REC_U_TILE_BYTES + ((tq * 2) * 4 + (gq >> 1)) * 16 + (gq & 1) * 4;
     __nv_bfloat16* const ob = STATE_ONLY ? nullptr : p.o + b * p.o_s[0] + tok0 * p.o_s[1] + h * p.o_s[2] + vrow0 + tq * 2;
-    const bool use_u = !(STATE_ONLY && p.zero_u);
+    const bool use_u = pair ? (plane == 1) : !(STATE_ONLY && p.zero_u);
 
     // rolling B fragments of P1: two k-steps ahead
     uint32_t bw[2][4], bq[2][4];
@@ -310,7 +319,7 @@ __global__ void __launch_bounds__((CW + 1) * 32, MINB) kda_k2m_kernel(const K2Pa
     }
 
     if (!failed && p.ht != nullptr) {
-      float* ht = p.ht + static_cast<size_t>(bh) * D * D;
+      float* ht = p.ht + static_cast<size_t>(chain) * D * D;
 #pragma unroll
       for (int nt = 0; nt < 16; ++nt) {
         *reinterpret_cast<float2*>(ht + (vrow0 + gq) * D + nt * 8 + tq * 2) = make_float2(hs[nt][0], hs[nt][1]);

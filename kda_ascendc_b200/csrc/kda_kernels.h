@@ -61,6 +61,10 @@ struct K2Params {
   int64_t o_s[3];
   float scale;
   int zero_u;        // state-only mode: drop the u term
+  // state-only "transform pair" mode: the launch runs 2 x chains; chain 2c starts from the identity
+  // with u dropped (M of the segment), chain 2c+1 from zero with u (Q); h0 is not read and ht is
+  // [chains][2][128][128]
+  int pair_mode;
   // packed variable-length input: one entry per sequence (first token, chunks, first record,
   // length); the grid then runs over (sequence, head); null for a fixed-length batch
   const int4* seq_table;
@@ -83,6 +87,10 @@ cudaError_t launch_k2m(const K2Params& p, int vsplit, bool state_only, cudaStrea
 //   "tc":       the whole 128-row state of a head in tensor memory, tcgen05 MMAs, one CTA per
 //               (batch, head), two CTAs per SM; outputs + final state only              (kda_k2t_sm100.cu)
 cudaError_t launch_k2t(const K2Params& p, long long n_records, cudaStream_t stream);
+
+// Walk of the per-segment affine state transforms of a sequence split (kda_fold_sm100.cu).
+cudaError_t launch_state_fold(const float* mq, long long seg_stride, long long chain_stride, const float* h0,
+                              float* s_in, int n_chains, int n_seg, cudaStream_t stream);
 
 // Token recurrence (decode / short sequences): no chunking, no workspace (kda_recurrent_sm100.cu).
 struct RecurrentParams {

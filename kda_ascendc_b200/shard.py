@@ -12,11 +12,16 @@ Two ways to spread one problem over the GPUs of a box:
   (V-first ``S`` is ``[V, K]``, ``M_seg`` is ``[K, K]``).  Rank ``j`` runs K1 on its
   contiguous segment once, then two state-only passes over the same chunk records:
   ``Q_seg`` is the final state from a zero state, ``M_seg`` the final state from the
-  identity with the ``u`` term dropped.  One all-gather of ``(M_seg, Q_seg)`` (fp32,
-  ``2 x 64 KiB`` per head) lets every rank fold the segments before it,
-  ``S_in[j] = (((h0 M_0 + Q_0) M_1 + Q_1) ...)`` in fp32, and a last ordinary K2 pass with
-  that entry state produces the rank's outputs.  Received tiles land in local memory first;
-  the exchange is NCCL on GPUs and works unchanged over gloo on CPU tensors.
+  identity with the ``u`` term dropped (one launch computes both).  The fold
+  ``S_in[j] = (((h0 M_0 + Q_0) M_1 + Q_1) ...)`` is a hand-written fp32 kernel
+  (``kda_state_fold``).  Two exchange patterns: **all-to-all** (default when the chains divide
+  over the ranks) -- rank ``r`` folds chains ``[r*hp, (r+1)*hp)`` of ALL segments and sends
+  every segment its entry states back, ``2 x 64 KiB`` per chain and hop instead of every
+  rank receiving every transform; **all-gather** -- every rank receives all transforms and
+  folds the segments before its own.  A last ordinary K2 pass from the entry state produces
+  the rank's outputs.  Received tiles land in local memory first; the exchange is NCCL on
+  GPUs and works unchanged over gloo on CPU tensors (with a caller-supplied fold).
+  ``SeqParallelPlan`` allocates every buffer, stream and argument block once.
 """
 from __future__ import annotations
 
@@ -70,11 +75,12 @@ def forward_head_shard(q, k, v, g, beta, *, rank: int, world: int, scale=None, i
 # ---------------------------------------------------------------------------
 def compose_entry_states(M: Sequence[torch.Tensor], Q: Sequence[torch.Tensor],
                          h0: Optional[torch.Tensor]) -> list[torch.Tensor]:
-    """Entry state of every segment and the state after the last one.
+    """Entry state of every segment and the state after the last one, by plain torch matmuls.
 
-    ``M[j]``, ``Q[j]``: ``[B, H, 128, 128]`` fp32 transforms of segment ``j``
-    (``S_out = S_in @ M + Q``).  Returns ``G + 1`` tensors: ``S_in[0..G-1]`` and the final state.
-    Plain fp32 matmuls (TF32 off): the fold is 128^3 per head and segment, off the hot path.
+    ``M[j]``, ``Q[j]``: ``[..., 128, 128]`` fp32 transforms of segment ``j``
+    (``S_out = S_in @ M + Q``).  Returns ``G + 1`` tensors.  This is the host-side statement of
+    what ``kda_state_fold`` computes on the GPU; the GPU paths below use the kernel, this
+    function serves CPU tensors (the gloo tests) and cross-checks.
     """
     S = torch.zeros_like(Q[0]) if h0 is None else h0.to(torch.float32)
     out = [S]
@@ -89,21 +95,106 @@ def compose_entry_states(M: Sequence[torch.Tensor], Q: Sequence[torch.Tensor],
     return out
 
 
-def exchange_segment_transforms(M_local: torch.Tensor, Q_local: torch.Tensor, group=None):
-    """All-gather of the per-rank ``(M_seg, Q_seg)``; returns two lists of ``world`` tensors."""
+def fold_states(mq: torch.Tensor, h0: Optional[torch.Tensor], out: Optional[torch.Tensor] = None,
+                n_seg: Optional[int] = None) -> torch.Tensor:
+    """``kda_state_fold`` on a CUDA tensor ``mq [n_seg_total, n_chains, 2, 128, 128]`` (fp32; ``M`` then
+    ``Q`` per chain, any segment / chain strides): returns ``s_in [n_seg + 1, n_chains, 128, 128]`` --
+    the entry state of segments ``0..n_seg-1`` and the state after segment ``n_seg - 1``
+    (``n_seg`` defaults to all segments of ``mq``)."""
+    if not mq.is_cuda:
+        raise RuntimeError("fold_states runs the CUDA kernel kda_state_fold; there is no CPU path")
+    if mq.dtype != torch.float32 or mq.ndim != 5 or mq.shape[2:] != (2, D, D) or mq.stride()[2:] != (D * D, D, 1):
+        raise ValueError("mq must be fp32 [segments, chains, 2, 128, 128] with dense (M, Q) pairs")
+    segs, chains = mq.shape[:2]
+    n_seg = segs if n_seg is None else n_seg
+    if not 0 <= n_seg <= segs:
+        raise ValueError(f"n_seg={n_seg} outside 0..{segs}")
+    if out is None:
+        out = torch.empty((n_seg + 1, chains, D, D), dtype=torch.float32, device=mq.device)
+    elif out.shape != (n_seg + 1, chains, D, D) or not out.is_contiguous() or out.dtype != torch.float32:
+        raise ValueError("out must be a contiguous fp32 [n_seg + 1, chains, 128, 128] tensor")
+    if h0 is not None:
+        h0 = h0.reshape(chains, D, D)
+        if h0.dtype != torch.float32 or not h0.is_contiguous():
+            raise ValueError("h0 must be contiguous fp32 [chains, 128, 128]")
+    with torch.cuda.device(mq.device):
+        api._check(_lib.load().kda_state_fold(ctypes.c_void_p(mq.data_ptr()), mq.stride(0), mq.stride(1),
+                                              None if h0 is None else ctypes.c_void_p(h0.data_ptr()),
+                                              ctypes.c_void_p(out.data_ptr()), chains, n_seg, api._stream_handle()))
+    return out
+
+
+def _torch_fold(mq, h0, out=None, n_seg=None):
+    """Same contract as :func:`fold_states` in plain torch (CPU tensors: the gloo tests)."""
+    n_seg = mq.shape[0] if n_seg is None else n_seg
+    st = compose_entry_states([mq[j, :, 0] for j in range(n_seg)], [mq[j, :, 1] for j in range(n_seg)],
+                              torch.zeros_like(mq[0, :, 0]) if h0 is None else h0.reshape(mq.shape[1], D, D))
+    res = torch.stack(st)
+    if out is not None:
+        out.copy_(res)
+        return out
+    return res
+
+
+def exchange_mode(chains: int, world: int, requested: str = "auto") -> str:
+    """``"a2a"`` (all-to-all, chains divided over the ranks) or ``"gather"``."""
+    if requested not in ("auto", "a2a", "gather"):
+        raise ValueError("exchange must be 'auto', 'a2a' or 'gather'")
+    if requested == "a2a" and chains % world:
+        raise ValueError(f"the all-to-all exchange needs the {chains} chains to divide over {world} ranks")
+    if requested == "auto":
+        return "a2a" if chains % world == 0 else "gather"
+    return requested
+
+
+def exchange_and_fold(mq_local: torch.Tensor, h0: Optional[torch.Tensor], rank: int, world: int, *, group=None,
+                      mode: str = "a2a", fold=None, bufs: Optional[dict] = None, want_final: bool = False):
+    """From this rank's ``mq_local [chains, 2, 128, 128]`` to the entry state of its segment.
+
+    Returns ``(s_entry [chains, 128, 128], final | None)``; ``final`` is the state after the last
+    segment, ``[chains, 128, 128]``, on every rank when ``want_final`` (one more small all-gather in
+    all-to-all mode).  ``bufs``: optional dict the function keeps its receive / send buffers in, so a
+    plan allocates them once.  ``fold``: the fold routine (default: the CUDA kernel).
+    """
     import torch.distributed as dist
 
-    world = dist.get_world_size(group)
-    packed = torch.stack([M_local, Q_local]).contiguous()
-    gathered = [torch.empty_like(packed) for _ in range(world)]
-    dist.all_gather(gathered, packed, group=group)
-    return [t[0] for t in gathered], [t[1] for t in gathered]
+    fold = fold_states if fold is None else fold
+    bufs = {} if bufs is None else bufs
+    chains = mq_local.shape[0]
+    kw = dict(dtype=torch.float32, device=mq_local.device)
+    h0c = None if h0 is None else h0.reshape(chains, D, D)
+
+    def buf(name, shape):
+        t = bufs.get(name)
+        if t is None or tuple(t.shape) != tuple(shape):
+            t = bufs[name] = torch.empty(shape, **kw)
+        return t
+
+    if mode == "gather":
+        allmq = buf("gathered", (world, chains, 2, D, D))
+        dist.all_gather_into_tensor(allmq.view(world * chains, 2, D, D), mq_local.contiguous(), group=group)
+        n_seg = world if want_final else rank
+        s_in = fold(allmq, h0c, out=buf("s_in", (n_seg + 1, chains, D, D)), n_seg=n_seg)
+        return s_in[rank], (s_in[world] if want_final else None)
+    hp = chains // world
+    recv = buf("recv_mq", (world, hp, 2, D, D))            # [segment][my chains]
+    dist.all_to_all_single(recv, mq_local.contiguous().view(world, hp, 2, D, D), group=group)
+    s_in = fold(recv, None if h0c is None else h0c[rank * hp:(rank + 1) * hp], out=buf("s_in", (world + 1, hp, D, D)))
+    entry = buf("entry", (world, hp, D, D))                # [owner of the chains][chains] = all chains in order
+    dist.all_to_all_single(entry, s_in[:world], group=group)
+    final = None
+    if want_final:
+        final = buf("final", (world, hp, D, D))
+        dist.all_gather_into_tensor(final.view(chains, D, D), s_in[world].contiguous(), group=group)
+        final = final.view(chains, D, D)
+    return entry.view(chains, D, D), final
 
 
 class _Segment:
-    """K1 records of one contiguous token segment plus what is needed to re-run K2 on them."""
+    """One contiguous token segment: fixed buffers and argument blocks for K1, the transform pass
+    (both transforms in one launch) and the ordinary K2 pass."""
 
-    def __init__(self, q, k, v, g, beta, scale, lower_bound, A_log, dt_bias):
+    def __init__(self, q, k, v, g, beta, scale, lower_bound, A_log, dt_bias, mq_out=None):
         api._validate_kda_inputs(q, k, v, g, beta, None, True, True, lower_bound, A_log, dt_bias, True,
                                  require_contiguous=False)
         api._require_cuda(q)
@@ -111,91 +202,114 @@ class _Segment:
         if self.T % api.BT:
             raise ValueError("a sequence segment must be a whole number of 16-token chunks, got T=%d" % self.T)
         self.dev = q.device
+        self.chains = self.B * self.H
         self.lib = _lib.load()
+        kw = dict(dtype=torch.float32, device=self.dev)
         self.ws = torch.empty(api.workspace_bytes(self.B, self.T, self.H), dtype=torch.uint8, device=self.dev)
         self.o = torch.empty((self.B, self.T, self.H, D), dtype=torch.bfloat16, device=self.dev)
-        self.ht = torch.empty((self.B, self.H, D, D), dtype=torch.float32, device=self.dev)
-        self.keep = (q, k, v, g, beta, A_log, dt_bias)   # the argument block holds raw pointers
+        self.ht = torch.empty((self.B, self.H, D, D), **kw)
+        self.mq = torch.empty((self.chains, 2, D, D), **kw) if mq_out is None else mq_out
+        if tuple(self.mq.shape) != (self.chains, 2, D, D) or not self.mq.is_contiguous():
+            raise ValueError("mq_out must be a contiguous [B*H, 2, 128, 128] fp32 tensor")
+        self.keep = (q, k, v, g, beta, A_log, dt_bias)   # the argument blocks hold raw pointers
         self.args = api.make_args(q, k, v, g, beta, scale=scale, lower_bound=lower_bound, A_log=A_log,
                                   dt_bias=dt_bias, h0=None, o=self.o, ht=self.ht, workspace=self.ws, flags=7)
-        self.stream = api._stream_handle()
+        self.args_mq = _lib.KdaFwdArgs.from_buffer_copy(self.args)
+        self.args_mq.h0 = None
+        self.args_mq.ht = ctypes.c_void_p(self.mq.data_ptr())
+        self._s_in = None
+
+    def k1(self, stream=None):
         with torch.cuda.device(self.dev):
-            api._check(self.lib.kda_fwd_k1(ctypes.byref(self.args), self.stream))
+            api._check(self.lib.kda_fwd_k1(ctypes.byref(self.args), api._stream_handle() if stream is None else stream))
 
-    def _with_state(self, h0, ht):
-        self.args.h0 = None if h0 is None else ctypes.c_void_p(h0.data_ptr())
-        self.args.ht = ctypes.c_void_p(ht.data_ptr())
-
-    def transforms(self):
-        """(M_seg, Q_seg): two state-only passes over the records.  They are independent (same records,
-        different entry state), and one pass leaves most of the GPU idle (a chain per head), so the second
-        runs beside the first on a side stream."""
-        eye = torch.eye(D, device=self.dev, dtype=torch.float32).expand(self.B, self.H, D, D).contiguous()
-        M = torch.empty_like(eye)
-        Q = torch.empty_like(eye)
-        cur = torch.cuda.current_stream(self.dev)
-        side = torch.cuda.Stream(device=self.dev)
-        args_m = _lib.KdaFwdArgs.from_buffer_copy(self.args)
-        args_m.h0 = ctypes.c_void_p(eye.data_ptr())
-        args_m.ht = ctypes.c_void_p(M.data_ptr())
+    def transforms(self, stream=None):
+        """(M_seg, Q_seg) of every chain into ``self.mq``: one state-only launch over 2 x chains."""
         with torch.cuda.device(self.dev):
-            side.wait_stream(cur)                      # K1's records (and eye) are ready
-            api._check(self.lib.kda_fwd_k2_state(ctypes.byref(args_m), 1, ctypes.c_void_p(side.cuda_stream)))
-            self._with_state(None, Q)
-            api._check(self.lib.kda_fwd_k2_state(ctypes.byref(self.args), 0, ctypes.c_void_p(cur.cuda_stream)))
-            cur.wait_stream(side)
-        self._eye = eye   # stays alive until the launches that read it have been ordered
-        return M, Q
+            api._check(self.lib.kda_fwd_k2_state(ctypes.byref(self.args_mq), 2,
+                                                 api._stream_handle() if stream is None else stream))
+        return self.mq
 
-    def outputs(self, S_in):
+    def outputs(self, S_in, stream=None):
         """Ordinary K2 pass from the true entry state: (o, state after the segment)."""
-        S_in = None if S_in is None else S_in.contiguous()
+        if S_in is not None and not (S_in.is_contiguous() and S_in.dtype == torch.float32):
+            S_in = S_in.contiguous().float()
+        self._s_in = S_in   # keep the entry state alive until the launch has been ordered
+        self.args.h0 = None if S_in is None else ctypes.c_void_p(S_in.data_ptr())
         with torch.cuda.device(self.dev):
-            self._with_state(S_in, self.ht)
-            api._check(self.lib.kda_fwd_k2(ctypes.byref(self.args), self.stream))
-        self._s_in = S_in
+            api._check(self.lib.kda_fwd_k2(ctypes.byref(self.args), api._stream_handle() if stream is None else stream))
         return self.o, self.ht
 
 
-def forward_seq_parallel(q, k, v, g, beta, *, scale=None, initial_state=None, lower_bound=-5.0,
-                         A_log=None, dt_bias=None, group=None):
-    """This rank's contiguous token segment of one long sequence (segments in rank order).
+class SeqParallelPlan:
+    """This rank's contiguous token segment of one long sequence, everything allocated once.
 
-    ``q, k, v, g, beta`` hold the local ``T / world`` tokens (a multiple of 16);
-    ``initial_state`` is the state before the FIRST segment (same tensor on every rank).
-    Returns ``(o_local, final_state)``; ``final_state`` is the state after the LAST segment on
-    every rank.  In-kernel gate, l2-norm and beta sigmoid, V-first state.
+    ``q, k, v, g, beta`` hold the local ``T / world`` tokens (a multiple of 16; views are fine) and are
+    re-read by every :meth:`run`; ``initial_state`` is the state before the FIRST segment (same
+    tensor on every rank).  :meth:`run` launches K1, the transform pass, the exchange + fold and the
+    final K2 on the current stream and returns ``(o_local, final_state)``: the state after the LAST
+    segment on the last rank (from its own K2 pass), on every rank with ``final_state_on_all_ranks``,
+    else ``None``.  In-kernel gate, l2-norm and beta sigmoid, V-first state.
     """
-    import torch.distributed as dist
 
-    if scale is None:
-        scale = D ** -0.5
-    rank, world = dist.get_rank(group), dist.get_world_size(group)
-    seg = _Segment(q, k, v, g, beta, scale, lower_bound, A_log, dt_bias)
-    if world == 1:
-        o, ht = seg.outputs(initial_state)
-        return o, ht.clone()
-    M, Q = seg.transforms()
-    Ms, Qs = exchange_segment_transforms(M, Q, group)
-    states = compose_entry_states(Ms, Qs, initial_state)
-    o, _ = seg.outputs(states[rank] if (rank > 0 or initial_state is not None) else None)
-    return o, states[world]
+    def __init__(self, q, k, v, g, beta, *, scale=None, initial_state=None, lower_bound=-5.0, A_log=None,
+                 dt_bias=None, group=None, exchange="auto", final_state_on_all_ranks=False):
+        import torch.distributed as dist
+
+        self.group = group
+        self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
+        self.seg = _Segment(q, k, v, g, beta, D ** -0.5 if scale is None else scale, lower_bound, A_log, dt_bias)
+        self.h0 = None if initial_state is None else initial_state.contiguous().float()
+        self.mode = exchange_mode(self.seg.chains, self.world, exchange)
+        self.want_final = bool(final_state_on_all_ranks)
+        self.bufs: dict = {}
+
+    def run(self):
+        seg = self.seg
+        seg.k1()
+        if self.world == 1:
+            o, ht = seg.outputs(self.h0)
+            return o, ht
+        mq = seg.transforms()
+        entry, final = exchange_and_fold(mq, self.h0, self.rank, self.world, group=self.group, mode=self.mode,
+                                         bufs=self.bufs, want_final=self.want_final)
+        o, ht = seg.outputs(entry.view(seg.B, seg.H, D, D))
+        if self.want_final:
+            return o, final.view(seg.B, seg.H, D, D)
+        return o, (ht if self.rank == self.world - 1 else None)
+
+
+def forward_seq_parallel(q, k, v, g, beta, *, scale=None, initial_state=None, lower_bound=-5.0,
+                         A_log=None, dt_bias=None, group=None, exchange="auto"):
+    """One-shot form of :class:`SeqParallelPlan`: returns ``(o_local, final_state)`` with the state
+    after the LAST segment on every rank."""
+    plan = SeqParallelPlan(q, k, v, g, beta, scale=scale, initial_state=initial_state, lower_bound=lower_bound,
+                           A_log=A_log, dt_bias=dt_bias, group=group, exchange=exchange,
+                           final_state_on_all_ranks=True)
+    o, ht = plan.run()
+    return o, ht.clone()
 
 
 def forward_seq_split_local(q, k, v, g, beta, n_segments: int, *, scale=None, initial_state=None,
                             lower_bound=-5.0, A_log=None, dt_bias=None):
-    """The same three-pass schedule on ONE GPU, segments standing in for ranks (no
-    communication): used to check the split against the one-pass forward."""
+    """The same schedule on ONE GPU, segments standing in for ranks (no communication): K1 and
+    the transform pass per segment, one fold over all segments, K2 per segment.  Used to check the
+    split against the one-pass forward."""
     if scale is None:
         scale = D ** -0.5
     B, T, H, _ = q.shape
     if T % (n_segments * api.BT):
         raise ValueError("T must split into n_segments multiples of 16")
     L = T // n_segments
+    mq = torch.empty((n_segments, B * H, 2, D, D), dtype=torch.float32, device=q.device)
     segs = [_Segment(q[:, j * L:(j + 1) * L], k[:, j * L:(j + 1) * L], v[:, j * L:(j + 1) * L],
-                     g[:, j * L:(j + 1) * L], beta[:, j * L:(j + 1) * L], scale, lower_bound, A_log, dt_bias)
+                     g[:, j * L:(j + 1) * L], beta[:, j * L:(j + 1) * L], scale, lower_bound, A_log, dt_bias,
+                     mq_out=mq[j])
             for j in range(n_segments)]
-    MQ = [s.transforms() for s in segs]
-    states = compose_entry_states([m for m, _ in MQ], [q_ for _, q_ in MQ], initial_state)
-    outs = [s.outputs(states[j] if (j > 0 or initial_state is not None) else None)[0] for j, s in enumerate(segs)]
-    return torch.cat(outs, dim=1), states[n_segments]
+    for s_ in segs:
+        s_.k1()
+        s_.transforms()
+    h0 = None if initial_state is None else initial_state.contiguous().float()
+    states = fold_states(mq, h0)
+    outs = [s_.outputs(states[j].view(B, H, D, D))[0] for j, s_ in enumerate(segs)]
+    return torch.cat(outs, dim=1), states[n_segments].view(B, H, D, D).clone()

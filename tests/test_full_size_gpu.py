@@ -96,9 +96,15 @@ def test_config4_b1_t131072_h16_sequence_split(cuda_device):
     o8, h8 = shard.forward_seq_split_local(d["q"], d["k"], d["v"], d["g"], d["beta"], 8, scale=d["scale"],
                                            initial_state=d["initial_state"], lower_bound=d["lower_bound"],
                                            A_log=d["A_log"], dt_bias=d["dt_bias"])
-    omax, hmax = o.float().abs().max().item(), ht.abs().max().item()
-    assert (o8.float() - o.float()).abs().max().item() <= 1e-2 * omax
-    assert (h8 - ht).abs().max().item() <= 1e-2 * hmax
+    # the split against the one-pass kernels: on this distribution the absolute bounds of the
+    # one-pass path hold for the split as well
+    assert (o8.float() - o.float()).abs().max().item() <= 1e-3
+    assert (h8 - ht).abs().max().item() <= 2e-3
+    # ... and against the ORACLE on two heads across the first segment boundary (token 16384)
+    heads, t_or = [0, 15], 16384 + 1024
+    o_r, _ = _oracle_on_heads(d, heads, t_or)
+    hs = torch.tensor(heads, device=o8.device)
+    assert (o8[:, :t_or].index_select(2, hs).float().cpu() - o_r.float()).abs().max().item() <= 1e-3
 
 
 def test_many_chains_b8_t2048_h32_tensor_memory_k2(cuda_device):

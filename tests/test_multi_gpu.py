@@ -28,26 +28,38 @@ def _rank_main(rank, world, port, ret):
     try:
         dev = torch.device("cuda", rank)
         T = 1024
-        inp = O.make_inputs(1, T, 4, seed0=21, regime="carry", h0_std=0.1)
-        d = {k: (v.to(dev) if torch.is_tensor(v) else v) for k, v in inp.items()}
-        kw = dict(scale=d["scale"], lower_bound=d["lower_bound"], A_log=d["A_log"], dt_bias=d["dt_bias"])
-        o1, h1 = K.kda_bt16_fwd(d["q"], d["k"], d["v"], d["g"], d["beta"], initial_state=d["initial_state"],
-                                output_final_state=True, use_qk_l2norm_in_kernel=True, use_gate_in_kernel=True,
-                                use_beta_sigmoid_in_kernel=True, **kw)
-        # sequence split: rank r owns tokens [r*T/world, (r+1)*T/world)
-        L = T // world
-        sl = slice(rank * L, (rank + 1) * L)
-        o2, h2 = shard.forward_seq_parallel(d["q"][:, sl], d["k"][:, sl], d["v"][:, sl], d["g"][:, sl],
-                                            d["beta"][:, sl], initial_state=d["initial_state"], **kw)
-        omax, hmax = o1.float().abs().max().item(), h1.abs().max().item()
-        e_seq_o = (o2.float() - o1[:, sl].float()).abs().max().item() / omax
-        e_seq_h = (h2 - h1).abs().max().item() / hmax
+        seq = {}
+        for regime, exchange in (("carry", "a2a"), ("carry", "gather"), ("baseline", "a2a")):
+            inp = O.make_inputs(1, T, 4, seed0=21, regime=regime, h0_std=0.1 if regime == "carry" else 0.02)
+            d = {k: (v.to(dev) if torch.is_tensor(v) else v) for k, v in inp.items()}
+            kw = dict(scale=d["scale"], lower_bound=d["lower_bound"], A_log=d["A_log"], dt_bias=d["dt_bias"])
+            o1, h1 = K.kda_bt16_fwd(d["q"], d["k"], d["v"], d["g"], d["beta"], initial_state=d["initial_state"],
+                                    output_final_state=True, use_qk_l2norm_in_kernel=True, use_gate_in_kernel=True,
+                                    use_beta_sigmoid_in_kernel=True, **kw)
+            # sequence split: rank r owns tokens [r*T/world, (r+1)*T/world); the plan is run twice on
+            # the same buffers (nothing may be left over from the first run)
+            L = T // world
+            sl = slice(rank * L, (rank + 1) * L)
+            plan = shard.SeqParallelPlan(d["q"][:, sl], d["k"][:, sl], d["v"][:, sl], d["g"][:, sl], d["beta"][:, sl],
+                                         initial_state=d["initial_state"], exchange=exchange,
+                                         final_state_on_all_ranks=True, **kw)
+            plan.run()
+            o2, h2 = plan.run()
+            omax, hmax = o1.float().abs().max().item(), h1.abs().max().item()
+            e_o = (o2.float() - o1[:, sl].float()).abs().max().item()
+            e_h = (h2 - h1).abs().max().item()
+            # against the CPU oracle too (1024 tokens x 4 heads: seconds)
+            o_r, h_r = O.run_chunk_reference(inp)
+            e_or = (o2.float().cpu() - o_r[:, sl].float()).abs().max().item()
+            e_hr = (h2.cpu() - h_r).abs().max().item()
+            seq[(regime, exchange)] = (e_o, e_h, e_or, e_hr, omax, hmax)
+        e_seq = seq
         # head shards: rank r owns a contiguous block of heads, nothing is exchanged
         o3, h3, (lo, hi) = shard.forward_head_shard(d["q"], d["k"], d["v"], d["g"], d["beta"], rank=rank, world=world,
                                                     initial_state=d["initial_state"], output_final_state=True, **kw)
         same = bool(torch.equal(o3, o1[:, :, lo:hi]) and torch.equal(h3, h1[:, lo:hi]))
         torch.cuda.synchronize()
-        ret[rank] = (e_seq_o, e_seq_h, same)
+        ret[rank] = (e_seq, same)
     finally:
         dist.destroy_process_group()
 
@@ -61,6 +73,12 @@ def test_two_ranks_sequence_split_and_head_shards():
     ret = mp.Manager().dict()
     mp.spawn(_rank_main, args=(world, _free_port(), ret), nprocs=world, join=True)
     for r in range(world):
-        e_o, e_h, same = ret[r]
-        assert e_o < 1e-2 and e_h < 1e-2, (r, e_o, e_h)
+        e_seq, same = ret[r]
+        for (regime, exchange), (e_o, e_h, e_or, e_hr, omax, hmax) in e_seq.items():
+            if regime == "baseline":   # benchmark distribution: the absolute bounds of the one-pass path
+                assert e_or <= 1e-3 and e_hr <= 2e-3, (r, regime, exchange, e_or, e_hr)
+                assert e_o <= 1e-3 and e_h <= 2e-3, (r, regime, exchange, e_o, e_h)
+            else:                      # O(1) persistent states: relative bounds
+                assert e_o < 1e-2 * omax and e_h < 1e-2 * hmax, (r, regime, exchange, e_o, e_h)
+                assert e_or < 2e-2 * omax and e_hr < 2e-2 * hmax, (r, regime, exchange, e_or, e_hr)
         assert same, r

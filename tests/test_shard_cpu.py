@@ -1,6 +1,7 @@
-"""CPU checks of the multi-GPU host logic: head ranges, the segment fold, and the
-all-gather + fold of a sequence split run as two gloo ranks (the per-segment transforms come
-from the CPU oracle here; on GPUs the kernels produce them)."""
+"""CPU checks of the multi-GPU host logic: head ranges, the segment fold, and both exchange
+patterns (all-to-all, all-gather) of a sequence split run as two gloo ranks (the per-segment
+transforms come from the CPU oracle and the fold is the torch statement here; on GPUs the kernels
+produce both)."""
 import os
 import socket
 
@@ -75,13 +76,21 @@ def _rank_main(rank, world, port, ret):
         inp = O.make_inputs(1, T, 2, seed0=9, regime="carry", h0_std=0.1)
         L = T // world
         seg, M, Q = _segment_transforms(inp, rank * L, (rank + 1) * L)
-        Ms, Qs = shard.exchange_segment_transforms(M, Q)
-        states = shard.compose_entry_states(Ms, Qs, inp["initial_state"])
-        o_loc, _ = O.run_chunk_reference(dict(seg, initial_state=states[rank]))
         o_full, h_full = O.run_chunk_reference(inp)
-        eo = (o_loc.float() - o_full[:, rank * L:(rank + 1) * L].float()).abs().max().item()
-        eh = (states[world] - h_full).abs().max().item()
-        ret[rank] = (eo, eh, o_full.float().abs().max().item(), h_full.abs().max().item())
+        mq = torch.stack([M[0], Q[0]], dim=1).contiguous()          # [chains = heads, 2, 128, 128]
+        res = {}
+        for mode in ("a2a", "gather"):
+            entry, final = shard.exchange_and_fold(mq, inp["initial_state"], rank, world, mode=mode,
+                                                   fold=shard._torch_fold, want_final=True)
+            o_loc, _ = O.run_chunk_reference(dict(seg, initial_state=entry.view(1, 2, D, D)))
+            eo = (o_loc.float() - o_full[:, rank * L:(rank + 1) * L].float()).abs().max().item()
+            eh = (final.view(1, 2, D, D) - h_full).abs().max().item()
+            res[mode] = (eo, eh)
+        # without the final state only the entry state comes back
+        entry2, none = shard.exchange_and_fold(mq, inp["initial_state"], rank, world, mode="gather",
+                                               fold=shard._torch_fold)
+        assert none is None and torch.equal(entry2, entry)
+        ret[rank] = (res, o_full.float().abs().max().item(), h_full.abs().max().item())
     finally:
         dist.destroy_process_group()
 
@@ -93,6 +102,16 @@ def test_sequence_split_over_two_gloo_ranks():
     mp.spawn(_rank_main, args=(world, _free_port(), ret), nprocs=world, join=True)
     assert sorted(ret.keys()) == [0, 1]
     for r in range(world):
-        eo, eh, omax, hmax = ret[r]
-        assert eo <= 2.0 ** -8 * omax, (r, eo)
-        assert eh <= 2e-5 * max(1.0, hmax), (r, eh)
+        res, omax, hmax = ret[r]
+        for mode, (eo, eh) in res.items():
+            assert eo <= 2.0 ** -8 * omax, (r, mode, eo)
+            assert eh <= 2e-5 * max(1.0, hmax), (r, mode, eh)
+
+
+def test_exchange_mode_choice():
+    assert shard.exchange_mode(32, 8) == "a2a" and shard.exchange_mode(16, 8) == "a2a"
+    assert shard.exchange_mode(5, 4) == "gather" and shard.exchange_mode(32, 8, "gather") == "gather"
+    with pytest.raises(ValueError):
+        shard.exchange_mode(5, 4, "a2a")
+    with pytest.raises(RuntimeError):
+        shard.fold_states(torch.zeros(1, 1, 2, D, D), None)       # the fold is a CUDA kernel: no CPU path

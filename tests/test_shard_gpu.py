@@ -44,9 +44,14 @@ def test_sequence_split_matches_one_pass_and_oracle(cuda_device, regime, T, nseg
                                            A_log=d["A_log"], dt_bias=d["dt_bias"])
     o_r, h_r = O.run_chunk_reference(inp)
     omax, hmax = o_r.float().abs().max().item(), h_r.abs().max().item()
-    # against the oracle: the reference's relative bound, 2e-2 of absmax
-    assert (o2.float().cpu() - o_r.float()).abs().max().item() < 2e-2 * omax
-    assert (h2.cpu() - h_r).abs().max().item() < 2e-2 * hmax
+    if regime == "baseline":
+        # benchmark distribution: the absolute bounds of the one-pass path, against the oracle
+        assert (o2.float().cpu() - o_r.float()).abs().max().item() <= 1e-3
+        assert (h2.cpu() - h_r).abs().max().item() <= 2e-3
+    else:
+        # O(1) states that persist: the reference's relative bound, 2e-2 of absmax, against the oracle
+        assert (o2.float().cpu() - o_r.float()).abs().max().item() < 2e-2 * omax
+        assert (h2.cpu() - h_r).abs().max().item() < 2e-2 * hmax
     # against the one-pass kernels: only the segment hand-over differs
     assert (o2.float() - o1.float()).abs().max().item() < 1e-2 * omax
     assert (h2 - h1).abs().max().item() < 1e-2 * hmax
@@ -56,3 +61,53 @@ def test_sequence_split_matches_one_pass_and_oracle(cuda_device, regime, T, nseg
                                           **{n: d[n][:, j * (T // nseg):(j + 1) * (T // nseg)].contiguous()
                                              for n in ("q", "k", "v", "g", "beta")}))[0] for j in range(nseg)], 1)
         assert (o_bad.float() - o1.float()).abs().max().item() > 0.1 * omax
+
+
+@pytest.mark.parametrize("chains,n_seg", [(1, 1), (3, 5), (8, 8)])
+def test_fold_kernel_against_float64(cuda_device, chains, n_seg):
+    """kda_state_fold (fp32 FMAs) against the same walk in float64, on strided and dense layouts."""
+    g = torch.Generator(device=cuda_device).manual_seed(chains * 10 + n_seg)
+    big = torch.randn(n_seg + 1, chains + 2, 2, 128, 128, device=cuda_device, generator=g) * 0.09
+    mq = big[:n_seg, 1:chains + 1]                                   # a strided view: the fold reads it in place
+    h0 = torch.randn(chains, 128, 128, device=cuda_device, generator=g)
+    out = shard.fold_states(mq, h0)
+    S = h0.double()
+    for j in range(n_seg):
+        assert (out[j].double() - S).abs().max().item() <= 2e-5 * max(1.0, S.abs().max().item())
+        S = S @ mq[j, :, 0].double() + mq[j, :, 1].double()
+    assert (out[n_seg].double() - S).abs().max().item() <= 2e-5 * max(1.0, S.abs().max().item())
+    # zero entry state, fewer segments than the buffer holds
+    out0 = shard.fold_states(mq, None, n_seg=max(0, n_seg - 1))
+    assert out0.shape[0] == max(0, n_seg - 1) + 1 and not out0[0].any()
+
+
+def test_transform_pair_pass_matches_the_two_single_passes(cuda_device):
+    """kda_fwd_k2_state(zero_u = 2) returns [chains][2][128][128] = (M, Q) of the two single passes."""
+    import ctypes
+    from kda_ascendc_b200 import _lib, api
+    inp = O.make_inputs(2, 96, 3, seed0=17, regime="carry", h0_std=0.1)
+    d = to_device(inp, cuda_device)
+    B, T, H = 2, 96, 3
+    lib = _lib.load()
+    st = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    ws = torch.empty(K.workspace_bytes(B, T, H), dtype=torch.uint8, device=cuda_device)
+    o = torch.empty(B, T, H, 128, dtype=torch.bfloat16, device=cuda_device)
+    eye = torch.eye(128, device=cuda_device).expand(B, H, 128, 128).contiguous()
+    M, Q = torch.empty_like(eye), torch.empty_like(eye)
+    mq = torch.empty(B * H, 2, 128, 128, device=cuda_device)
+
+    def args(h0, ht):
+        return api.make_args(d["q"], d["k"], d["v"], d["g"], d["beta"], scale=d["scale"], lower_bound=d["lower_bound"],
+                             A_log=d["A_log"], dt_bias=d["dt_bias"], h0=h0, o=o, ht=ht, workspace=ws, flags=7)
+    a = args(eye, M)
+    assert lib.kda_fwd_k1(ctypes.byref(a), st) == 0, _lib.last_error()
+    assert lib.kda_fwd_k2_state(ctypes.byref(a), 1, st) == 0, _lib.last_error()
+    a = args(None, Q)
+    assert lib.kda_fwd_k2_state(ctypes.byref(a), 0, st) == 0, _lib.last_error()
+    a = args(None, mq)
+    assert lib.kda_fwd_k2_state(ctypes.byref(a), 2, st) == 0, _lib.last_error()
+    torch.cuda.synchronize()
+    # the pair launch may run another organisation of K2 (twice the chains): fp32 summation order only
+    assert (mq[:, 0].view(B, H, 128, 128) - M).abs().max().item() <= 1e-5
+    assert (mq[:, 1].view(B, H, 128, 128) - Q).abs().max().item() <= 1e-4 * max(1.0, Q.abs().max().item())
+    assert lib.kda_fwd_k2_state(ctypes.byref(a), 3, st) == -1 and "zero_u" in _lib.last_error()
