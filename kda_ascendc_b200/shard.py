@@ -264,16 +264,31 @@ class SeqParallelPlan:
         self.want_final = bool(final_state_on_all_ranks)
         self.bufs: dict = {}
 
-    def run(self):
+    def run(self, timeline: Optional[list] = None):
+        """One forward.  ``timeline``: a list that receives ``(phase, torch.cuda.Event)`` pairs
+        recorded on the current stream after K1, the transform pass, the exchange + fold and K2
+        (for per-phase timing; the events must have been created with ``enable_timing=True``)."""
+        def mark(name):
+            if timeline is not None:
+                ev = torch.cuda.Event(enable_timing=True)
+                ev.record()
+                timeline.append((name, ev))
+
         seg = self.seg
+        mark("start")
         seg.k1()
+        mark("k1")
         if self.world == 1:
             o, ht = seg.outputs(self.h0)
+            mark("k2")
             return o, ht
         mq = seg.transforms()
+        mark("transforms")
         entry, final = exchange_and_fold(mq, self.h0, self.rank, self.world, group=self.group, mode=self.mode,
                                          bufs=self.bufs, want_final=self.want_final)
+        mark("exchange_fold")
         o, ht = seg.outputs(entry.view(seg.B, seg.H, D, D))
+        mark("k2")
         if self.want_final:
             return o, final.view(seg.B, seg.H, D, D)
         return o, (ht if self.rank == self.world - 1 else None)
