@@ -131,10 +131,13 @@ int kda_fwd_k2_state(const KdaFwdArgs* args, int zero_u, void* stream);
  * (strides in floats, so the buffer of an all-gather or of an all-to-all is read in place);
  * s_in: [n_seg + 1][n_chains][128][128] fp32 contiguous; h0: [n_chains][128][128] or NULL.
  * M_j is what kda_fwd_k2_state(zero_u = 1) returns from an identity entry state, Q_j what
- * kda_fwd_k2_state(zero_u = 0) returns from a zero one.  No reference kernel: the reference only
- * analyses the route (tools/probe_segment_affine.py:100-125, docs/SEGMENT_SCAN_ROUTE_A_EVAL.md:92-118). */
+ * kda_fwd_k2_state(zero_u = 0) returns from a zero one (zero_u = 2 returns both in this layout).
+ * status: device word (NULL = none) that receives a non-zero code if a bounded wait inside the
+ * kernel gives up -- pass the start of a workspace and read it with kda_fwd_status.  No reference
+ * kernel: the reference only analyses the route (tools/probe_segment_affine.py:100-125,
+ * docs/SEGMENT_SCAN_ROUTE_A_EVAL.md:92-118). */
 int kda_state_fold(const float* mq, int64_t seg_stride, int64_t chain_stride, const float* h0, float* s_in,
-                   int32_t n_chains, int32_t n_seg, void* stream);
+                   int32_t n_chains, int32_t n_seg, int32_t* status, void* stream);
 
 /* Token-by-token recurrence for decode steps and short sequences (T of one to a few dozen
  * tokens): reads the state from args->h0 (NULL = zeros), applies args->T tokens, writes the

@@ -61,7 +61,7 @@ def load() -> ctypes.CDLL:
     lib.kda_fwd_k2_state.argtypes = [ctypes.POINTER(KdaFwdArgs), ctypes.c_int, ctypes.c_void_p]
     lib.kda_state_fold.restype = ctypes.c_int
     lib.kda_state_fold.argtypes = [ctypes.c_void_p, ctypes.c_int64, ctypes.c_int64, ctypes.c_void_p, ctypes.c_void_p,
-                                   ctypes.c_int32, ctypes.c_int32, ctypes.c_void_p]
+                                   ctypes.c_int32, ctypes.c_int32, ctypes.c_void_p, ctypes.c_void_p]
     lib.kda_selftest_bounded_wait.restype = ctypes.c_int
     lib.kda_selftest_bounded_wait.argtypes = [ctypes.c_void_p, ctypes.c_void_p]
     lib.kda_varlen_fill_tables.restype = ctypes.c_int

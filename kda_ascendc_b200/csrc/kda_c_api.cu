@@ -227,13 +227,33 @@ int do_k2(const KdaFwdArgs* a, bool state_only, int zero_u, cudaStream_t st) {
     p.seq_table = reinterpret_cast<const int4*>(a->seq_table);
     p.n_seqs = a->n_seqs;
   }
-  if (p.pair_mode) {   // two chains per (batch, head): transition matrix and offset
-    const long long bh2 = 2LL * (a->n_seqs > 0 ? a->n_seqs : a->B) * a->H;
-    if (bh2 > 0x3fffffffLL) return fail(KDA_ERR_INVALID_ARG, "kda: too many chains%s", "");
-    p.n_chains = static_cast<int>(bh2);
-  }
   int vsplit = 4, variant = 3;
-  pick_split(a, state_only, &vsplit, &variant, 0, p.pair_mode ? 2 : 1);
+  pick_split(a, state_only, &vsplit, &variant);
+  if (p.pair_mode) {
+    // Both transforms of a segment in one launch.  Few chains (two recurrences per chain still give
+    // every warp an SM sub-partition to itself): the 8-row form over twice as many chains.  Up to
+    // the 8-row form's own limit: the two recurrences share a warp and its operand loads.  Beyond:
+    // the 16-row form over twice as many chains.
+    int dev = 0, sms = 148;
+    if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    const long long bh = static_cast<long long>(a->n_seqs > 0 ? a->n_seqs : a->B) * a->H;
+    if (2 * bh > 0x3fffffffLL) return fail(KDA_ERR_INVALID_ARG, "kda: too many chains%s", "");
+    cudaError_t pe;
+    if (a->k2_variant == 0 && a->k2_vsplit == 0 && 2 * bh * 4 <= sms) {
+      p.n_chains = static_cast<int>(2 * bh);
+      pe = kda::launch_k2n(p, 2 * bh * 16 <= sms ? 16 : 2 * bh * 8 <= sms ? 8 : 4, 1, true, st);
+    } else if (variant == 1) {
+      p.pair_mode = 0;   // the pair is compiled into the kernel
+      pe = kda::launch_k2n_pair(p, vsplit, st);
+    } else {
+      p.n_chains = static_cast<int>(2 * bh);
+      pick_split(a, state_only, &vsplit, &variant, 0, 2);
+      pe = (variant == 3) ? kda::launch_k2m(p, vsplit, true, st) : cudaErrorInvalidValue;
+    }
+    if (pe != cudaSuccess) return fail(KDA_ERR_CUDA, "kda: K2 (transform pair) launch failed: %s", cudaGetErrorString(pe));
+    ++g_launches;
+    return KDA_OK;
+  }
   cudaError_t e;
   if (variant == 4) {
     const long long n_records = a->n_seqs > 0 ? static_cast<long long>(a->n_chunks) * a->H
@@ -366,7 +386,7 @@ int kda_recurrent_fwd(const KdaFwdArgs* a, void* stream) {
 }
 
 int kda_state_fold(const float* mq, int64_t seg_stride, int64_t chain_stride, const float* h0, float* s_in,
-                   int32_t n_chains, int32_t n_seg, void* stream) {
+                   int32_t n_chains, int32_t n_seg, int32_t* status, void* stream) {
   g_launches = 0;
   if (mq == nullptr || s_in == nullptr) return fail(KDA_ERR_INVALID_ARG, "kda: the fold needs mq and s_in%s", "");
   if (n_chains <= 0 || n_seg < 0)
@@ -374,12 +394,16 @@ int kda_state_fold(const float* mq, int64_t seg_stride, int64_t chain_stride, co
   const int64_t pair = 2LL * kda::D * kda::D;
   if (n_seg > 0 && (chain_stride < pair || (n_seg > 1 && seg_stride < pair)))
     return fail(KDA_ERR_INVALID_ARG, "kda: the fold's strides must span an (M, Q) pair of 2 x 128 x 128 floats%s", "");
+  if (seg_stride % 4 != 0 || chain_stride % 4 != 0)
+    return fail(KDA_ERR_INVALID_ARG, "kda: the fold's strides must be multiples of 4 floats%s (every M_j is copied 16 bytes at a time)", "");
+  if (status != nullptr && reinterpret_cast<uintptr_t>(status) % 4 != 0)
+    return fail(KDA_ERR_INVALID_ARG, "kda: status must be 4-byte aligned%s", "");
   for (const void* ptr : {static_cast<const void*>(mq), static_cast<const void*>(h0), static_cast<const void*>(s_in)})
     if (ptr != nullptr && reinterpret_cast<uintptr_t>(ptr) % 16 != 0)
       return fail(KDA_ERR_INVALID_ARG, "kda: mq, h0 and s_in must be 16-byte aligned%s", "");
   if (static_cast<long long>(n_chains) * (kda::D / 4) > 0x7fffffffLL)
     return fail(KDA_ERR_INVALID_ARG, "kda: too many chains for one fold launch%s", "");
-  cudaError_t e = kda::launch_state_fold(mq, seg_stride, chain_stride, h0, s_in, n_chains, n_seg,
+  cudaError_t e = kda::launch_state_fold(mq, seg_stride, chain_stride, h0, s_in, n_chains, n_seg, status,
                                          static_cast<cudaStream_t>(stream));
   if (e != cudaSuccess) return fail(KDA_ERR_CUDA, "kda: fold launch failed: %s", cudaGetErrorString(e));
   ++g_launches;

@@ -42,27 +42,38 @@ namespace kda {
 
 constexpr int K2_STAGES = 4;
 
-template <int CW, int NVT>
+// UT = 8-column u tiles a warp reads per step (its NVT row tiles; one in the transform-pair mode)
+template <int CW, int UT>
 struct K2Smem {
-  static constexpr int STAGE = REC_SHARED_BYTES + CW * NVT * REC_U_TILE_BYTES;
+  static constexpr int STAGE = REC_SHARED_BYTES + CW * UT * REC_U_TILE_BYTES;
   static constexpr int BARS = K2_STAGES * STAGE;               // full[S], empty[S]
   static constexpr int FLAG = BARS + 2 * K2_STAGES * 8;        // abort flag, issued count
   static constexpr int TOTAL = FLAG + 16;
 };
 
-template <int CW, int NVT, bool STATE_ONLY>
+// PAIR (state-only, NVT = 2): the transform-pair pass of the sequence split.  The two 8-row tiles
+// of a warp are the SAME eight state rows of two recurrences over the same records -- tile 0 starts
+// from the identity with the u term dropped (the segment's transition matrix M), tile 1 from zero
+// with u (its offset Q) -- so every operand fragment fetched from shared memory feeds two MMAs.
+// The states leave as [chains][2][128][128].
+template <int CW, int NVT, bool STATE_ONLY, bool PAIR = false>
 __global__ void __launch_bounds__((CW + 1) * 32, 1) kda_k2_kernel(const K2Params p) {
+  static_assert(!PAIR || (STATE_ONLY && NVT == 2), "the pair mode is a state-only pass over two tiles");
   extern __shared__ __align__(1024) uint8_t smem[];
-  using SM = K2Smem<CW, NVT>;
-  constexpr int VCOLS = CW * NVT * 8;   // state rows (v) per CTA
+  constexpr int RT = PAIR ? 1 : NVT;    // distinct 8-row tiles per warp
+  using SM = K2Smem<CW, RT>;
+  constexpr int VCOLS = CW * RT * 8;    // state rows (v) per CTA
   constexpr int NV = D / VCOLS;         // CTAs per (batch, head)
   const int tid = threadIdx.x;
   const int lane = tid & 31;
   const int warp = tid >> 5;
+  // chain: index of the recurrence this CTA works on.  With K2Params::pair_mode (state-only, one
+  // tile per warp) the launch runs two chains per (batch, head): 2c from the identity without u,
+  // 2c + 1 from zero with u, and writes them as [chains][2][128][128].
   const int chain = blockIdx.x / NV + p.chain0;
-  const bool pair = STATE_ONLY && p.pair_mode != 0;
-  const int bh = pair ? (chain >> 1) : chain;      // the (batch, head) whose records are walked
-  const int plane = pair ? (chain & 1) : 1;        // pair mode: 0 = transition matrix, 1 = offset
+  const bool pair_rt = !PAIR && STATE_ONLY && p.pair_mode != 0;
+  const int bh = pair_rt ? (chain >> 1) : chain;   // the (batch, head) whose records are walked
+  const int plane = pair_rt ? (chain & 1) : 1;
   const int vs = blockIdx.x % NV;
   int b = bh / p.H;
   const int h = bh % p.H;
@@ -109,8 +120,8 @@ __global__ void __launch_bounds__((CW + 1) * 32, 1) kda_k2_kernel(const K2Params
         const uint32_t dst = sbase + s * SM::STAGE;
         mbar_arrive_expect_tx(full0 + s * 8, SM::STAGE);
         bulk_g2s(dst, rec, REC_SHARED_BYTES, full0 + s * 8);
-        bulk_g2s(dst + REC_SHARED_BYTES, rec + REC_U + vs * (CW * NVT * REC_U_TILE_BYTES),
-                 CW * NVT * REC_U_TILE_BYTES, full0 + s * 8);
+        bulk_g2s(dst + REC_SHARED_BYTES, rec + REC_U + vs * (CW * RT * REC_U_TILE_BYTES),
+                 CW * RT * REC_U_TILE_BYTES, full0 + s * 8);
         *sIssued = n + 1;
       }
     }
@@ -118,10 +129,18 @@ __global__ void __launch_bounds__((CW + 1) * 32, 1) kda_k2_kernel(const K2Params
   } else {
     // ------------------------------ consumers ------------------------------
     const int gq = lane >> 2, tq = lane & 3;
-    const int v0 = vs * VCOLS + warp * (NVT * 8);   // first state row of this warp
-    // hT[m][nv][e]: k = 16m + gq (+8 for e >= 2), v = v0 + 8nv + 2tq + (e & 1)
+    const int v0 = vs * VCOLS + warp * (RT * 8);   // first state row of this warp
+    // hT[m][nv][e]: k = 16m + gq (+8 for e >= 2), v = v0 + 8nv + 2tq + (e & 1)   (PAIR: v = v0 + 2tq + (e & 1))
     float hT[8][NVT][4];
-    if (pair) {
+    if (PAIR) {
+#pragma unroll
+      for (int m = 0; m < 8; ++m)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          hT[m][0][e] = ((v0 + tq * 2 + (e & 1)) == (m * 16 + gq + (e >> 1) * 8)) ? 1.f : 0.f;
+          hT[m][NVT - 1][e] = (NVT > 1) ? 0.f : hT[m][0][e];
+        }
+    } else if (pair_rt) {
 #pragma unroll
       for (int m = 0; m < 8; ++m)
 #pragma unroll
@@ -155,9 +174,9 @@ __global__ void __launch_bounds__((CW + 1) * 32, 1) kda_k2_kernel(const K2Params
     static_assert(SM::STAGE % 256 == 0 && REC_W % 256 == 0 && REC_QG % 256 == 0 && REC_KGH % 256 == 0 && REC_KGL % 256 == 0,
                   "tile bases must keep address bits 5..7 clear");
     const uint32_t a1_lane = swz_off(a1_row, a1_col), a2_lane = swz_off(a2_row, a2_col);
-    const uint32_t u_off = REC_SHARED_BYTES + warp * (NVT * REC_U_TILE_BYTES) + lane * 16;
+    const uint32_t u_off = REC_SHARED_BYTES + warp * (RT * REC_U_TILE_BYTES) + lane * 16;
     __nv_bfloat16* const ob = STATE_ONLY ? nullptr : p.o + b * p.o_s[0] + tok0 * p.o_s[1] + h * p.o_s[2] + v0 + tq * 2;
-    const bool use_u = pair ? (plane == 1) : !(STATE_ONLY && p.zero_u);
+    const bool use_u = PAIR || (pair_rt ? plane == 1 : !(STATE_ONLY && p.zero_u));
 
     uint32_t aw[8][4], aq[8][4];     // A fragments of w and qg (one per 16-wide k-step)
     float dk[8][2];                  // decay of the rows k = 16m+gq and 16m+gq+8
@@ -179,7 +198,8 @@ __global__ void __launch_bounds__((CW + 1) * 32, 1) kda_k2_kernel(const K2Params
       }
 #pragma unroll
       for (int nv = 0; nv < NVT; ++nv)
-        u[nv] = use_u ? *reinterpret_cast<const float4*>(smem + u_off + nv * REC_U_TILE_BYTES) : make_float4(0, 0, 0, 0);
+        u[nv] = (use_u && !(PAIR && nv == 0)) ? *reinterpret_cast<const float4*>(smem + u_off + (PAIR ? 0 : nv) * REC_U_TILE_BYTES)
+                                              : make_float4(0, 0, 0, 0);
     }
 
     for (int n = 0; n < NT && !failed; ++n) {
@@ -309,7 +329,8 @@ __global__ void __launch_bounds__((CW + 1) * 32, 1) kda_k2_kernel(const K2Params
       if (more) {
 #pragma unroll
         for (int nv = 0; nv < NVT; ++nv)
-          u[nv] = use_u ? *reinterpret_cast<const float4*>(spg1 + u_off + nv * REC_U_TILE_BYTES) : make_float4(0, 0, 0, 0);
+          u[nv] = (use_u && !(PAIR && nv == 0)) ? *reinterpret_cast<const float4*>(spg1 + u_off + (PAIR ? 0 : nv) * REC_U_TILE_BYTES)
+                                                : make_float4(0, 0, 0, 0);
       }
     }
 
@@ -325,14 +346,15 @@ __global__ void __launch_bounds__((CW + 1) * 32, 1) kda_k2_kernel(const K2Params
     }
 
     if (!failed && p.ht != nullptr) {
-      float* ht = p.ht + static_cast<size_t>(chain) * D * D;
+      float* ht = p.ht + static_cast<size_t>(PAIR ? 2 * bh : chain) * D * D;
 #pragma unroll
       for (int m = 0; m < 8; ++m)
 #pragma unroll
         for (int nv = 0; nv < NVT; ++nv)
 #pragma unroll
           for (int e = 0; e < 4; ++e)
-            ht[(v0 + nv * 8 + tq * 2 + (e & 1)) * D + m * 16 + gq + (e >> 1) * 8] = hT[m][nv][e];
+            if (PAIR) ht[(static_cast<size_t>(nv) * D + v0 + tq * 2 + (e & 1)) * D + m * 16 + gq + (e >> 1) * 8] = hT[m][nv][e];
+            else ht[(v0 + nv * 8 + tq * 2 + (e & 1)) * D + m * 16 + gq + (e >> 1) * 8] = hT[m][nv][e];
     }
   }
 
@@ -346,20 +368,21 @@ __global__ void __launch_bounds__((CW + 1) * 32, 1) kda_k2_kernel(const K2Params
   }
 }
 
-template <int CW, int NVT, bool STATE_ONLY>
+template <int CW, int NVT, bool STATE_ONLY, bool PAIR = false>
 static cudaError_t launch_k2_t(const K2Params& p, cudaStream_t stream) {
-  constexpr int smem_bytes = K2Smem<CW, NVT>::TOTAL;
+  constexpr int RT = PAIR ? 1 : NVT;
+  constexpr int smem_bytes = K2Smem<CW, RT>::TOTAL;
   static bool configured[64] = {};
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev < 64 && !configured[dev]) {
-    cudaError_t e = cudaFuncSetAttribute(kda_k2_kernel<CW, NVT, STATE_ONLY>,
+    cudaError_t e = cudaFuncSetAttribute(kda_k2_kernel<CW, NVT, STATE_ONLY, PAIR>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
     if (e != cudaSuccess) return e;
     configured[dev] = true;
   }
-  const int nblocks = (p.n_chains > 0 ? p.n_chains : (p.seq_table != nullptr ? p.n_seqs : p.B) * p.H) * (D / (CW * NVT * 8));
-  kda_k2_kernel<CW, NVT, STATE_ONLY><<<nblocks, (CW + 1) * 32, smem_bytes, stream>>>(p);
+  const int nblocks = (p.n_chains > 0 ? p.n_chains : (p.seq_table != nullptr ? p.n_seqs : p.B) * p.H) * (D / (CW * RT * 8));
+  kda_k2_kernel<CW, NVT, STATE_ONLY, PAIR><<<nblocks, (CW + 1) * 32, smem_bytes, stream>>>(p);
   return cudaGetLastError();
 }
 
@@ -374,6 +397,16 @@ cudaError_t launch_k2n(const K2Params& p, int vsplit, int ntile, bool state_only
   KDA_K2_CASE(16, 1, 1)
 #undef KDA_K2_CASE
   return cudaErrorInvalidValue;
+}
+
+cudaError_t launch_k2n_pair(const K2Params& p, int vsplit, cudaStream_t stream) {
+  // the transform-pair pass: two recurrences over the same eight rows per warp, 16 / vsplit consumer warps per CTA
+  switch (vsplit) {
+    case 4: return launch_k2_t<4, 2, true, true>(p, stream);
+    case 8: return launch_k2_t<2, 2, true, true>(p, stream);
+    case 16: return launch_k2_t<1, 2, true, true>(p, stream);
+    default: return cudaErrorInvalidValue;
+  }
 }
 
 }  // namespace kda

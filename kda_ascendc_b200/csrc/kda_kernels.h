@@ -61,9 +61,9 @@ struct K2Params {
   int64_t o_s[3];
   float scale;
   int zero_u;        // state-only mode: drop the u term
-  // state-only "transform pair" mode: the launch runs 2 x chains; chain 2c starts from the identity
-  // with u dropped (M of the segment), chain 2c+1 from zero with u (Q); h0 is not read and ht is
-  // [chains][2][128][128]
+  // state-only "transform pair" mode of the m16 form: the launch runs 2 x chains; chain 2c starts from
+  // the identity with u dropped (M of the segment), chain 2c+1 from zero with u (Q); h0 is not read
+  // and ht is [chains][2][128][128]
   int pair_mode;
   // packed variable-length input: one entry per sequence (first token, chunks, first record,
   // length); the grid then runs over (sequence, head); null for a fixed-length batch
@@ -84,13 +84,17 @@ cudaError_t k1_encode_tensor_maps(K1Params& p, bool g_bf16, const char** what);
 // vsplit = CTAs per (batch, head).
 cudaError_t launch_k2n(const K2Params& p, int vsplit, int ntile, bool state_only, cudaStream_t stream);
 cudaError_t launch_k2m(const K2Params& p, int vsplit, bool state_only, cudaStream_t stream);
+// the transform-pair pass of the sequence split in the "n8" form: both recurrences (M: identity entry
+// state without u; Q: zero entry state with u) on the same eight rows of one warp, so every operand
+// fragment read from shared memory feeds two MMAs; ht is [chains][2][128][128]
+cudaError_t launch_k2n_pair(const K2Params& p, int vsplit, cudaStream_t stream);
 //   "tc":       the whole 128-row state of a head in tensor memory, tcgen05 MMAs, one CTA per
 //               (batch, head), two CTAs per SM; outputs + final state only              (kda_k2t_sm100.cu)
 cudaError_t launch_k2t(const K2Params& p, long long n_records, cudaStream_t stream);
 
 // Walk of the per-segment affine state transforms of a sequence split (kda_fold_sm100.cu).
 cudaError_t launch_state_fold(const float* mq, long long seg_stride, long long chain_stride, const float* h0,
-                              float* s_in, int n_chains, int n_seg, cudaStream_t stream);
+                              float* s_in, int n_chains, int n_seg, int* status, cudaStream_t stream);
 
 // Token recurrence (decode / short sequences): no chunking, no workspace (kda_recurrent_sm100.cu).
 struct RecurrentParams {

@@ -96,11 +96,12 @@ def compose_entry_states(M: Sequence[torch.Tensor], Q: Sequence[torch.Tensor],
 
 
 def fold_states(mq: torch.Tensor, h0: Optional[torch.Tensor], out: Optional[torch.Tensor] = None,
-                n_seg: Optional[int] = None) -> torch.Tensor:
+                n_seg: Optional[int] = None, status: Optional[torch.Tensor] = None) -> torch.Tensor:
     """``kda_state_fold`` on a CUDA tensor ``mq [n_seg_total, n_chains, 2, 128, 128]`` (fp32; ``M`` then
     ``Q`` per chain, any segment / chain strides): returns ``s_in [n_seg + 1, n_chains, 128, 128]`` --
     the entry state of segments ``0..n_seg-1`` and the state after segment ``n_seg - 1``
-    (``n_seg`` defaults to all segments of ``mq``)."""
+    (``n_seg`` defaults to all segments of ``mq``).  ``status``: a workspace (or any int32 device
+    tensor) whose first word receives a code if a bounded wait inside the kernel gives up."""
     if not mq.is_cuda:
         raise RuntimeError("fold_states runs the CUDA kernel kda_state_fold; there is no CPU path")
     if mq.dtype != torch.float32 or mq.ndim != 5 or mq.shape[2:] != (2, D, D) or mq.stride()[2:] != (D * D, D, 1):
@@ -120,7 +121,9 @@ def fold_states(mq: torch.Tensor, h0: Optional[torch.Tensor], out: Optional[torc
     with torch.cuda.device(mq.device):
         api._check(_lib.load().kda_state_fold(ctypes.c_void_p(mq.data_ptr()), mq.stride(0), mq.stride(1),
                                               None if h0 is None else ctypes.c_void_p(h0.data_ptr()),
-                                              ctypes.c_void_p(out.data_ptr()), chains, n_seg, api._stream_handle()))
+                                              ctypes.c_void_p(out.data_ptr()), chains, n_seg,
+                                              None if status is None else ctypes.c_void_p(status.data_ptr()),
+                                              api._stream_handle()))
     return out
 
 
@@ -148,21 +151,30 @@ def exchange_mode(chains: int, world: int, requested: str = "auto") -> str:
 
 
 def exchange_and_fold(mq_local: torch.Tensor, h0: Optional[torch.Tensor], rank: int, world: int, *, group=None,
-                      mode: str = "a2a", fold=None, bufs: Optional[dict] = None, want_final: bool = False):
-    """From this rank's ``mq_local [chains, 2, 128, 128]`` to the entry state of its segment.
+                      mode: str = "a2a", sub: int = 1, fold=None, bufs: Optional[dict] = None,
+                      want_final: bool = False, status: Optional[torch.Tensor] = None):
+    """From this rank's transforms to the entry states of its segment(s).
 
-    Returns ``(s_entry [chains, 128, 128], final | None)``; ``final`` is the state after the last
-    segment, ``[chains, 128, 128]``, on every rank when ``want_final`` (one more small all-gather in
-    all-to-all mode).  ``bufs``: optional dict the function keeps its receive / send buffers in, so a
-    plan allocates them once.  ``fold``: the fold routine (default: the CUDA kernel).
+    ``mq_local``: ``[sub * chains, 2, 128, 128]`` -- ``sub`` consecutive sub-segments of this rank
+    (sub-segment major), ``chains`` (batch, head) chains each.  Returns ``(s_entry, final | None)``:
+    ``s_entry [sub, chains, 128, 128]`` are the entry states of this rank's sub-segments and
+    ``final [chains, 128, 128]`` the state after the last segment of the last rank, on every rank
+    when ``want_final`` (one more small all-gather in all-to-all mode).  ``sub > 1`` needs the
+    all-gather exchange.  ``bufs``: optional dict the function keeps its receive / send buffers in,
+    so a plan allocates them once.  ``fold``: the fold routine (default: the CUDA kernel).
     """
     import torch.distributed as dist
 
     fold = fold_states if fold is None else fold
     bufs = {} if bufs is None else bufs
-    chains = mq_local.shape[0]
+    if mq_local.shape[0] % sub:
+        raise ValueError("mq_local does not hold a whole number of sub-segments")
+    chains = mq_local.shape[0] // sub
+    if sub > 1 and mode != "gather":
+        raise ValueError("several segments per rank need the all-gather exchange")
     kw = dict(dtype=torch.float32, device=mq_local.device)
     h0c = None if h0 is None else h0.reshape(chains, D, D)
+    skw = {} if status is None else dict(status=status)
 
     def buf(name, shape):
         t = bufs.get(name)
@@ -171,15 +183,17 @@ def exchange_and_fold(mq_local: torch.Tensor, h0: Optional[torch.Tensor], rank: 
         return t
 
     if mode == "gather":
-        allmq = buf("gathered", (world, chains, 2, D, D))
-        dist.all_gather_into_tensor(allmq.view(world * chains, 2, D, D), mq_local.contiguous(), group=group)
-        n_seg = world if want_final else rank
-        s_in = fold(allmq, h0c, out=buf("s_in", (n_seg + 1, chains, D, D)), n_seg=n_seg)
-        return s_in[rank], (s_in[world] if want_final else None)
+        segs = world * sub
+        allmq = buf("gathered", (segs, chains, 2, D, D))      # segment = rank * sub + sub-segment
+        dist.all_gather_into_tensor(allmq.view(segs * chains, 2, D, D), mq_local.contiguous(), group=group)
+        n_seg = segs if want_final else rank * sub + sub - 1
+        s_in = fold(allmq, h0c, out=buf("s_in", (n_seg + 1, chains, D, D)), n_seg=n_seg, **skw)
+        return s_in[rank * sub:rank * sub + sub], (s_in[segs] if want_final else None)
     hp = chains // world
     recv = buf("recv_mq", (world, hp, 2, D, D))            # [segment][my chains]
     dist.all_to_all_single(recv, mq_local.contiguous().view(world, hp, 2, D, D), group=group)
-    s_in = fold(recv, None if h0c is None else h0c[rank * hp:(rank + 1) * hp], out=buf("s_in", (world + 1, hp, D, D)))
+    s_in = fold(recv, None if h0c is None else h0c[rank * hp:(rank + 1) * hp], out=buf("s_in", (world + 1, hp, D, D)),
+                **skw)
     entry = buf("entry", (world, hp, D, D))                # [owner of the chains][chains] = all chains in order
     dist.all_to_all_single(entry, s_in[:world], group=group)
     final = None
@@ -187,7 +201,12 @@ def exchange_and_fold(mq_local: torch.Tensor, h0: Optional[torch.Tensor], rank: 
         final = buf("final", (world, hp, D, D))
         dist.all_gather_into_tensor(final.view(chains, D, D), s_in[world].contiguous(), group=group)
         final = final.view(chains, D, D)
-    return entry.view(chains, D, D), final
+    return entry.view(1, chains, D, D), final
+
+
+def _sub_segments(x: torch.Tensor, sub: int) -> torch.Tensor:
+    """``[1, L, ...]`` -> ``[sub, L / sub, ...]`` as a view (consecutive token blocks as batch entries)."""
+    return x[0].unflatten(0, (sub, x.shape[1] // sub))
 
 
 class _Segment:
@@ -250,24 +269,52 @@ class SeqParallelPlan:
     final K2 on the current stream and returns ``(o_local, final_state)``: the state after the LAST
     segment on the last rank (from its own K2 pass), on every rank with ``final_state_on_all_ranks``,
     else ``None``.  In-kernel gate, l2-norm and beta sigmoid, V-first state.
+
+    ``segments_per_rank``: a K2 pass is one serial chain per (batch, head), so a rank with few heads
+    leaves most of its GPU idle; cutting the rank's tokens into 2 or 4 consecutive sub-segments
+    (handled as batch entries of the same launches, no copy) runs that many chains side by side
+    for the same total work.  ``"auto"`` takes the largest of 1, 2, 4 that still leaves every warp
+    of the 8-row K2 form an SM sub-partition of its own (batch 1 only; it implies the all-gather
+    exchange).
     """
 
     def __init__(self, q, k, v, g, beta, *, scale=None, initial_state=None, lower_bound=-5.0, A_log=None,
-                 dt_bias=None, group=None, exchange="auto", final_state_on_all_ranks=False):
+                 dt_bias=None, group=None, exchange="auto", final_state_on_all_ranks=False, segments_per_rank="auto"):
         import torch.distributed as dist
 
         self.group = group
         self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
+        B, L, H = q.shape[0], q.shape[1], v.shape[2]
+        sub = 1
+        if segments_per_rank == "auto":
+            if B == 1 and self.world > 1 and q.is_cuda and exchange != "a2a":
+                sms = torch.cuda.get_device_properties(q.device).multi_processor_count
+                for cand in (4, 2):
+                    if cand * H * 4 <= sms and L % (cand * api.BT) == 0:
+                        sub = cand
+                        break
+        else:
+            sub = int(segments_per_rank)
+            if sub < 1 or (sub > 1 and (B != 1 or L % (sub * api.BT))):
+                raise ValueError("segments_per_rank needs batch 1 and a token count that splits into multiples of 16")
+        self.sub = sub
+        if sub > 1:
+            if exchange == "a2a":
+                raise ValueError("several segments per rank need the all-gather exchange")
+            q, k, v, g, beta = (_sub_segments(x, sub) for x in (q, k, v, g, beta))
+            exchange = "gather"
         self.seg = _Segment(q, k, v, g, beta, D ** -0.5 if scale is None else scale, lower_bound, A_log, dt_bias)
+        self.chains = B * H
         self.h0 = None if initial_state is None else initial_state.contiguous().float()
-        self.mode = exchange_mode(self.seg.chains, self.world, exchange)
+        self.mode = exchange_mode(self.chains, self.world, exchange)
         self.want_final = bool(final_state_on_all_ranks)
         self.bufs: dict = {}
+        self.out_shape = (B, L, H, D)
 
     def run(self, timeline: Optional[list] = None):
         """One forward.  ``timeline``: a list that receives ``(phase, torch.cuda.Event)`` pairs
         recorded on the current stream after K1, the transform pass, the exchange + fold and K2
-        (for per-phase timing; the events must have been created with ``enable_timing=True``)."""
+        (for per-phase timing)."""
         def mark(name):
             if timeline is not None:
                 ev = torch.cuda.Event(enable_timing=True)
@@ -285,13 +332,14 @@ class SeqParallelPlan:
         mq = seg.transforms()
         mark("transforms")
         entry, final = exchange_and_fold(mq, self.h0, self.rank, self.world, group=self.group, mode=self.mode,
-                                         bufs=self.bufs, want_final=self.want_final)
+                                         sub=self.sub, bufs=self.bufs, want_final=self.want_final, status=seg.ws)
         mark("exchange_fold")
-        o, ht = seg.outputs(entry.view(seg.B, seg.H, D, D))
+        o, ht = seg.outputs(entry.reshape(seg.B, seg.H, D, D))
         mark("k2")
+        o = o.view(self.out_shape)
         if self.want_final:
-            return o, final.view(seg.B, seg.H, D, D)
-        return o, (ht if self.rank == self.world - 1 else None)
+            return o, final.view(self.out_shape[0], seg.H, D, D)
+        return o, (ht[seg.B - self.out_shape[0]:] if self.rank == self.world - 1 else None)
 
 
 def forward_seq_parallel(q, k, v, g, beta, *, scale=None, initial_state=None, lower_bound=-5.0,

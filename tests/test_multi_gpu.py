@@ -29,7 +29,8 @@ def _rank_main(rank, world, port, ret):
         dev = torch.device("cuda", rank)
         T = 1024
         seq = {}
-        for regime, exchange in (("carry", "a2a"), ("carry", "gather"), ("baseline", "a2a")):
+        for regime, exchange, sub in (("carry", "a2a", 1), ("carry", "gather", 1), ("carry", "gather", 2),
+                                      ("baseline", "a2a", 1), ("baseline", "auto", "auto")):
             inp = O.make_inputs(1, T, 4, seed0=21, regime=regime, h0_std=0.1 if regime == "carry" else 0.02)
             d = {k: (v.to(dev) if torch.is_tensor(v) else v) for k, v in inp.items()}
             kw = dict(scale=d["scale"], lower_bound=d["lower_bound"], A_log=d["A_log"], dt_bias=d["dt_bias"])
@@ -42,7 +43,7 @@ def _rank_main(rank, world, port, ret):
             sl = slice(rank * L, (rank + 1) * L)
             plan = shard.SeqParallelPlan(d["q"][:, sl], d["k"][:, sl], d["v"][:, sl], d["g"][:, sl], d["beta"][:, sl],
                                          initial_state=d["initial_state"], exchange=exchange,
-                                         final_state_on_all_ranks=True, **kw)
+                                         final_state_on_all_ranks=True, segments_per_rank=sub, **kw)
             plan.run()
             o2, h2 = plan.run()
             omax, hmax = o1.float().abs().max().item(), h1.abs().max().item()
@@ -52,7 +53,7 @@ def _rank_main(rank, world, port, ret):
             o_r, h_r = O.run_chunk_reference(inp)
             e_or = (o2.float().cpu() - o_r[:, sl].float()).abs().max().item()
             e_hr = (h2.cpu() - h_r).abs().max().item()
-            seq[(regime, exchange)] = (e_o, e_h, e_or, e_hr, omax, hmax)
+            seq[(regime, exchange, sub)] = (e_o, e_h, e_or, e_hr, omax, hmax)
         e_seq = seq
         # head shards: rank r owns a contiguous block of heads, nothing is exchanged
         o3, h3, (lo, hi) = shard.forward_head_shard(d["q"], d["k"], d["v"], d["g"], d["beta"], rank=rank, world=world,
@@ -74,11 +75,11 @@ def test_two_ranks_sequence_split_and_head_shards():
     mp.spawn(_rank_main, args=(world, _free_port(), ret), nprocs=world, join=True)
     for r in range(world):
         e_seq, same = ret[r]
-        for (regime, exchange), (e_o, e_h, e_or, e_hr, omax, hmax) in e_seq.items():
+        for (regime, exchange, sub), (e_o, e_h, e_or, e_hr, omax, hmax) in e_seq.items():
             if regime == "baseline":   # benchmark distribution: the absolute bounds of the one-pass path
-                assert e_or <= 1e-3 and e_hr <= 2e-3, (r, regime, exchange, e_or, e_hr)
-                assert e_o <= 1e-3 and e_h <= 2e-3, (r, regime, exchange, e_o, e_h)
+                assert e_or <= 1e-3 and e_hr <= 2e-3, (r, regime, exchange, sub, e_or, e_hr)
+                assert e_o <= 1e-3 and e_h <= 2e-3, (r, regime, exchange, sub, e_o, e_h)
             else:                      # O(1) persistent states: relative bounds
-                assert e_o < 1e-2 * omax and e_h < 1e-2 * hmax, (r, regime, exchange, e_o, e_h)
-                assert e_or < 2e-2 * omax and e_hr < 2e-2 * hmax, (r, regime, exchange, e_or, e_hr)
+                assert e_o < 1e-2 * omax and e_h < 1e-2 * hmax, (r, regime, exchange, sub, e_o, e_h)
+                assert e_or < 2e-2 * omax and e_hr < 2e-2 * hmax, (r, regime, exchange, sub, e_or, e_hr)
         assert same, r
