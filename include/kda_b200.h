@@ -51,6 +51,11 @@ extern "C" {
 #define KDA_FLAG_GATE_IN_KERNEL 1u    /* g is the raw gate; apply A_log/dt_bias/sigmoid/cumsum */
 #define KDA_FLAG_QK_L2NORM 2u         /* l2-normalise q and k (eps 1e-6) */
 #define KDA_FLAG_BETA_SIGMOID 4u      /* beta holds logits */
+#define KDA_FLAG_STATE_K_FIRST 8u     /* h0 / ht are [B, H, K, V] (the reference's state_v_first=False,
+                                         src/kda_bt16/kernels.py:497-510, where it is a host-side transpose);
+                                         read and written in that layout by kda_fwd, kda_fwd_k2 and
+                                         kda_fwd_k2_state(zero_u 0 / 1); kda_recurrent_fwd and the transform
+                                         pair (zero_u = 2) keep [B, H, V, K] */
 
 typedef struct KdaFwdArgs {
   /* inputs: [B, T, H, 128], innermost dimension contiguous; strides in ELEMENTS.

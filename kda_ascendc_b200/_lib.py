@@ -12,7 +12,7 @@ LIB_PATH = Path(__file__).resolve().parent / "libkda_b200.so"
 
 KDA_G_FP32, KDA_G_BF16 = 0, 1
 STATIC_SCRATCH_BYTES = 32 * 1024 * 1024   # KDA_STATIC_SCRATCH_BYTES of include/kda_b200.h
-FLAG_GATE, FLAG_L2NORM, FLAG_BETA_SIGMOID = 1, 2, 4
+FLAG_GATE, FLAG_L2NORM, FLAG_BETA_SIGMOID, FLAG_STATE_K_FIRST = 1, 2, 4, 8
 
 EXPORTS = (
     "kda_fwd_workspace_bytes", "kda_fwd", "kda_fwd_k1", "kda_fwd_k2", "kda_fwd_k2_state", "kda_recurrent_fwd",

@@ -270,9 +270,7 @@ def _forward(q, k, v, g, beta, scale, initial_state, output_final_state, use_qk_
     B, T, _, K = q.shape
     H = v.shape[2]
     dev = q.device
-    h0 = initial_state
-    if h0 is not None and not state_v_first:
-        h0 = h0.transpose(-1, -2).contiguous()  # kernels keep the state V-first
+    h0 = initial_state   # either layout is read and written in place by the chunk kernels
     o = torch.empty((B, T, H, HEAD_DIM), dtype=torch.bfloat16, device=dev)
     n_states, ws_tokens, tables = B, T, None
     if cu_seqlens is not None:
@@ -287,7 +285,8 @@ def _forward(q, k, v, g, beta, scale, initial_state, output_final_state, use_qk_
     args = make_args(q, k, v, g, beta, scale=scale, lower_bound=lower_bound, A_log=A_log, dt_bias=dt_bias,
                      h0=h0, o=o, ht=ht, workspace=ws, g_out=g_out, ainv_out=ainv, k2_vsplit=k2_vsplit,
                      k2_variant=k2_variant,
-                     flags=_flags(use_gate_in_kernel, use_qk_l2norm_in_kernel, use_beta_sigmoid_in_kernel))
+                     flags=_flags(use_gate_in_kernel, use_qk_l2norm_in_kernel, use_beta_sigmoid_in_kernel) |
+                     (0 if state_v_first else _lib.FLAG_STATE_K_FIRST))
     if tables is not None:
         args.n_seqs, args.n_chunks = tables[0], tables[1]
         args.chunk_table, args.seq_table = _ptr(tables[2]), _ptr(tables[3])
@@ -309,8 +308,6 @@ def _forward(q, k, v, g, beta, scale, initial_state, output_final_state, use_qk_
             _check(lib.kda_fwd(ctypes.byref(args), stream))
     _LAUNCH_COUNTS["kda_k1"] += 1
     _LAUNCH_COUNTS["kda_k2"] += 1
-    if ht is not None and not state_v_first:
-        ht = ht.transpose(-1, -2).contiguous()
     if return_intermediates:
         from .layout import unpack_records
         inter = unpack_records(ws, B, T, H)

@@ -222,6 +222,7 @@ int do_k2(const KdaFwdArgs* a, bool state_only, int zero_u, cudaStream_t st) {
   for (int i = 0; i < 3; ++i) p.o_s[i] = a->o_stride[i];
   p.scale = a->scale;
   p.zero_u = zero_u == 1;
+  p.k_first = (a->flags & KDA_FLAG_STATE_K_FIRST) ? 1 : 0;
   p.pair_mode = (state_only && zero_u == 2) ? 1 : 0;
   if (a->n_seqs > 0) {
     p.seq_table = reinterpret_cast<const int4*>(a->seq_table);
@@ -230,6 +231,7 @@ int do_k2(const KdaFwdArgs* a, bool state_only, int zero_u, cudaStream_t st) {
   int vsplit = 4, variant = 3;
   pick_split(a, state_only, &vsplit, &variant);
   if (p.pair_mode) {
+    p.k_first = 0;   // the transforms are always written [chains][2][V][K]
     // Both transforms of a segment in one launch.  Few chains (two recurrences per chain still give
     // every warp an SM sub-partition to itself): the 8-row form over twice as many chains.  Up to
     // the 8-row form's own limit: the two recurrences share a warp and its operand loads.  Beyond:
@@ -352,6 +354,8 @@ int kda_recurrent_fwd(const KdaFwdArgs* a, void* stream) {
   const uint32_t all = KDA_FLAG_GATE_IN_KERNEL | KDA_FLAG_QK_L2NORM | KDA_FLAG_BETA_SIGMOID;
   if ((a->flags & all) != all)
     return fail(KDA_ERR_INVALID_ARG, "kda: the recurrent step computes gate, l2-norm and beta sigmoid in the kernel%s; set all three flags", "");
+  if (a->flags & KDA_FLAG_STATE_K_FIRST)
+    return fail(KDA_ERR_INVALID_ARG, "kda: the recurrent step keeps its state [B, H, V, K]%s (KDA_FLAG_STATE_K_FIRST is for the chunk kernels)", "");
   if (a->g_dtype != KDA_G_FP32 && a->g_dtype != KDA_G_BF16)
     return fail(KDA_ERR_INVALID_ARG, "kda: g_dtype must be KDA_G_FP32 or KDA_G_BF16%s (got %lld)", "", a->g_dtype);
   if (!(a->lower_bound > -11.0f && a->lower_bound < 0.0f))

@@ -156,7 +156,8 @@ __global__ void __launch_bounds__((CW + 1) * 32, 1) kda_k2_kernel(const K2Params
         for (int nv = 0; nv < NVT; ++nv)
 #pragma unroll
           for (int e = 0; e < 4; ++e)
-            hT[m][nv][e] = h0[(v0 + nv * 8 + tq * 2 + (e & 1)) * D + m * 16 + gq + (e >> 1) * 8];
+            hT[m][nv][e] = p.k_first ? h0[(m * 16 + gq + (e >> 1) * 8) * D + v0 + nv * 8 + tq * 2 + (e & 1)]
+                                     : h0[(v0 + nv * 8 + tq * 2 + (e & 1)) * D + m * 16 + gq + (e >> 1) * 8];
     } else {
 #pragma unroll
       for (int m = 0; m < 8; ++m)
@@ -354,6 +355,7 @@ __global__ void __launch_bounds__((CW + 1) * 32, 1) kda_k2_kernel(const K2Params
 #pragma unroll
           for (int e = 0; e < 4; ++e)
             if (PAIR) ht[(static_cast<size_t>(nv) * D + v0 + tq * 2 + (e & 1)) * D + m * 16 + gq + (e >> 1) * 8] = hT[m][nv][e];
+            else if (p.k_first) ht[(m * 16 + gq + (e >> 1) * 8) * D + v0 + nv * 8 + tq * 2 + (e & 1)] = hT[m][nv][e];
             else ht[(v0 + nv * 8 + tq * 2 + (e & 1)) * D + m * 16 + gq + (e >> 1) * 8] = hT[m][nv][e];
     }
   }

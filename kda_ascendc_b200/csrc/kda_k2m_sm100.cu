@@ -118,9 +118,14 @@ __global__ void __launch_bounds__((CW + 1) * 32, MINB) kda_k2m_kernel(const K2Pa
       const float* h0 = p.h0 + static_cast<size_t>(bh) * D * D;
 #pragma unroll
       for (int nt = 0; nt < 16; ++nt) {
-        const float2 a = *reinterpret_cast<const float2*>(h0 + (vrow0 + gq) * D + nt * 8 + tq * 2);
-        const float2 c = *reinterpret_cast<const float2*>(h0 + (vrow0 + gq + 8) * D + nt * 8 + tq * 2);
-        hs[nt][0] = a.x; hs[nt][1] = a.y; hs[nt][2] = c.x; hs[nt][3] = c.y;
+        if (p.k_first) {
+          const float* c0 = h0 + (nt * 8 + tq * 2) * D + vrow0 + gq;
+          hs[nt][0] = c0[0]; hs[nt][1] = c0[D]; hs[nt][2] = c0[8]; hs[nt][3] = c0[D + 8];
+        } else {
+          const float2 a = *reinterpret_cast<const float2*>(h0 + (vrow0 + gq) * D + nt * 8 + tq * 2);
+          const float2 c = *reinterpret_cast<const float2*>(h0 + (vrow0 + gq + 8) * D + nt * 8 + tq * 2);
+          hs[nt][0] = a.x; hs[nt][1] = a.y; hs[nt][2] = c.x; hs[nt][3] = c.y;
+        }
       }
     } else {
 #pragma unroll
@@ -322,8 +327,13 @@ __global__ void __launch_bounds__((CW + 1) * 32, MINB) kda_k2m_kernel(const K2Pa
       float* ht = p.ht + static_cast<size_t>(chain) * D * D;
 #pragma unroll
       for (int nt = 0; nt < 16; ++nt) {
-        *reinterpret_cast<float2*>(ht + (vrow0 + gq) * D + nt * 8 + tq * 2) = make_float2(hs[nt][0], hs[nt][1]);
-        *reinterpret_cast<float2*>(ht + (vrow0 + gq + 8) * D + nt * 8 + tq * 2) = make_float2(hs[nt][2], hs[nt][3]);
+        if (p.k_first && !pair) {
+          float* c0 = ht + (nt * 8 + tq * 2) * D + vrow0 + gq;
+          c0[0] = hs[nt][0]; c0[D] = hs[nt][1]; c0[8] = hs[nt][2]; c0[D + 8] = hs[nt][3];
+        } else {
+          *reinterpret_cast<float2*>(ht + (vrow0 + gq) * D + nt * 8 + tq * 2) = make_float2(hs[nt][0], hs[nt][1]);
+          *reinterpret_cast<float2*>(ht + (vrow0 + gq + 8) * D + nt * 8 + tq * 2) = make_float2(hs[nt][2], hs[nt][3]);
+        }
       }
     }
   }

@@ -307,12 +307,25 @@ __global__ void __launch_bounds__(KT_THREADS, 2) kda_k2t_kernel(const __grid_con
 #pragma unroll 1
       for (int hh = 0; hh < 2; ++hh) {
         const int r0 = quad * 32 + hh * 16 + g4;
-        const float* src = p.h0 != nullptr ? p.h0 + (static_cast<size_t>(bh) * D + r0) * D + half * 64 + t4 * 2 : nullptr;
+        // element (v, k) sits at v*128 + k (V-first) or k*128 + v (K-first); this thread holds rows
+        // v = r0, r0 + 8 and columns k = 64 half + 8 n8 + 2 t4, +1
+        const float* src = p.h0 == nullptr ? nullptr
+                           : p.k_first ? p.h0 + (static_cast<size_t>(bh) * D + half * 64 + t4 * 2) * D + r0
+                                       : p.h0 + (static_cast<size_t>(bh) * D + r0) * D + half * 64 + t4 * 2;
         uint32_t sr[32], ar[16];
 #pragma unroll
         for (int n8 = 0; n8 < 8; ++n8) {
-          const float2 x = src != nullptr ? *reinterpret_cast<const float2*>(src + n8 * 8) : make_float2(0.f, 0.f);
-          const float2 y = src != nullptr ? *reinterpret_cast<const float2*>(src + 8 * D + n8 * 8) : make_float2(0.f, 0.f);
+          float2 x = make_float2(0.f, 0.f), y = x;
+          if (src != nullptr) {
+            if (p.k_first) {
+              const float* c0 = src + n8 * 8 * D;
+              x = make_float2(c0[0], c0[D]);
+              y = make_float2(c0[8], c0[D + 8]);
+            } else {
+              x = *reinterpret_cast<const float2*>(src + n8 * 8);
+              y = *reinterpret_cast<const float2*>(src + 8 * D + n8 * 8);
+            }
+          }
           const float2 dd = *reinterpret_cast<const float2*>(dec0 + n8 * 8 + t4 * 2);
           ar[n8 * 2] = pack_bf16(x.x, x.y);
           ar[n8 * 2 + 1] = pack_bf16(y.x, y.y);
@@ -471,12 +484,20 @@ __global__ void __launch_bounds__(KT_THREADS, 2) kda_k2t_kernel(const __grid_con
         tc_wait_ld();
         pin16(reinterpret_cast<uint32_t (&)[16]>(fr[0]));
         pin16(reinterpret_cast<uint32_t (&)[16]>(fr[16]));
-        float* dst = p.ht + (static_cast<size_t>(bh) * D + quad * 32 + hh * 16 + g4) * D + half * 64 + t4 * 2;
+        const int vr = quad * 32 + hh * 16 + g4;
+        float* dst = p.k_first ? p.ht + (static_cast<size_t>(bh) * D + half * 64 + t4 * 2) * D + vr
+                               : p.ht + (static_cast<size_t>(bh) * D + vr) * D + half * 64 + t4 * 2;
 #pragma unroll
         for (int n8 = 0; n8 < 8; ++n8) {
-          *reinterpret_cast<float2*>(dst + n8 * 8) = make_float2(__uint_as_float(fr[n8 * 4]), __uint_as_float(fr[n8 * 4 + 1]));
-          *reinterpret_cast<float2*>(dst + 8 * D + n8 * 8) =
-              make_float2(__uint_as_float(fr[n8 * 4 + 2]), __uint_as_float(fr[n8 * 4 + 3]));
+          if (p.k_first) {
+            float* c0 = dst + n8 * 8 * D;
+            c0[0] = __uint_as_float(fr[n8 * 4]); c0[D] = __uint_as_float(fr[n8 * 4 + 1]);
+            c0[8] = __uint_as_float(fr[n8 * 4 + 2]); c0[D + 8] = __uint_as_float(fr[n8 * 4 + 3]);
+          } else {
+            *reinterpret_cast<float2*>(dst + n8 * 8) = make_float2(__uint_as_float(fr[n8 * 4]), __uint_as_float(fr[n8 * 4 + 1]));
+            *reinterpret_cast<float2*>(dst + 8 * D + n8 * 8) =
+                make_float2(__uint_as_float(fr[n8 * 4 + 2]), __uint_as_float(fr[n8 * 4 + 3]));
+          }
         }
       }
     }

@@ -60,6 +60,7 @@ struct K2Params {
   int B, T, H, NT;
   int64_t o_s[3];
   float scale;
+  int k_first;       // h0 and ht are [B,H,K,V] (element (v, k) at k*128 + v) instead of [B,H,V,K]
   int zero_u;        // state-only mode: drop the u term
   // state-only "transform pair" mode of the m16 form: the launch runs 2 x chains; chain 2c starts from
   // the identity with u dropped (M of the segment), chain 2c+1 from zero with u (Q); h0 is not read

@@ -15,8 +15,9 @@ Two layers:
   its own kernels for the rest.  Off unless called; ``FLA_KDA_B200=0`` disables it afterwards.
 
 FLA keeps the state K-first (``[N, H, K, V]``) unless ``transpose_state_layout`` (older releases:
-``state_v_first``) is set; the kernels keep it V-first, so the K-first case costs one transpose
-on the way in and one on the way out, as in the reference (src/kda_bt16/kernels.py:497-510).
+``state_v_first``) is set.  The chunk kernels read and write either layout in place (the
+reference transposes on the host, src/kda_bt16/kernels.py:497-510); the token recurrence keeps its
+state V-first, so ``fused_recurrent_kda`` pays one transpose each way for K-first states.
 """
 from __future__ import annotations
 

@@ -119,6 +119,29 @@ def test_state_layouts_and_transpose_detection(cuda_device):
     assert err <= O_TOL and bad > 20 * err
 
 
+@pytest.mark.parametrize("variant", [1, 3, 4])
+def test_k_first_state_is_read_and_written_natively(cuda_device, variant):
+    """[B, H, K, V] states go through every organisation of K2 without a host-side transpose and give
+    bit for bit what the [B, H, V, K] run gives (same arithmetic, other addresses)."""
+    from kda_ascendc_b200 import api
+    inp = O.make_inputs(2, 80, 3, seed0=19, h0_std=1.0)
+    d = to_device(inp, cuda_device)
+
+    def run(h0, v_first):
+        return api._forward(d["q"], d["k"], d["v"], d["g"], d["beta"], d["scale"], h0, True, True, True, True,
+                            d["lower_bound"], d["A_log"], d["dt_bias"], v_first, k2_variant=variant)
+
+    o_v, h_v = run(d["initial_state"], True)
+    h0_k = d["initial_state"].transpose(-1, -2).contiguous()
+    keep = h0_k.clone()
+    o_k, h_k = run(h0_k, False)
+    assert torch.equal(h0_k, keep)                               # the caller's state is not touched
+    assert torch.equal(o_v, o_k)
+    assert torch.equal(h_v, h_k.transpose(-1, -2))
+    o_r, h_r = O.run_chunk_reference(inp)
+    assert (h_k.transpose(-1, -2).cpu() - h_r).abs().max().item() <= 2e-2 * h_r.abs().max().item()
+
+
 def test_output_axis_order(cuda_device):
     """[B,T,H,D] vs [B,H,T,D]: the swapped candidate must be far worse than the result."""
     inp = O.make_inputs(1, 32, 32, seed0=4, h0_std=0.02)
