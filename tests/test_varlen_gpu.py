@@ -1,6 +1,7 @@
 """Packed variable-length sequences (cu_seqlens) against the oracle run per sequence and against
-this build's own fixed-length calls (bit-identical: a chunk's valid rows never read the rows past
-its sequence's end).  Tolerances as for the fixed-length path: o 1e-3, state 2e-3 (benchmark
+this build's own fixed-length calls (a chunk's valid rows never read the rows past its sequence's
+end: within one bf16 step of o and 2e-5 on the state, since the packed batch may run another K2
+organisation; bit-equal for a single packed sequence).  Tolerances as for the fixed-length path: o 1e-3, state 2e-3 (benchmark
 distribution)."""
 import pytest
 import torch
