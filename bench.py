@@ -54,6 +54,7 @@ import torch  # noqa: E402
 B, T, H, D = 1, 8192, 32, 128
 BT = 16
 METRIC = "KDA fwd tokens/s at B1 T8192 H32 K=V=128 bf16"
+K2_VARIANT = 0               # 0 = the library's automatic choice (always, except in --kernels-only captures)
 # long-context configuration of the sequence split
 SP_T, SP_H = 131072, 16
 # parity bounds of the forward against the reference's torch chunk implementation
@@ -337,7 +338,8 @@ def run_gpu_arm(steps, warmup, n_gpus, kernels_only=False):
     o = torch.empty(B, T, H, D, dtype=torch.bfloat16, device=dev)
     ht = torch.empty(B, H, D, D, dtype=torch.float32, device=dev)
     args = api.make_args(d["q"], d["k"], d["v"], d["g"], d["beta"], scale=scale, lower_bound=-5.0,
-                         A_log=d["A_log"], dt_bias=d["dt_bias"], h0=d["h0"], o=o, ht=ht, workspace=ws, flags=7)
+                         A_log=d["A_log"], dt_bias=d["dt_bias"], h0=d["h0"], o=o, ht=ht, workspace=ws, flags=7,
+                         k2_variant=K2_VARIANT)
 
     def fwd_whole():
         rc = lib.kda_fwd(ctypes.byref(args), stream)
@@ -676,7 +678,14 @@ def main():
     ap.add_argument("--shape", default=None,
                     help="B,T,H of another workload for --kernels-only runs (profiler captures of other regimes); "
                          "the default and every reported line use the headline shape")
+    ap.add_argument("--k2-variant", type=int, default=0,
+                    help="K2 organisation for --kernels-only runs (profiler captures of a form the automatic "
+                         "choice does not take, e.g. 5 = look-ahead); every reported line uses the automatic choice")
     a = ap.parse_args()
+    if a.k2_variant and not a.kernels_only:
+        ap.error("--k2-variant goes with --kernels-only")
+    global K2_VARIANT
+    K2_VARIANT = a.k2_variant
     if a.shape is not None:
         if not a.kernels_only:
             ap.error("--shape goes with --kernels-only")

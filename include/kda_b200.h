@@ -91,7 +91,10 @@ typedef struct KdaFwdArgs {
                            1 "n8":  8 rows per warp  (k2_vsplit 4, 8 or 16), rows on the MMA N dimension
                            3 "m16": 16 rows per warp (k2_vsplit 2, 4 or 8), rows on the MMA M dimension
                            4 "tc":  all 128 rows of a head in tensor memory, tcgen05 MMAs (k2_vsplit ignored;
-                                    not for kda_fwd_k2_state) */
+                                    not for kda_fwd_k2_state)
+                           5 "la":  the 8-row form with a one-chunk look-ahead (no dependent hand-over inside
+                                    a step; k2_vsplit 4, 8 or 16); measured slower than "n8" and never chosen
+                                    automatically */
   /* Packed variable-length sequences (optional; not in the reference, whose README.md:509 lists
    * it as future work).  n_seqs > 0 selects it: B must be 1, T is the total number of packed
    * tokens, h0 / ht are [n_seqs, H, 128, 128], and the two tables (DEVICE memory, int32, made by

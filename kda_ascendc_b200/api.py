@@ -202,7 +202,7 @@ def check_device_status(workspace: torch.Tensor) -> int:
     return st.value
 
 
-K2_FORMS = {1: "n8", 3: "m16", 4: "tc"}
+K2_FORMS = {1: "n8", 3: "m16", 4: "tc", 5: "la"}
 
 
 def k2_choice(B: int, T: int, H: int, *, state_only: bool = False, n_seqs: int = 0, n_chunks: int = 0,

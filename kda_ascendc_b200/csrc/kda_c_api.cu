@@ -86,14 +86,14 @@ int check_k2(const KdaFwdArgs* a, bool state_only) {
     if (ptr != nullptr && reinterpret_cast<uintptr_t>(ptr) % 16 != 0)
       return fail(KDA_ERR_INVALID_ARG, "kda: h0 and ht must be 16-byte aligned%s", "");
   const int vs = a->k2_vsplit, var = a->k2_variant;
-  if (var < 0 || var > 4 || var == 2)
-    return fail(KDA_ERR_INVALID_ARG, "kda: k2_variant must be 0, 1, 3 or 4%s (got %lld)", "", var);
+  if (var < 0 || var > 5 || var == 2)
+    return fail(KDA_ERR_INVALID_ARG, "kda: k2_variant must be 0, 1, 3, 4 or 5%s (got %lld)", "", var);
   if (var == 4 && state_only)
     return fail(KDA_ERR_INVALID_ARG, "kda: the tensor-memory K2 (k2_variant 4) has no state-only form%s", "");
   if (var == 4) return KDA_OK;
   if (vs != 0 && vs != 2 && vs != 4 && vs != 8 && vs != 16)
     return fail(KDA_ERR_INVALID_ARG, "kda: k2_vsplit must be 0, 2, 4, 8 or 16%s (got %lld)", "", vs);
-  if (vs != 0 && var != 0 && ((var == 1) ? (vs < 4) : (vs > 8)))
+  if (vs != 0 && var != 0 && ((var == 1 || var == 5) ? (vs < 4) : (vs > 8)))
     return fail(KDA_ERR_INVALID_ARG, "kda: k2_vsplit %lld%s does not go with k2_variant %lld", "", vs, var);
   return KDA_OK;
 }
@@ -131,11 +131,11 @@ void pick_split(const KdaFwdArgs* a, bool state_only, int* vsplit, int* variant,
     else var = (bh * 4 <= sms) ? 1 : 3;
   }
   if (vs == 0) {
-    if (var == 1) vs = (bh * 16 <= sms) ? 16 : (bh * 8 <= sms) ? 8 : 4;
+    if (var == 1 || var == 5) vs = (bh * 16 <= sms) ? 16 : (bh * 8 <= sms) ? 8 : 4;
     else vs = (bh * 4 <= sms) ? 4 : 2;
   }
-  if (var == 1 && vs < 4) vs = 4;
-  if (var != 1 && vs > 8) vs = 8;
+  if ((var == 1 || var == 5) && vs < 4) vs = 4;
+  if (var != 1 && var != 5 && vs > 8) vs = 8;
   *vsplit = vs;
   *variant = var;
 }
@@ -244,7 +244,7 @@ int do_k2(const KdaFwdArgs* a, bool state_only, int zero_u, cudaStream_t st) {
     if (a->k2_variant == 0 && a->k2_vsplit == 0 && 2 * bh * 4 <= sms) {
       p.n_chains = static_cast<int>(2 * bh);
       pe = kda::launch_k2n(p, 2 * bh * 16 <= sms ? 16 : 2 * bh * 8 <= sms ? 8 : 4, 1, true, st);
-    } else if (variant == 1) {
+    } else if (variant == 1 || variant == 5) {
       p.pair_mode = 0;   // the pair is compiled into the kernel
       pe = kda::launch_k2n_pair(p, vsplit, st);
     } else {
@@ -285,7 +285,9 @@ int do_k2(const KdaFwdArgs* a, bool state_only, int zero_u, cudaStream_t st) {
       e = kda::launch_k2t(p, n_records, st);
     }
   } else {
-    e = (variant == 3) ? kda::launch_k2m(p, vsplit, state_only, st) : kda::launch_k2n(p, vsplit, 1, state_only, st);
+    e = (variant == 3) ? kda::launch_k2m(p, vsplit, state_only, st)
+        : (variant == 5) ? kda::launch_k2la(p, vsplit, state_only, st)
+                         : kda::launch_k2n(p, vsplit, 1, state_only, st);
   }
   if (e != cudaSuccess) return fail(KDA_ERR_CUDA, "kda: K2 launch failed: %s", cudaGetErrorString(e));
   ++g_launches;
@@ -458,8 +460,8 @@ int kda_fwd_status(const void* workspace, void* stream, int32_t* status_out) {
 int kda_fwd_k2_choice(const KdaFwdArgs* args, int state_only, int sm_count, int32_t* variant_out, int32_t* vsplit_out) {
   if (args == nullptr || variant_out == nullptr || vsplit_out == nullptr)
     return fail(KDA_ERR_INVALID_ARG, "kda: null pointer%s", "");
-  if (args->k2_variant < 0 || args->k2_variant > 4 || args->k2_variant == 2)
-    return fail(KDA_ERR_INVALID_ARG, "kda: k2_variant%s %lld is not one of 0, 1, 3, 4", "", static_cast<long long>(args->k2_variant));
+  if (args->k2_variant < 0 || args->k2_variant > 5 || args->k2_variant == 2)
+    return fail(KDA_ERR_INVALID_ARG, "kda: k2_variant%s %lld is not one of 0, 1, 3, 4, 5", "", static_cast<long long>(args->k2_variant));
   int vs = 0, var = 0;
   pick_split(args, state_only != 0, &vs, &var, sm_count);
   *variant_out = var;

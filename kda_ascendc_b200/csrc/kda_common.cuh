@@ -203,6 +203,14 @@ __device__ __forceinline__ void mma_bf16_v(float (&d)[4], const uint32_t (&a)[4]
       : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 
+// D = A * B with a zero accumulator: the first MMA of a chain needs no register initialisation
+__device__ __forceinline__ void mma_bf16_z(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+      : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1), "f"(0.f));
+}
+
 // Read-only global loads pinned where they are written: used to fetch per-item parameters a whole
 // iteration before their use, which the compiler would otherwise sink next to the use.
 __device__ __forceinline__ float ldg_pinned(const float* p) {

@@ -111,7 +111,8 @@ __global__ void __launch_bounds__(128, 4) kda_k1_kernel(const __grid_constant__ 
 
   if (tid == 0) {
     mbar_init(mbar, 1);
-    *sFlag = 0;
+    sFlag[0] = 0;   // a wait gave up
+    sFlag[1] = 0;   // the next item's q and k are already normalised
     fence_mbar_init();
   }
   __syncthreads();
@@ -155,7 +156,50 @@ __global__ void __launch_bounds__(128, 4) kda_k1_kernel(const __grid_constant__ 
     if (tid == 48) sBetaAll[32 + slot] = use_gate ? expf(q.a_log) : 1.f;
   };
 
+  // l2-normalisation of the q and k tiles in place: 8 threads per row, two 16-byte units each (units seg
+  // and seg + 8, so that a quarter-warp's 16-byte accesses cover 128 contiguous bytes).  `gid` numbers
+  // the participating threads 0 .. nthr-1 (whole warps, nthr a multiple of 32).
+  auto l2_normalise = [&](int gid, int nthr) {
+    for (int task = gid; task < 128; task += nthr) {
+      const int r = task >> 3, seg = task & 7;
+      uint4 qa[2], ka[2];
+      float sq = 0.f, sk = 0.f;
+#pragma unroll
+      for (int hseg = 0; hseg < 2; ++hseg) {
+        qa[hseg] = *reinterpret_cast<const uint4*>(smem + S_Q + r * 256 + (seg + hseg * 8) * 16);
+        ka[hseg] = *reinterpret_cast<const uint4*>(smem + S_K + r * 256 + (seg + hseg * 8) * 16);
+        const uint32_t aw[4] = {qa[hseg].x, qa[hseg].y, qa[hseg].z, qa[hseg].w};
+        const uint32_t cw[4] = {ka[hseg].x, ka[hseg].y, ka[hseg].z, ka[hseg].w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const float x0 = bf16_lo_to_f32(aw[i]), x1 = bf16_hi_to_f32(aw[i]);
+          const float y0 = bf16_lo_to_f32(cw[i]), y1 = bf16_hi_to_f32(cw[i]);
+          sq = fmaf(x0, x0, sq); sq = fmaf(x1, x1, sq);
+          sk = fmaf(y0, y0, sk); sk = fmaf(y1, y1, sk);
+        }
+      }
+#pragma unroll
+      for (int m = 1; m < 8; m <<= 1) {
+        sq += __shfl_xor_sync(0xffffffffu, sq, m);
+        sk += __shfl_xor_sync(0xffffffffu, sk, m);
+      }
+      const float rq = rsqrtf(sq + L2NORM_EPS), rk = rsqrtf(sk + L2NORM_EPS);
+      auto scale4 = [](uint4 v, float f) {
+        uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) w[i] = pack_bf16(bf16_lo_to_f32(w[i]) * f, bf16_hi_to_f32(w[i]) * f);
+        return make_uint4(w[0], w[1], w[2], w[3]);
+      };
+#pragma unroll
+      for (int hseg = 0; hseg < 2; ++hseg) {
+        *reinterpret_cast<uint4*>(smem + S_Q + r * 256 + (seg + hseg * 8) * 16) = scale4(qa[hseg], rq);
+        *reinterpret_cast<uint4*>(smem + S_K + r * 256 + (seg + hseg * 8) * 16) = scale4(ka[hseg], rk);
+      }
+    }
+  };
+
   int id = blockIdx.x;
+  bool pre_normalised = false;   // the current item's q and k were normalised one iteration early
   K1Item cur{}, nxt{};
   Par par{}, par_next{};
   if (id < n_items) {
@@ -181,43 +225,9 @@ __global__ void __launch_bounds__(128, 4) kda_k1_kernel(const __grid_constant__ 
     const bool ok = mbar_wait_bounded(mbar, it & 1, sFlag);
     if (!ok) *sFlag = 1;
 
-    // ---- phase A: l2-normalise q and k in place (8 threads per row, 16 elements each) ----
-    if (use_l2 && ok) {
-      const int r = tid >> 3, seg = tid & 7;
-      uint4 qa[2], ka[2];
-      float sq = 0.f, sk = 0.f;
-#pragma unroll
-      for (int hseg = 0; hseg < 2; ++hseg) {
-        qa[hseg] = *reinterpret_cast<const uint4*>(smem + S_Q + r * 256 + seg * 32 + hseg * 16);
-        ka[hseg] = *reinterpret_cast<const uint4*>(smem + S_K + r * 256 + seg * 32 + hseg * 16);
-        const uint32_t aw[4] = {qa[hseg].x, qa[hseg].y, qa[hseg].z, qa[hseg].w};
-        const uint32_t cw[4] = {ka[hseg].x, ka[hseg].y, ka[hseg].z, ka[hseg].w};
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          const float x0 = bf16_lo_to_f32(aw[i]), x1 = bf16_hi_to_f32(aw[i]);
-          const float y0 = bf16_lo_to_f32(cw[i]), y1 = bf16_hi_to_f32(cw[i]);
-          sq = fmaf(x0, x0, sq); sq = fmaf(x1, x1, sq);
-          sk = fmaf(y0, y0, sk); sk = fmaf(y1, y1, sk);
-        }
-      }
-#pragma unroll
-      for (int m = 1; m < 8; m <<= 1) {
-        sq += __shfl_xor_sync(0xffffffffu, sq, m);
-        sk += __shfl_xor_sync(0xffffffffu, sk, m);
-      }
-      const float rq = rsqrtf(sq + L2NORM_EPS), rk = rsqrtf(sk + L2NORM_EPS);
-      auto scale4 = [](uint4 v, float f) {
-        uint32_t w[4] = {v.x, v.y, v.z, v.w};
-#pragma unroll
-        for (int i = 0; i < 4; ++i) w[i] = pack_bf16(bf16_lo_to_f32(w[i]) * f, bf16_hi_to_f32(w[i]) * f);
-        return make_uint4(w[0], w[1], w[2], w[3]);
-      };
-#pragma unroll
-      for (int hseg = 0; hseg < 2; ++hseg) {
-        *reinterpret_cast<uint4*>(smem + S_Q + r * 256 + seg * 32 + hseg * 16) = scale4(qa[hseg], rq);
-        *reinterpret_cast<uint4*>(smem + S_K + r * 256 + seg * 32 + hseg * 16) = scale4(ka[hseg], rk);
-      }
-    }
+    // ---- phase A: l2-normalise q and k in place, unless warps 1..3 already did it under the previous
+    //      item's solve ----
+    if (use_l2 && ok && !pre_normalised) l2_normalise(tid, 128);
     __syncthreads();
     if (*sFlag != 0) {
       // a copy never completed: report, give in-flight copies one more bounded wait, leave
@@ -422,6 +432,15 @@ __global__ void __launch_bounds__(128, 4) kda_k1_kernel(const __grid_constant__ 
     // next item's scalar parameters (warp 1, while warp 0 solves)
     if (has_next) publish_params(par_next, nxt.nvalid, (it + 1) & 1);
 
+    // Warps 1..3 have nothing to do during the solve.  The next item's inputs were requested two
+    // phases ago: if they have landed already (one probe, no waiting), those warps normalise its q
+    // and k now, and the next iteration starts at the gate phase.
+    if (warp != 0 && use_l2) {
+      if (tid == 32) sFlag[1] = (has_next && mbar_test_wait(mbar, (it + 1) & 1)) ? 1 : 0;
+      asm volatile("bar.sync 1, 96;" ::: "memory");   // warps 1..3 only
+      if (sFlag[1] != 0) l2_normalise(tid - 32, 96);
+    }
+
     // ---- phase D: X = (I + L)^-1, lane j of warp 0 owns column j ---------------
     // Column sweep (right-looking): once x[m] is final, every later row takes its update, so the
     // dependent chain is 16 FMAs long; -L is read four columns at a time.
@@ -454,6 +473,7 @@ __global__ void __launch_bounds__(128, 4) kda_k1_kernel(const __grid_constant__ 
     }
     fence_proxy_async();   // qg / kg / Aqk / dec tiles were written with plain stores
     __syncthreads();
+    const bool pre_next = use_l2 && sFlag[1] != 0;
 
     // the finished tiles leave while phase E runs
     if (tid == 0) {
@@ -512,6 +532,7 @@ __global__ void __launch_bounds__(128, 4) kda_k1_kernel(const __grid_constant__ 
     }
     cur = nxt;
     par = par_next;
+    pre_normalised = pre_next;
   }
   if (tid == 0) bulk_wait_read_all();
 }

@@ -230,16 +230,22 @@ __global__ void __launch_bounds__((CW + 1) * 32, 1) kda_k2_kernel(const K2Params
 
       // P1 (two accumulator sets: even / odd k-steps), carrying the kg fragment loads of this
       // step and the decay of the fp32 state
-      float pw[2][NVT][4] = {}, pq[2][NVT][4] = {};
+      float pw[2][NVT][4], pq[2][NVT][4];
       uint32_t kgh[8][4], kgl[8][4];
 #pragma unroll
       for (int ks = 0; ks < 8; ++ks) {
 #pragma unroll
-        for (int nv = 0; nv < NVT; ++nv) mma_bf16_v(pw[ks & 1][nv], aw[ks], bh[ks][nv][0], bh[ks][nv][1]);
+        for (int nv = 0; nv < NVT; ++nv) {
+          if (ks < 2) mma_bf16_z(pw[ks & 1][nv], aw[ks], bh[ks][nv][0], bh[ks][nv][1]);
+          else mma_bf16_v(pw[ks & 1][nv], aw[ks], bh[ks][nv][0], bh[ks][nv][1]);
+        }
         ldsm_x4_t((t2 ^ (ks << 5)) + REC_KGH, kgh[ks][0], kgh[ks][1], kgh[ks][2], kgh[ks][3]);
         if (!STATE_ONLY) {
 #pragma unroll
-          for (int nv = 0; nv < NVT; ++nv) mma_bf16_v(pq[ks & 1][nv], aq[ks], bh[ks][nv][0], bh[ks][nv][1]);
+          for (int nv = 0; nv < NVT; ++nv) {
+            if (ks < 2) mma_bf16_z(pq[ks & 1][nv], aq[ks], bh[ks][nv][0], bh[ks][nv][1]);
+            else mma_bf16_v(pq[ks & 1][nv], aq[ks], bh[ks][nv][0], bh[ks][nv][1]);
+          }
         }
         ldsm_x4_t((t2 ^ (ks << 5)) + REC_KGL, kgl[ks][0], kgl[ks][1], kgl[ks][2], kgl[ks][3]);
 #pragma unroll

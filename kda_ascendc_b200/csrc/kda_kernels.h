@@ -85,6 +85,11 @@ cudaError_t k1_encode_tensor_maps(K1Params& p, bool g_bf16, const char** what);
 // vsplit = CTAs per (batch, head).
 cudaError_t launch_k2n(const K2Params& p, int vsplit, int ntile, bool state_only, cudaStream_t stream);
 cudaError_t launch_k2m(const K2Params& p, int vsplit, bool state_only, cudaStream_t stream);
+//   "n8 look-ahead": the 8-row form with the products of chunk n+1 taken from the decayed state of
+//               step n plus a 16x16 cross-Gram correction, so that a step has no dependent hand-over;
+//               16 / vsplit in {1, 2, 4} consumer warps per CTA; measured slower than "n8", never
+//               chosen automatically                                           (kda_k2la_sm100.cu)
+cudaError_t launch_k2la(const K2Params& p, int vsplit, bool state_only, cudaStream_t stream);
 // the transform-pair pass of the sequence split in the "n8" form: both recurrences (M: identity entry
 // state without u; Q: zero entry state with u) on the same eight rows of one warp, so every operand
 // fragment read from shared memory feeds two MMAs; ht is [chains][2][128][128]
