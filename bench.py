@@ -439,7 +439,8 @@ def run_gpu_arm(steps, warmup, n_gpus, kernels_only=False):
             seq_split=dict(ms_per_step=ms_seq / steps, tokens_per_s=B * T * steps / (ms_seq * 1e-3),
                            tokens_per_gpu=L, exchange=plan.mode,
                            timeline_us={n: v * 1e3 for n, v in zip(ph_names, ph_max)},
-                           collectives="2 all-to-all (NCCL) per forward",
+                           sub_segments_per_rank=plan.sub,
+                           collectives="2 all-to-all (NCCL) per forward" if plan.mode == "a2a" else "1 all-gather (NCCL) per forward",
                            max_abs_vs_one_gpu=dict(o=e_s_o, ht=e_s_s)),
             limiter="K2 is one serial chain of T/16 chunk steps per head: fewer heads per GPU shorten K1 only, "
                     "fewer tokens per GPU shorten every kernel but add the transform pass and the exchange")
@@ -475,7 +476,7 @@ def run_gpu_arm(steps, warmup, n_gpus, kernels_only=False):
         res = max_over_ranks([ms_sp, t_one, e_o, e_h] + [v for _, v in ph])
         seq_parallel = dict(workload="KDA fwd B=1 T=%d H=%d, %d contiguous segments of %d tokens" % (SP_T, SP_H, world, Ll),
                             ms=res[0], tokens_per_s=SP_T / (res[0] * 1e-3), one_gpu_ms=res[1],
-                            speedup_over_one_gpu=res[1] / res[0], exchange=plan.mode,
+                            speedup_over_one_gpu=res[1] / res[0], exchange=plan.mode, sub_segments_per_rank=plan.sub,
                             timeline_us={n: v * 1e3 for (n, _), v in zip(ph, res[4:])},
                             max_abs_vs_one_gpu=dict(o=res[2], ht=res[3]), o_bound=O_TOL, ht_bound=HT_TOL)
         del plan, dl, o1, h1, o2, h2

@@ -147,6 +147,28 @@ int kda_fwd_k2_state(const KdaFwdArgs* args, int zero_u, void* stream);
 int kda_state_fold(const float* mq, int64_t seg_stride, int64_t chain_stride, const float* h0, float* s_in,
                    int32_t n_chains, int32_t n_seg, int32_t* status, void* stream);
 
+/* The same walk with every layout choice exposed (what the two-level sequence split uses: a rank
+ * first composes the transforms of its own sub-segments, then walks its sub-segments from the entry
+ * state the exchange returns).  h0_stride / final_stride: floats between the states of consecutive
+ * chains, 0 = dense (128 x 128).  s_in and final_out are both optional (at least one): final_out
+ * receives only the state after the last segment, with its own chain stride, so that it can be
+ * written straight into an (M, Q) buffer.  use_q = 0 drops the offsets: S <- S * M_j, which with
+ * h0 = M_0 composes transition matrices (M_0 M_1 ... ); use_q = 1 with h0 = Q_0 over segments 1..
+ * composes the offsets (((Q_0 M_1 + Q_1) M_2 + Q_2) ...).  No reference counterpart. */
+typedef struct KdaFoldArgs {
+  const float* mq;        /* M_j[c] at mq + j * seg_stride + c * chain_stride; Q_j[c] 128 x 128 floats behind it */
+  int64_t seg_stride, chain_stride;
+  const float* h0;        /* or NULL (zeros) */
+  int64_t h0_stride;
+  float* s_in;            /* [n_seg + 1][n_chains][128][128] contiguous, or NULL */
+  float* final_out;       /* or NULL */
+  int64_t final_stride;
+  int32_t n_chains, n_seg;
+  int32_t use_q;
+  int32_t* status;        /* device word, or NULL */
+} KdaFoldArgs;
+int kda_state_fold_ex(const KdaFoldArgs* args, void* stream);
+
 /* Token-by-token recurrence for decode steps and short sequences (T of one to a few dozen
  * tokens): reads the state from args->h0 (NULL = zeros), applies args->T tokens, writes the
  * outputs to args->o and the new state to args->ht (may be NULL; may be the same buffer as h0

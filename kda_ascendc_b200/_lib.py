@@ -17,7 +17,7 @@ FLAG_GATE, FLAG_L2NORM, FLAG_BETA_SIGMOID, FLAG_STATE_K_FIRST = 1, 2, 4, 8
 EXPORTS = (
     "kda_fwd_workspace_bytes", "kda_fwd", "kda_fwd_k1", "kda_fwd_k2", "kda_fwd_k2_state", "kda_recurrent_fwd",
     "kda_varlen_fill_tables", "kda_selftest_bounded_wait", "kda_fwd_static_scratch",
-    "kda_fwd_static_scratch_status", "kda_state_fold",
+    "kda_fwd_static_scratch_status", "kda_state_fold", "kda_state_fold_ex",
     "kda_fwd_status", "kda_fwd_k2_choice", "kda_last_launch_count", "kda_last_error", "kda_version",
 )
 
@@ -35,6 +35,16 @@ class KdaFwdArgs(ctypes.Structure):
         ("k2_vsplit", ctypes.c_int32), ("k2_variant", ctypes.c_int32),
         ("n_seqs", ctypes.c_int32), ("chunk_table", ctypes.c_void_p), ("seq_table", ctypes.c_void_p),
         ("n_chunks", ctypes.c_int32), ("Hq", ctypes.c_int32),
+    ]
+
+
+class KdaFoldArgs(ctypes.Structure):
+    _fields_ = [
+        ("mq", ctypes.c_void_p), ("seg_stride", ctypes.c_int64), ("chain_stride", ctypes.c_int64),
+        ("h0", ctypes.c_void_p), ("h0_stride", ctypes.c_int64),
+        ("s_in", ctypes.c_void_p), ("final_out", ctypes.c_void_p), ("final_stride", ctypes.c_int64),
+        ("n_chains", ctypes.c_int32), ("n_seg", ctypes.c_int32), ("use_q", ctypes.c_int32),
+        ("status", ctypes.c_void_p),
     ]
 
 
@@ -62,6 +72,8 @@ def load() -> ctypes.CDLL:
     lib.kda_state_fold.restype = ctypes.c_int
     lib.kda_state_fold.argtypes = [ctypes.c_void_p, ctypes.c_int64, ctypes.c_int64, ctypes.c_void_p, ctypes.c_void_p,
                                    ctypes.c_int32, ctypes.c_int32, ctypes.c_void_p, ctypes.c_void_p]
+    lib.kda_state_fold_ex.restype = ctypes.c_int
+    lib.kda_state_fold_ex.argtypes = [ctypes.POINTER(KdaFoldArgs), ctypes.c_void_p]
     lib.kda_selftest_bounded_wait.restype = ctypes.c_int
     lib.kda_selftest_bounded_wait.argtypes = [ctypes.c_void_p, ctypes.c_void_p]
     lib.kda_varlen_fill_tables.restype = ctypes.c_int

@@ -391,29 +391,52 @@ int kda_recurrent_fwd(const KdaFwdArgs* a, void* stream) {
   return KDA_OK;
 }
 
-int kda_state_fold(const float* mq, int64_t seg_stride, int64_t chain_stride, const float* h0, float* s_in,
-                   int32_t n_chains, int32_t n_seg, int32_t* status, void* stream) {
+int kda_state_fold_ex(const KdaFoldArgs* f, void* stream) {
   g_launches = 0;
-  if (mq == nullptr || s_in == nullptr) return fail(KDA_ERR_INVALID_ARG, "kda: the fold needs mq and s_in%s", "");
-  if (n_chains <= 0 || n_seg < 0)
-    return fail(KDA_ERR_INVALID_ARG, "kda: the fold needs n_chains > 0 and n_seg >= 0%s (got %lld, %lld)", "", n_chains, n_seg);
-  const int64_t pair = 2LL * kda::D * kda::D;
-  if (n_seg > 0 && (chain_stride < pair || (n_seg > 1 && seg_stride < pair)))
-    return fail(KDA_ERR_INVALID_ARG, "kda: the fold's strides must span an (M, Q) pair of 2 x 128 x 128 floats%s", "");
-  if (seg_stride % 4 != 0 || chain_stride % 4 != 0)
+  if (f == nullptr) return fail(KDA_ERR_INVALID_ARG, "kda: fold args is NULL%s", "");
+  if (f->mq == nullptr || (f->s_in == nullptr && f->final_out == nullptr))
+    return fail(KDA_ERR_INVALID_ARG, "kda: the fold needs mq and at least one of s_in / final_out%s", "");
+  if (f->n_chains <= 0 || f->n_seg < 0)
+    return fail(KDA_ERR_INVALID_ARG, "kda: the fold needs n_chains > 0 and n_seg >= 0%s (got %lld, %lld)", "", f->n_chains, f->n_seg);
+  const int64_t state = static_cast<int64_t>(kda::D) * kda::D;
+  const int64_t span = f->use_q ? 2 * state : state;   // without Q only the M block has to lie inside a stride
+  if (f->n_seg > 0 && ((f->n_chains > 1 && f->chain_stride < span) || (f->n_seg > 1 && f->seg_stride < span)))
+    return fail(KDA_ERR_INVALID_ARG, "kda: the fold's strides must span the 128 x 128 blocks they step over%s", "");
+  if (f->seg_stride % 4 != 0 || f->chain_stride % 4 != 0)
     return fail(KDA_ERR_INVALID_ARG, "kda: the fold's strides must be multiples of 4 floats%s (every M_j is copied 16 bytes at a time)", "");
-  if (status != nullptr && reinterpret_cast<uintptr_t>(status) % 4 != 0)
+  const int64_t h0_stride = f->h0_stride != 0 ? f->h0_stride : state;
+  const int64_t final_stride = f->final_stride != 0 ? f->final_stride : state;
+  if (h0_stride < state || final_stride < state)
+    return fail(KDA_ERR_INVALID_ARG, "kda: h0_stride and final_stride must be 0 (dense) or at least 128 x 128%s", "");
+  if (f->status != nullptr && reinterpret_cast<uintptr_t>(f->status) % 4 != 0)
     return fail(KDA_ERR_INVALID_ARG, "kda: status must be 4-byte aligned%s", "");
-  for (const void* ptr : {static_cast<const void*>(mq), static_cast<const void*>(h0), static_cast<const void*>(s_in)})
+  for (const void* ptr : {static_cast<const void*>(f->mq), static_cast<const void*>(f->h0), static_cast<const void*>(f->s_in),
+                          static_cast<const void*>(f->final_out)})
     if (ptr != nullptr && reinterpret_cast<uintptr_t>(ptr) % 16 != 0)
-      return fail(KDA_ERR_INVALID_ARG, "kda: mq, h0 and s_in must be 16-byte aligned%s", "");
-  if (static_cast<long long>(n_chains) * (kda::D / 4) > 0x7fffffffLL)
+      return fail(KDA_ERR_INVALID_ARG, "kda: mq, h0, s_in and final_out must be 16-byte aligned%s", "");
+  if (static_cast<long long>(f->n_chains) * (kda::D / 4) > 0x7fffffffLL)
     return fail(KDA_ERR_INVALID_ARG, "kda: too many chains for one fold launch%s", "");
-  cudaError_t e = kda::launch_state_fold(mq, seg_stride, chain_stride, h0, s_in, n_chains, n_seg, status,
-                                         static_cast<cudaStream_t>(stream));
+  kda::FoldParams p;
+  memset(&p, 0, sizeof(p));
+  p.mq = f->mq; p.seg_stride = f->seg_stride; p.chain_stride = f->chain_stride;
+  p.h0 = f->h0; p.h0_stride = h0_stride;
+  p.s_in = f->s_in; p.final_out = f->final_out; p.final_stride = final_stride;
+  p.n_chains = f->n_chains; p.n_seg = f->n_seg; p.use_q = f->use_q ? 1 : 0;
+  p.status = f->status;
+  cudaError_t e = kda::launch_state_fold(p, static_cast<cudaStream_t>(stream));
   if (e != cudaSuccess) return fail(KDA_ERR_CUDA, "kda: fold launch failed: %s", cudaGetErrorString(e));
   ++g_launches;
   return KDA_OK;
+}
+
+int kda_state_fold(const float* mq, int64_t seg_stride, int64_t chain_stride, const float* h0, float* s_in,
+                   int32_t n_chains, int32_t n_seg, int32_t* status, void* stream) {
+  if (s_in == nullptr) return fail(KDA_ERR_INVALID_ARG, "kda: the fold needs mq and s_in%s", "");
+  KdaFoldArgs f;
+  memset(&f, 0, sizeof(f));
+  f.mq = mq; f.seg_stride = seg_stride; f.chain_stride = chain_stride; f.h0 = h0; f.s_in = s_in;
+  f.n_chains = n_chains; f.n_seg = n_seg; f.use_q = 1; f.status = status;
+  return kda_state_fold_ex(&f, stream);
 }
 
 int kda_varlen_fill_tables(const int32_t* cu, int32_t n_seqs, int32_t H, int32_t* chunk_table, int32_t* seq_table) {

@@ -37,8 +37,13 @@ struct FoldSmem {
 
 template <int ROWS>
 __global__ void __launch_bounds__(D, 1)
-kda_state_fold_kernel(const float* __restrict__ mq, long long seg_stride, long long chain_stride,
-                      const float* __restrict__ h0, float* __restrict__ s_in, int n_chains, int n_seg, int* status) {
+kda_state_fold_kernel(const FoldParams p) {
+  const float* __restrict__ mq = p.mq;
+  const float* __restrict__ h0 = p.h0;
+  float* __restrict__ s_in = p.s_in;
+  const long long seg_stride = p.seg_stride, chain_stride = p.chain_stride;
+  const int n_chains = p.n_chains, n_seg = p.n_seg;
+  int* status = p.status;
   extern __shared__ __align__(1024) uint8_t smem[];
   using SM = FoldSmem<ROWS>;
   const int t = threadIdx.x;
@@ -74,19 +79,18 @@ kda_state_fold_kernel(const float* __restrict__ mq, long long seg_stride, long l
   float s[ROWS];
 #pragma unroll
   for (int r = 0; r < ROWS; ++r)
-    s[r] = (h0 != nullptr) ? h0[chain * state_elems + static_cast<size_t>(r0 + r) * D + t] : 0.f;
+    s[r] = (h0 != nullptr) ? h0[static_cast<size_t>(chain) * p.h0_stride + static_cast<size_t>(r0 + r) * D + t] : 0.f;
   __syncthreads();   // barriers initialised
 
   int issued = n_seg < 2 ? n_seg : 2;
   for (int j = 0; j < n_seg; ++j) {
-    float* out = s_in + (static_cast<size_t>(j) * n_chains + chain) * state_elems;
     const float* Q = m_ptr(j) + state_elems;
     float acc[ROWS];
 #pragma unroll
     for (int r = 0; r < ROWS; ++r) {
-      out[static_cast<size_t>(r0 + r) * D + t] = s[r];
+      if (s_in != nullptr) s_in[(static_cast<size_t>(j) * n_chains + chain) * state_elems + static_cast<size_t>(r0 + r) * D + t] = s[r];
       sS[j & 1][r][t] = s[r];
-      acc[r] = __ldg(Q + static_cast<size_t>(r0 + r) * D + t);
+      acc[r] = p.use_q ? __ldg(Q + static_cast<size_t>(r0 + r) * D + t) : 0.f;
     }
     const bool ok = mbar_wait_bounded(full0 + (j & 1) * 8, (j >> 1) & 1, sAbort);
     if (!ok) *sAbort = 1;
@@ -126,14 +130,15 @@ kda_state_fold_kernel(const float* __restrict__ mq, long long seg_stride, long l
     __syncthreads();
     return;
   }
-  float* out = s_in + (static_cast<size_t>(n_seg) * n_chains + chain) * state_elems;
 #pragma unroll
-  for (int r = 0; r < ROWS; ++r) out[static_cast<size_t>(r0 + r) * D + t] = s[r];
+  for (int r = 0; r < ROWS; ++r) {
+    if (s_in != nullptr) s_in[(static_cast<size_t>(n_seg) * n_chains + chain) * state_elems + static_cast<size_t>(r0 + r) * D + t] = s[r];
+    if (p.final_out != nullptr) p.final_out[static_cast<size_t>(chain) * p.final_stride + static_cast<size_t>(r0 + r) * D + t] = s[r];
+  }
 }
 
 template <int ROWS>
-static cudaError_t launch_fold_t(const float* mq, long long seg_stride, long long chain_stride, const float* h0,
-                                 float* s_in, int n_chains, int n_seg, int* status, cudaStream_t stream) {
+static cudaError_t launch_fold_t(const FoldParams& p, cudaStream_t stream) {
   constexpr int smem_bytes = FoldSmem<ROWS>::TOTAL;
   static bool configured[64] = {};
   int dev = 0;
@@ -143,20 +148,18 @@ static cudaError_t launch_fold_t(const float* mq, long long seg_stride, long lon
     if (e != cudaSuccess) return e;
     configured[dev] = true;
   }
-  kda_state_fold_kernel<ROWS><<<n_chains * (D / ROWS), D, smem_bytes, stream>>>(mq, seg_stride, chain_stride, h0, s_in,
-                                                                               n_chains, n_seg, status);
+  kda_state_fold_kernel<ROWS><<<p.n_chains * (D / ROWS), D, smem_bytes, stream>>>(p);
   return cudaGetLastError();
 }
 
-cudaError_t launch_state_fold(const float* mq, long long seg_stride, long long chain_stride, const float* h0,
-                              float* s_in, int n_chains, int n_seg, int* status, cudaStream_t stream) {
+cudaError_t launch_state_fold(const FoldParams& p, cudaStream_t stream) {
   int dev = 0, sms = 148;
   if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   // Measured on B200 (8 segments): the walk is bound by the L2-to-shared copies of M_j (every CTA of a
   // chain pulls all 64 KiB of it), so few rows per CTA only pay while the CTAs fit one wave:
   // 4 chains 23 us with 4 rows per CTA against 35 us with 16; 32 chains 100 us against 65 us.
-  if (n_chains * (D / 4) <= sms) return launch_fold_t<4>(mq, seg_stride, chain_stride, h0, s_in, n_chains, n_seg, status, stream);
-  return launch_fold_t<16>(mq, seg_stride, chain_stride, h0, s_in, n_chains, n_seg, status, stream);
+  if (p.n_chains * (D / 4) <= sms) return launch_fold_t<4>(p, stream);
+  return launch_fold_t<16>(p, stream);
 }
 
 }  // namespace kda

@@ -99,8 +99,19 @@ cudaError_t launch_k2n_pair(const K2Params& p, int vsplit, cudaStream_t stream);
 cudaError_t launch_k2t(const K2Params& p, long long n_records, cudaStream_t stream);
 
 // Walk of the per-segment affine state transforms of a sequence split (kda_fold_sm100.cu).
-cudaError_t launch_state_fold(const float* mq, long long seg_stride, long long chain_stride, const float* h0,
-                              float* s_in, int n_chains, int n_seg, int* status, cudaStream_t stream);
+struct FoldParams {
+  const float* mq;             // M_j[c] at mq + j*seg_stride + c*chain_stride (floats), Q_j[c] 128*128 floats behind it
+  long long seg_stride, chain_stride;
+  const float* h0;             // entry state of chain c at h0 + c*h0_stride, or null (zeros)
+  long long h0_stride;
+  float* s_in;                 // [n_seg + 1][n_chains][128][128] or null: the state before every segment and after the last
+  float* final_out;            // or null: the state after the last segment of chain c at final_out + c*final_stride
+  long long final_stride;
+  int n_chains, n_seg;
+  int use_q;                   // 0: the walk is S <- S * M_j (composition of transition matrices)
+  int* status;
+};
+cudaError_t launch_state_fold(const FoldParams& p, cudaStream_t stream);
 
 // Token recurrence (decode / short sequences): no chunking, no workspace (kda_recurrent_sm100.cu).
 struct RecurrentParams {

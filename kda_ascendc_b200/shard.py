@@ -95,48 +95,69 @@ def compose_entry_states(M: Sequence[torch.Tensor], Q: Sequence[torch.Tensor],
     return out
 
 
+def _walk_cuda(mq, h0, n_seg, *, use_q=True, s_in=None, final_out=None, status=None):
+    """``kda_state_fold_ex`` on tensors.  ``mq``: fp32 ``[segments, chains, 2, 128, 128]`` view (any segment /
+    chain strides, dense 128 x 128 blocks, Q behind M); ``h0`` / ``final_out``: ``[chains, 128, 128]`` views
+    (any chain stride) or None; ``s_in``: contiguous ``[n_seg + 1, chains, 128, 128]`` or None."""
+    if not mq.is_cuda:
+        raise RuntimeError("the fold runs the CUDA kernel kda_state_fold; there is no CPU path")
+    chains = mq.shape[1]
+    for t, name in ((mq, "mq"), (h0, "h0"), (final_out, "final_out")):
+        if t is not None and (t.dtype != torch.float32 or t.stride()[-2:] != (D, 1)):
+            raise ValueError(f"{name} must be fp32 with dense 128 x 128 blocks")
+    if mq.ndim != 5 or mq.shape[2:] != (2, D, D) or mq.stride(2) != D * D:
+        raise ValueError("mq must be [segments, chains, 2, 128, 128] with Q directly behind M")
+    f = _lib.KdaFoldArgs()
+    f.mq = mq.data_ptr()
+    f.seg_stride, f.chain_stride = (mq.stride(0) if mq.shape[0] > 1 else 2 * D * D), (mq.stride(1) if chains > 1 else 2 * D * D)
+    if h0 is not None:
+        f.h0, f.h0_stride = h0.data_ptr(), (h0.stride(0) if chains > 1 else D * D)
+    if s_in is not None:
+        if tuple(s_in.shape) != (n_seg + 1, chains, D, D) or not s_in.is_contiguous() or s_in.dtype != torch.float32:
+            raise ValueError("s_in must be a contiguous fp32 [n_seg + 1, chains, 128, 128] tensor")
+        f.s_in = s_in.data_ptr()
+    if final_out is not None:
+        f.final_out, f.final_stride = final_out.data_ptr(), (final_out.stride(0) if chains > 1 else D * D)
+    f.n_chains, f.n_seg, f.use_q = chains, n_seg, int(bool(use_q))
+    if status is not None:
+        f.status = status.data_ptr()
+    with torch.cuda.device(mq.device):
+        api._check(_lib.load().kda_state_fold_ex(ctypes.byref(f), api._stream_handle()))
+
+
+def _walk_torch(mq, h0, n_seg, *, use_q=True, s_in=None, final_out=None, status=None):
+    """The same contract in plain torch (CPU tensors: the gloo tests)."""
+    chains = mq.shape[1]
+    S = torch.zeros(chains, D, D, dtype=torch.float32, device=mq.device) if h0 is None else h0.clone().float()
+    for j in range(n_seg):
+        if s_in is not None:
+            s_in[j].copy_(S)
+        S = torch.matmul(S, mq[j, :, 0])
+        if use_q:
+            S = S + mq[j, :, 1]
+    if s_in is not None:
+        s_in[n_seg].copy_(S)
+    if final_out is not None:
+        final_out.copy_(S)
+
+
 def fold_states(mq: torch.Tensor, h0: Optional[torch.Tensor], out: Optional[torch.Tensor] = None,
                 n_seg: Optional[int] = None, status: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """``kda_state_fold`` on a CUDA tensor ``mq [n_seg_total, n_chains, 2, 128, 128]`` (fp32; ``M`` then
+    """The fold kernel on a CUDA tensor ``mq [n_seg_total, n_chains, 2, 128, 128]`` (fp32; ``M`` then
     ``Q`` per chain, any segment / chain strides): returns ``s_in [n_seg + 1, n_chains, 128, 128]`` --
     the entry state of segments ``0..n_seg-1`` and the state after segment ``n_seg - 1``
     (``n_seg`` defaults to all segments of ``mq``).  ``status``: a workspace (or any int32 device
     tensor) whose first word receives a code if a bounded wait inside the kernel gives up."""
-    if not mq.is_cuda:
-        raise RuntimeError("fold_states runs the CUDA kernel kda_state_fold; there is no CPU path")
-    if mq.dtype != torch.float32 or mq.ndim != 5 or mq.shape[2:] != (2, D, D) or mq.stride()[2:] != (D * D, D, 1):
-        raise ValueError("mq must be fp32 [segments, chains, 2, 128, 128] with dense (M, Q) pairs")
     segs, chains = mq.shape[:2]
     n_seg = segs if n_seg is None else n_seg
     if not 0 <= n_seg <= segs:
         raise ValueError(f"n_seg={n_seg} outside 0..{segs}")
     if out is None:
         out = torch.empty((n_seg + 1, chains, D, D), dtype=torch.float32, device=mq.device)
-    elif out.shape != (n_seg + 1, chains, D, D) or not out.is_contiguous() or out.dtype != torch.float32:
-        raise ValueError("out must be a contiguous fp32 [n_seg + 1, chains, 128, 128] tensor")
     if h0 is not None:
         h0 = h0.reshape(chains, D, D)
-        if h0.dtype != torch.float32 or not h0.is_contiguous():
-            raise ValueError("h0 must be contiguous fp32 [chains, 128, 128]")
-    with torch.cuda.device(mq.device):
-        api._check(_lib.load().kda_state_fold(ctypes.c_void_p(mq.data_ptr()), mq.stride(0), mq.stride(1),
-                                              None if h0 is None else ctypes.c_void_p(h0.data_ptr()),
-                                              ctypes.c_void_p(out.data_ptr()), chains, n_seg,
-                                              None if status is None else ctypes.c_void_p(status.data_ptr()),
-                                              api._stream_handle()))
+    _walk_cuda(mq, h0, n_seg, s_in=out, status=status)
     return out
-
-
-def _torch_fold(mq, h0, out=None, n_seg=None):
-    """Same contract as :func:`fold_states` in plain torch (CPU tensors: the gloo tests)."""
-    n_seg = mq.shape[0] if n_seg is None else n_seg
-    st = compose_entry_states([mq[j, :, 0] for j in range(n_seg)], [mq[j, :, 1] for j in range(n_seg)],
-                              torch.zeros_like(mq[0, :, 0]) if h0 is None else h0.reshape(mq.shape[1], D, D))
-    res = torch.stack(st)
-    if out is not None:
-        out.copy_(res)
-        return out
-    return res
 
 
 def exchange_mode(chains: int, world: int, requested: str = "auto") -> str:
@@ -151,30 +172,36 @@ def exchange_mode(chains: int, world: int, requested: str = "auto") -> str:
 
 
 def exchange_and_fold(mq_local: torch.Tensor, h0: Optional[torch.Tensor], rank: int, world: int, *, group=None,
-                      mode: str = "a2a", sub: int = 1, fold=None, bufs: Optional[dict] = None,
-                      want_final: bool = False, status: Optional[torch.Tensor] = None):
+                      mode: str = "a2a", sub: int = 1, two_level: Optional[bool] = None, walk=None,
+                      bufs: Optional[dict] = None, want_final: bool = False, status: Optional[torch.Tensor] = None):
     """From this rank's transforms to the entry states of its segment(s).
 
     ``mq_local``: ``[sub * chains, 2, 128, 128]`` -- ``sub`` consecutive sub-segments of this rank
     (sub-segment major), ``chains`` (batch, head) chains each.  Returns ``(s_entry, final | None)``:
     ``s_entry [sub, chains, 128, 128]`` are the entry states of this rank's sub-segments and
     ``final [chains, 128, 128]`` the state after the last segment of the last rank, on every rank
-    when ``want_final`` (one more small all-gather in all-to-all mode).  ``sub > 1`` needs the
-    all-gather exchange.  ``bufs``: optional dict the function keeps its receive / send buffers in,
-    so a plan allocates them once.  ``fold``: the fold routine (default: the CUDA kernel).
+    when ``want_final`` (one more small all-gather in all-to-all mode).
+
+    Two levels when ``sub > 1``: the rank first composes the transforms of its own sub-segments into
+    one transform of its whole segment (two walks: the transition matrices, the offsets), only
+    those are exchanged and folded, and a last local walk from the returned entry state gives the
+    entry states of the rank's sub-segments -- the exchange and the cross-rank fold stay as small as
+    without sub-segments, at the price of three more small launches.  ``two_level=None`` takes it
+    when there are more than eight segments in all (measured: two ranks x two sub-segments 72 us
+    flat against 119 us in two levels; at 32 segments the flat all-gather alone moves 64 MB per
+    rank); the flat form all-gathers every sub-segment's transform and needs ``mode="gather"``.  ``bufs``: optional dict the function keeps its buffers in, so a plan
+    allocates them once.  ``walk``: the fold routine (default: the CUDA kernel; the CPU tests pass
+    the torch statement).
     """
     import torch.distributed as dist
 
-    fold = fold_states if fold is None else fold
+    walk = _walk_cuda if walk is None else walk
     bufs = {} if bufs is None else bufs
     if mq_local.shape[0] % sub:
         raise ValueError("mq_local does not hold a whole number of sub-segments")
     chains = mq_local.shape[0] // sub
-    if sub > 1 and mode != "gather":
-        raise ValueError("several segments per rank need the all-gather exchange")
     kw = dict(dtype=torch.float32, device=mq_local.device)
     h0c = None if h0 is None else h0.reshape(chains, D, D)
-    skw = {} if status is None else dict(status=status)
 
     def buf(name, shape):
         t = bufs.get(name)
@@ -182,26 +209,53 @@ def exchange_and_fold(mq_local: torch.Tensor, h0: Optional[torch.Tensor], rank: 
             t = bufs[name] = torch.empty(shape, **kw)
         return t
 
-    if mode == "gather":
+    mq5 = mq_local.contiguous().view(sub, chains, 2, D, D)
+    if two_level is None:
+        two_level = world * sub > 8 or mode != "gather"
+    if sub > 1 and not two_level:
+        if mode != "gather":
+            raise ValueError("the flat exchange of several segments per rank needs the all-gather")
         segs = world * sub
         allmq = buf("gathered", (segs, chains, 2, D, D))      # segment = rank * sub + sub-segment
-        dist.all_gather_into_tensor(allmq.view(segs * chains, 2, D, D), mq_local.contiguous(), group=group)
+        dist.all_gather_into_tensor(allmq.view(segs * chains, 2, D, D), mq5.view(sub * chains, 2, D, D), group=group)
         n_seg = segs if want_final else rank * sub + sub - 1
-        s_in = fold(allmq, h0c, out=buf("s_in", (n_seg + 1, chains, D, D)), n_seg=n_seg, **skw)
+        s_in = buf("s_in", (n_seg + 1, chains, D, D))
+        walk(allmq, h0c, n_seg, s_in=s_in, status=status)
         return s_in[rank * sub:rank * sub + sub], (s_in[segs] if want_final else None)
-    hp = chains // world
-    recv = buf("recv_mq", (world, hp, 2, D, D))            # [segment][my chains]
-    dist.all_to_all_single(recv, mq_local.contiguous().view(world, hp, 2, D, D), group=group)
-    s_in = fold(recv, None if h0c is None else h0c[rank * hp:(rank + 1) * hp], out=buf("s_in", (world + 1, hp, D, D)),
-                **skw)
-    entry = buf("entry", (world, hp, D, D))                # [owner of the chains][chains] = all chains in order
-    dist.all_to_all_single(entry, s_in[:world], group=group)
+    if sub > 1:   # this rank's whole segment as one transform
+        rank_mq = buf("rank_mq", (chains, 2, D, D))
+        walk(mq5[1:], mq5[0, :, 0], sub - 1, use_q=False, final_out=rank_mq[:, 0], status=status)
+        walk(mq5[1:], mq5[0, :, 1], sub - 1, use_q=True, final_out=rank_mq[:, 1], status=status)
+    else:
+        rank_mq = mq5[0]
+
     final = None
-    if want_final:
-        final = buf("final", (world, hp, D, D))
-        dist.all_gather_into_tensor(final.view(chains, D, D), s_in[world].contiguous(), group=group)
-        final = final.view(chains, D, D)
-    return entry.view(1, chains, D, D), final
+    if mode == "gather":
+        allmq = buf("gathered", (world, chains, 2, D, D))
+        dist.all_gather_into_tensor(allmq.view(world * chains, 2, D, D), rank_mq, group=group)
+        n_seg = world if want_final else rank
+        s_in = buf("s_in", (n_seg + 1, chains, D, D))
+        walk(allmq, h0c, n_seg, s_in=s_in, status=status)
+        entry = s_in[rank]
+        final = s_in[world] if want_final else None
+    else:
+        hp = chains // world
+        recv = buf("recv_mq", (world, hp, 2, D, D))            # [segment][my chains]
+        dist.all_to_all_single(recv, rank_mq.view(world, hp, 2, D, D), group=group)
+        s_in = buf("s_in", (world + 1, hp, D, D))
+        walk(recv, None if h0c is None else h0c[rank * hp:(rank + 1) * hp], world, s_in=s_in, status=status)
+        ent = buf("entry", (world, hp, D, D))                  # [owner of the chains][chains] = all chains in order
+        dist.all_to_all_single(ent, s_in[:world], group=group)
+        entry = ent.view(chains, D, D)
+        if want_final:
+            final = buf("final", (world, hp, D, D))
+            dist.all_gather_into_tensor(final.view(chains, D, D), s_in[world].contiguous(), group=group)
+            final = final.view(chains, D, D)
+    if sub == 1:
+        return entry.view(1, chains, D, D), final
+    sub_entry = buf("sub_entry", (sub, chains, D, D))          # entry states of this rank's sub-segments
+    walk(mq5, entry, sub - 1, s_in=sub_entry, status=status)
+    return sub_entry, final
 
 
 def _sub_segments(x: torch.Tensor, sub: int) -> torch.Tensor:
@@ -273,9 +327,11 @@ class SeqParallelPlan:
     ``segments_per_rank``: a K2 pass is one serial chain per (batch, head), so a rank with few heads
     leaves most of its GPU idle; cutting the rank's tokens into 2 or 4 consecutive sub-segments
     (handled as batch entries of the same launches, no copy) runs that many chains side by side
-    for the same total work.  ``"auto"`` takes the largest of 1, 2, 4 that still leaves every warp
-    of the 8-row K2 form an SM sub-partition of its own (batch 1 only; it implies the all-gather
-    exchange).
+    for the same total work.  ``"auto"`` takes the largest of 4, 2 that keeps the chains of a pass at
+    64 or fewer and the sub-segments at 2,048 tokens or more, else 1 (measured per rank on B200, 16
+    heads x 16,384 tokens: K1 + transform pass + K2 = 1,060 us with one, 766 us with two, 605 us with
+    four sub-segments).  The exchange stays that of one segment per rank: the rank composes its
+    sub-segments' transforms into one before the exchange and walks them again after it.  Batch 1 only.
     """
 
     def __init__(self, q, k, v, g, beta, *, scale=None, initial_state=None, lower_bound=-5.0, A_log=None,
@@ -287,10 +343,9 @@ class SeqParallelPlan:
         B, L, H = q.shape[0], q.shape[1], v.shape[2]
         sub = 1
         if segments_per_rank == "auto":
-            if B == 1 and self.world > 1 and q.is_cuda and exchange != "a2a":
-                sms = torch.cuda.get_device_properties(q.device).multi_processor_count
+            if B == 1 and self.world > 1 and q.is_cuda:
                 for cand in (4, 2):
-                    if cand * H * 4 <= sms and L % (cand * api.BT) == 0:
+                    if cand * H <= 64 and L % (cand * api.BT) == 0 and L // cand >= 2048:
                         sub = cand
                         break
         else:
@@ -299,13 +354,12 @@ class SeqParallelPlan:
                 raise ValueError("segments_per_rank needs batch 1 and a token count that splits into multiples of 16")
         self.sub = sub
         if sub > 1:
-            if exchange == "a2a":
-                raise ValueError("several segments per rank need the all-gather exchange")
             q, k, v, g, beta = (_sub_segments(x, sub) for x in (q, k, v, g, beta))
-            exchange = "gather"
         self.seg = _Segment(q, k, v, g, beta, D ** -0.5 if scale is None else scale, lower_bound, A_log, dt_bias)
         self.chains = B * H
         self.h0 = None if initial_state is None else initial_state.contiguous().float()
+        if exchange == "auto" and sub > 1 and self.world * sub <= 8:
+            exchange = "gather"   # few segments: one all-gather of every sub-segment's transform, one flat walk
         self.mode = exchange_mode(self.chains, self.world, exchange)
         self.want_final = bool(final_state_on_all_ranks)
         self.bufs: dict = {}

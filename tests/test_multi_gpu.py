@@ -29,7 +29,7 @@ def _rank_main(rank, world, port, ret):
         dev = torch.device("cuda", rank)
         T = 1024
         seq = {}
-        for regime, exchange, sub in (("carry", "a2a", 1), ("carry", "gather", 1), ("carry", "gather", 2),
+        for regime, exchange, sub in (("carry", "a2a", 1), ("carry", "gather", 1), ("carry", "gather", 2), ("carry", "a2a", 4),
                                       ("baseline", "a2a", 1), ("baseline", "auto", "auto")):
             inp = O.make_inputs(1, T, 4, seed0=21, regime=regime, h0_std=0.1 if regime == "carry" else 0.02)
             d = {k: (v.to(dev) if torch.is_tensor(v) else v) for k, v in inp.items()}

@@ -75,20 +75,25 @@ def _rank_main(rank, world, port, ret):
         T = 64
         inp = O.make_inputs(1, T, 2, seed0=9, regime="carry", h0_std=0.1)
         L = T // world
-        seg, M, Q = _segment_transforms(inp, rank * L, (rank + 1) * L)
         o_full, h_full = O.run_chunk_reference(inp)
-        mq = torch.stack([M[0], Q[0]], dim=1).contiguous()          # [chains = heads, 2, 128, 128]
         res = {}
-        for mode in ("a2a", "gather"):
-            entry, final = shard.exchange_and_fold(mq, inp["initial_state"], rank, world, mode=mode,
-                                                   fold=shard._torch_fold, want_final=True)
-            o_loc, _ = O.run_chunk_reference(dict(seg, initial_state=entry.view(1, 2, D, D)))
+        for mode, sub in (("a2a", 1), ("gather", 1), ("a2a", 2), ("gather", 2)):
+            Ls = L // sub
+            parts = [_segment_transforms(inp, rank * L + s * Ls, rank * L + (s + 1) * Ls) for s in range(sub)]
+            # [sub * chains, 2, 128, 128], sub-segment major
+            mq = torch.cat([torch.stack([M[0], Q[0]], dim=1) for _, M, Q in parts]).contiguous()
+            entry, final = shard.exchange_and_fold(mq, inp["initial_state"], rank, world, mode=mode, sub=sub,
+                                                   walk=shard._walk_torch, want_final=True)
+            assert tuple(entry.shape) == (sub, 2, D, D)
+            outs = [O.run_chunk_reference(dict(seg, initial_state=entry[s].reshape(1, 2, D, D)))[0]
+                    for s, (seg, _, _) in enumerate(parts)]
+            o_loc = torch.cat(outs, 1)
             eo = (o_loc.float() - o_full[:, rank * L:(rank + 1) * L].float()).abs().max().item()
             eh = (final.view(1, 2, D, D) - h_full).abs().max().item()
-            res[mode] = (eo, eh)
-        # without the final state only the entry state comes back
-        entry2, none = shard.exchange_and_fold(mq, inp["initial_state"], rank, world, mode="gather",
-                                               fold=shard._torch_fold)
+            res[(mode, sub)] = (eo, eh)
+        # without the final state only the entry states come back
+        entry2, none = shard.exchange_and_fold(mq, inp["initial_state"], rank, world, mode="gather", sub=2,
+                                               walk=shard._walk_torch)
         assert none is None and torch.equal(entry2, entry)
         ret[rank] = (res, o_full.float().abs().max().item(), h_full.abs().max().item())
     finally:
@@ -103,9 +108,9 @@ def test_sequence_split_over_two_gloo_ranks():
     assert sorted(ret.keys()) == [0, 1]
     for r in range(world):
         res, omax, hmax = ret[r]
-        for mode, (eo, eh) in res.items():
-            assert eo <= 2.0 ** -8 * omax, (r, mode, eo)
-            assert eh <= 2e-5 * max(1.0, hmax), (r, mode, eh)
+        for key, (eo, eh) in res.items():
+            assert eo <= 2.0 ** -8 * omax, (r, key, eo)
+            assert eh <= 2e-5 * max(1.0, hmax), (r, key, eh)
 
 
 def test_exchange_mode_choice():

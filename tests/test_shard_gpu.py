@@ -111,3 +111,28 @@ def test_transform_pair_pass_matches_the_two_single_passes(cuda_device):
     assert (mq[:, 0].view(B, H, 128, 128) - M).abs().max().item() <= 1e-5
     assert (mq[:, 1].view(B, H, 128, 128) - Q).abs().max().item() <= 1e-4 * max(1.0, Q.abs().max().item())
     assert lib.kda_fwd_k2_state(ctypes.byref(a), 3, st) == -1 and "zero_u" in _lib.last_error()
+
+
+def test_two_level_fold_equals_the_flat_walk(cuda_device):
+    """Composing the transforms of a rank's sub-segments first (transition matrices with use_q = 0,
+    offsets with use_q = 1, written straight into an (M, Q) buffer through final_out) and walking the
+    composed transforms gives the states of the flat walk over all sub-segments."""
+    g = torch.Generator(device=cuda_device).manual_seed(5)
+    ranks, sub, chains = 3, 4, 2
+    mq = torch.randn(ranks * sub, chains, 2, 128, 128, device=cuda_device, generator=g) * 0.09
+    h0 = torch.randn(chains, 128, 128, device=cuda_device, generator=g)
+    flat = shard.fold_states(mq, h0)                                  # [ranks * sub + 1, chains, 128, 128]
+    rank_mq = torch.full((ranks, chains, 2, 128, 128), float("nan"), device=cuda_device)
+    for r in range(ranks):
+        m5 = mq[r * sub:(r + 1) * sub]
+        shard._walk_cuda(m5[1:], m5[0, :, 0], sub - 1, use_q=False, final_out=rank_mq[r, :, 0])
+        shard._walk_cuda(m5[1:], m5[0, :, 1], sub - 1, use_q=True, final_out=rank_mq[r, :, 1])
+    top = shard.fold_states(rank_mq, h0)                              # entry state of every rank
+    for r in range(ranks + 1):
+        ref = flat[r * sub]
+        assert (top[r] - ref).abs().max().item() <= 5e-5 * max(1.0, ref.abs().max().item()), r
+    for r in range(ranks):                                            # the local walk from the rank's entry state
+        loc = torch.empty(sub, chains, 128, 128, device=cuda_device)
+        shard._walk_cuda(mq[r * sub:(r + 1) * sub], top[r], sub - 1, s_in=loc)
+        ref = flat[r * sub:(r + 1) * sub]
+        assert (loc - ref).abs().max().item() <= 5e-5 * max(1.0, ref.abs().max().item()), r
