@@ -53,9 +53,9 @@ extern "C" {
 #define KDA_FLAG_BETA_SIGMOID 4u      /* beta holds logits */
 #define KDA_FLAG_STATE_K_FIRST 8u     /* h0 / ht are [B, H, K, V] (the reference's state_v_first=False,
                                          src/kda_bt16/kernels.py:497-510, where it is a host-side transpose);
-                                         read and written in that layout by kda_fwd, kda_fwd_k2 and
-                                         kda_fwd_k2_state(zero_u 0 / 1); kda_recurrent_fwd and the transform
-                                         pair (zero_u = 2) keep [B, H, V, K] */
+                                         read and written in that layout by kda_fwd, kda_fwd_k2,
+                                         kda_fwd_k2_state(zero_u 0 / 1) and kda_recurrent_fwd; the transform
+                                         pair (zero_u = 2) keeps [B, H, V, K] */
 
 typedef struct KdaFwdArgs {
   /* inputs: [B, T, H, 128], innermost dimension contiguous; strides in ELEMENTS.
@@ -172,7 +172,8 @@ int kda_state_fold_ex(const KdaFoldArgs* args, void* stream);
 /* Token-by-token recurrence for decode steps and short sequences (T of one to a few dozen
  * tokens): reads the state from args->h0 (NULL = zeros), applies args->T tokens, writes the
  * outputs to args->o and the new state to args->ht (may be NULL; may be the same buffer as h0
- * for an in-place update).  Needs all three KDA_FLAG_* bits; args->workspace is not used.
+ * for an in-place update; [B, H, V, K], or [B, H, K, V] with KDA_FLAG_STATE_K_FIRST, moved in that
+ * layout).  Needs the gate, l2-norm and beta-sigmoid flag bits; args->workspace is not used.
  * The reference has no decode kernel (README.md:503-505 lists it as future work); the
  * arithmetic is the token recurrence its tests take as the gold (fused_recurrent_kda,
  * tests/test_kda_bt16.py:26-39) with the chunk path's rounding of the normalised q and k, so a

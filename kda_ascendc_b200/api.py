@@ -318,20 +318,21 @@ def _forward(q, k, v, g, beta, scale, initial_state, output_final_state, use_qk_
 
 
 def kda_recurrent_fwd(q, k, v, g, beta, scale=None, initial_state=None, output_final_state=True,
-                      lower_bound=-5.0, A_log=None, dt_bias=None, inplace_state=False):
+                      lower_bound=-5.0, A_log=None, dt_bias=None, inplace_state=False, state_v_first=True):
     """Token-by-token KDA recurrence for decode steps and short sequences.
 
     Same tensors as :func:`kda_bt16_fwd` with the in-kernel gate, l2-norm and beta sigmoid
     (``g`` raw, ``beta`` logits, ``A_log`` required), any ``T >= 1`` (calls of more than
-    ``RECURRENT_MAX_TOKENS`` tokens run on the chunk kernels, which are faster from there on), V-first fp32
-    state ``[B, H, 128, 128]``.  Returns ``(o, state)``; with
+    ``RECURRENT_MAX_TOKENS`` tokens run on the chunk kernels, which are faster from there on), fp32
+    state ``[B, H, V, K]`` or, with ``state_v_first=False``, ``[B, H, K, V]`` (read and written in
+    that layout by the kernels, no transpose).  Returns ``(o, state)``; with
     ``inplace_state=True`` the new state overwrites ``initial_state`` (which is returned).
     The reference has no decode function; the arithmetic is the token recurrence its tests use
     as the gold (``fused_recurrent_kda``, ``tests/test_kda_bt16.py:26-39`` of the reference) with
     the chunk path's bf16 rounding of the normalised q and k, so that a prefill by
     :func:`kda_bt16_fwd` followed by steps of this function continues the same sequence.
     """
-    _validate_kda_inputs(q, k, v, g, beta, initial_state, True, True, lower_bound, A_log, dt_bias, True,
+    _validate_kda_inputs(q, k, v, g, beta, initial_state, True, True, lower_bound, A_log, dt_bias, state_v_first,
                          require_contiguous=False)
     _require_cuda(q)
     if inplace_state and initial_state is None:
@@ -355,7 +356,8 @@ def kda_recurrent_fwd(q, k, v, g, beta, scale=None, initial_state=None, output_f
     chunked = T > RECURRENT_MAX_TOKENS
     ws = _get_workspace(dev, B, T, H, True) if chunked else None
     args = make_args(q, k, v, g, beta, scale=scale, lower_bound=lower_bound, A_log=A_log, dt_bias=dt_bias,
-                     h0=initial_state, o=o, ht=ht, workspace=ws, flags=_flags(True, True, True))
+                     h0=initial_state, o=o, ht=ht, workspace=ws,
+                     flags=_flags(True, True, True) | (0 if state_v_first else _lib.FLAG_STATE_K_FIRST))
     lib = _lib.load()
     with torch.cuda.device(dev):
         _check((lib.kda_fwd if chunked else lib.kda_recurrent_fwd)(ctypes.byref(args), _stream_handle()))
@@ -428,11 +430,13 @@ class RecurrentPlan:
     A serving loop writes each new token's ``q, k, v, g, beta`` into the SAME tensors and calls
     :meth:`step`; validation, output allocation and the argument block are done once here.  ``o``
     is reused by every step (copy it if it must outlive the next one); ``state`` is updated in
-    place.  Same arithmetic and checks as :func:`kda_recurrent_fwd`.
+    place (``[B, H, V, K]``, or ``[B, H, K, V]`` with ``state_v_first=False``).  Same arithmetic and
+    checks as :func:`kda_recurrent_fwd`.
     """
 
-    def __init__(self, q, k, v, g, beta, state, *, scale=None, lower_bound=-5.0, A_log=None, dt_bias=None):
-        _validate_kda_inputs(q, k, v, g, beta, state, True, True, lower_bound, A_log, dt_bias, True,
+    def __init__(self, q, k, v, g, beta, state, *, scale=None, lower_bound=-5.0, A_log=None, dt_bias=None,
+                 state_v_first=True):
+        _validate_kda_inputs(q, k, v, g, beta, state, True, True, lower_bound, A_log, dt_bias, state_v_first,
                              require_contiguous=False)
         _require_cuda(q)
         if state is None:
@@ -444,7 +448,7 @@ class RecurrentPlan:
         self._keep = (q, k, v, g, beta, A_log, dt_bias)   # the argument block holds raw pointers
         self._args = make_args(q, k, v, g, beta, scale=K ** -0.5 if scale is None else scale, lower_bound=lower_bound,
                                A_log=A_log, dt_bias=dt_bias, h0=state, o=self.o, ht=state, workspace=None,
-                               flags=_flags(True, True, True))
+                               flags=_flags(True, True, True) | (0 if state_v_first else _lib.FLAG_STATE_K_FIRST))
         self._ref = ctypes.byref(self._args)
         self._fn = _lib.load().kda_recurrent_fwd
 

@@ -356,8 +356,6 @@ int kda_recurrent_fwd(const KdaFwdArgs* a, void* stream) {
   const uint32_t all = KDA_FLAG_GATE_IN_KERNEL | KDA_FLAG_QK_L2NORM | KDA_FLAG_BETA_SIGMOID;
   if ((a->flags & all) != all)
     return fail(KDA_ERR_INVALID_ARG, "kda: the recurrent step computes gate, l2-norm and beta sigmoid in the kernel%s; set all three flags", "");
-  if (a->flags & KDA_FLAG_STATE_K_FIRST)
-    return fail(KDA_ERR_INVALID_ARG, "kda: the recurrent step keeps its state [B, H, V, K]%s (KDA_FLAG_STATE_K_FIRST is for the chunk kernels)", "");
   if (a->g_dtype != KDA_G_FP32 && a->g_dtype != KDA_G_BF16)
     return fail(KDA_ERR_INVALID_ARG, "kda: g_dtype must be KDA_G_FP32 or KDA_G_BF16%s (got %lld)", "", a->g_dtype);
   if (!(a->lower_bound > -11.0f && a->lower_bound < 0.0f))
@@ -377,6 +375,7 @@ int kda_recurrent_fwd(const KdaFwdArgs* a, void* stream) {
   p.h0 = a->h0; p.ht = a->ht; p.o = static_cast<__nv_bfloat16*>(a->o);
   p.B = a->B; p.T = a->T; p.H = a->H;
   p.group = a->Hq > 0 ? a->H / a->Hq : 1;
+  p.k_first = (a->flags & KDA_FLAG_STATE_K_FIRST) ? 1 : 0;
   for (int i = 0; i < 3; ++i) {
     p.q_s[i] = a->q_stride[i]; p.k_s[i] = a->k_stride[i]; p.v_s[i] = a->v_stride[i];
     p.g_s[i] = a->g_stride[i]; p.beta_s[i] = a->beta_stride[i]; p.o_s[i] = a->o_stride[i];

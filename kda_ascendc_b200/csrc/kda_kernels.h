@@ -123,6 +123,7 @@ struct RecurrentParams {
   __nv_bfloat16* o;
   int B, T, H;
   int group;                // value heads per q/k head (1 = plain multi-head)
+  int k_first;              // h0 / ht are [B,H,K,V] instead of [B,H,V,K]
   int64_t q_s[3], k_s[3], v_s[3], g_s[3], beta_s[3], o_s[3];
   float scale, lower_bound;
 };

@@ -12,7 +12,10 @@
 // them in registers over all T tokens: lane l holds columns 4l..4l+3 of each row (one 16-byte
 // load per row), the two dot products per row and token are warp reductions.  The kernel moves
 // 64 KiB of state in and out per (batch, head) and a few hundred bytes per token: HBM bound; the
-// grid is (batch x head) x (128 / rows per CTA) CTAs.
+// grid is (batch x head) x (128 / rows per CTA) CTAs.  A K-first state h[K][V] (the layout
+// flash-linear-attention keeps) is read and written in place: for one column k the warp's ROWS
+// rows are ROWS consecutive floats, so the lane moves them as 16- or 8-byte pieces (full 32-byte
+// sectors at 8 rows per warp) into the same registers.
 #include "kda_common.cuh"
 #include "kda_kernels.h"
 
@@ -64,7 +67,25 @@ __global__ void __launch_bounds__(REC_WARPS * 32) kda_recurrent_kernel(const Rec
   const int k0 = lane * 4;                             // first state column of this lane
 
   float4 s[ROWS];
-  if (p.h0 != nullptr) {
+  constexpr int PIECE = (ROWS % 4 == 0) ? 4 : 2;   // floats per access along v in the K-first layout
+  if (p.h0 != nullptr && p.k_first) {
+    const float* h0 = p.h0 + (static_cast<size_t>(bh) * D + k0) * D + v0;   // element (k0 + c, v0 + r) at c * D + r
+    float t[4][ROWS];
+#pragma unroll
+    for (int c = 0; c < 4; ++c)
+#pragma unroll
+      for (int r = 0; r < ROWS; r += PIECE) {
+        if (PIECE == 4) {
+          const float4 x = *reinterpret_cast<const float4*>(h0 + c * D + r);
+          t[c][r] = x.x; t[c][r + 1] = x.y; t[c][r + 2] = x.z; t[c][r + 3] = x.w;
+        } else {
+          const float2 x = *reinterpret_cast<const float2*>(h0 + c * D + r);
+          t[c][r] = x.x; t[c][r + 1] = x.y;
+        }
+      }
+#pragma unroll
+    for (int r = 0; r < ROWS; ++r) s[r] = make_float4(t[0][r], t[1][r], t[2][r], t[3][r]);
+  } else if (p.h0 != nullptr) {
     const float* h0 = p.h0 + (static_cast<size_t>(bh) * D + v0) * D + k0;
 #pragma unroll
     for (int r = 0; r < ROWS; ++r) s[r] = *reinterpret_cast<const float4*>(h0 + r * D);
@@ -136,7 +157,17 @@ __global__ void __launch_bounds__(REC_WARPS * 32) kda_recurrent_kernel(const Rec
     if ((lane & ((1 << SH) - 1)) == 0) op[t * p.o_s[1] + (lane >> SH)] = __float2bfloat16(p.scale * od);
   }
 
-  if (p.ht != nullptr) {
+  if (p.ht != nullptr && p.k_first) {
+    float* ht = p.ht + (static_cast<size_t>(bh) * D + k0) * D + v0;
+#pragma unroll
+    for (int c = 0; c < 4; ++c)
+#pragma unroll
+      for (int r = 0; r < ROWS; r += PIECE) {
+        auto comp = [&](int rr) { return c == 0 ? s[rr].x : (c == 1 ? s[rr].y : (c == 2 ? s[rr].z : s[rr].w)); };
+        if (PIECE == 4) *reinterpret_cast<float4*>(ht + c * D + r) = make_float4(comp(r), comp(r + 1), comp(r + 2), comp(r + 3));
+        else *reinterpret_cast<float2*>(ht + c * D + r) = make_float2(comp(r), comp(r + 1));
+      }
+  } else if (p.ht != nullptr) {
     float* ht = p.ht + (static_cast<size_t>(bh) * D + v0) * D + k0;
 #pragma unroll
     for (int r = 0; r < ROWS; ++r) *reinterpret_cast<float4*>(ht + r * D) = s[r];

@@ -15,9 +15,8 @@ Two layers:
   its own kernels for the rest.  Off unless called; ``FLA_KDA_B200=0`` disables it afterwards.
 
 FLA keeps the state K-first (``[N, H, K, V]``) unless ``transpose_state_layout`` (older releases:
-``state_v_first``) is set.  The chunk kernels read and write either layout in place (the
-reference transposes on the host, src/kda_bt16/kernels.py:497-510); the token recurrence keeps its
-state V-first, so ``fused_recurrent_kda`` pays one transpose each way for K-first states.
+``state_v_first``) is set.  The chunk kernels and the token recurrence read and write either layout
+in place (the reference transposes on the host, src/kda_bt16/kernels.py:497-510).
 """
 from __future__ import annotations
 
@@ -97,16 +96,10 @@ def fused_recurrent_kda(q, k, v, g, beta, A_log=None, dt_bias=None, scale=None, 
         ok, why = False, "the recurrent step takes a fixed-length batch"
     if not ok:
         raise NotImplementedError(f"{BACKEND_NAME}: {why}")
-    v_first = _v_first(kwargs, transpose_state_layout)
-    h0 = initial_state
-    if h0 is not None and not v_first:
-        h0 = h0.transpose(-1, -2).contiguous()
-    o, ht = api.kda_recurrent_fwd(q, k, v, g, beta.float(), scale=scale, initial_state=h0,
-                                  output_final_state=output_final_state, lower_bound=lower_bound, A_log=A_log,
-                                  dt_bias=None if dt_bias is None else dt_bias.reshape(-1))
-    if ht is not None and not v_first:
-        ht = ht.transpose(-1, -2).contiguous()
-    return o, ht
+    return api.kda_recurrent_fwd(q, k, v, g, beta.float(), scale=scale, initial_state=initial_state,
+                                 output_final_state=output_final_state, lower_bound=lower_bound, A_log=A_log,
+                                 dt_bias=None if dt_bias is None else dt_bias.reshape(-1),
+                                 state_v_first=_v_first(kwargs, transpose_state_layout))
 
 
 def register() -> bool:

@@ -73,6 +73,10 @@ def test_adapter_matches_native_calls_and_state_layouts():
                                          scale=d["scale"], initial_state=d["initial_state"], lower_bound=d["lower_bound"],
                                          A_log=d["A_log"], dt_bias=d["dt_bias"])
         assert torch.equal(o_r, o_r2) and torch.equal(h_r, h_r2)
+        # FLA's default (K-first) layout on the recurrent adapter: moved by the kernel, no transpose
+        o_rk, h_rk = FB.fused_recurrent_kda(d["q"][:, :5], d["k"][:, :5], d["v"][:, :5], d["g"][:, :5], d["beta"][:, :5],
+                                            initial_state=d["initial_state"].transpose(-1, -2).contiguous(), **kw_r)
+        assert torch.equal(o_rk, o_r2) and torch.equal(h_rk, h_r2.transpose(-1, -2))
 
 
 @pytest.mark.gpu

@@ -105,6 +105,32 @@ def test_recurrent_argument_errors():
         K.kda_recurrent_fwd(d["q"], d["k"], d["v"], d["g"], d["beta"], scale=d["scale"], A_log=None, dt_bias=d["dt_bias"])
 
 
+@pytest.mark.parametrize("B,T,H", [(1, 3, 2), (5, 2, 8), (40, 1, 32), (2, 40, 3)])
+def test_recurrent_k_first_state_is_read_and_written_natively(B, T, H):
+    """state_v_first=False: the kernel moves the [B,H,K,V] state itself.  Bit-equal to the V-first run on
+    the transposed state, for every rows-per-warp choice (2 / 4 / 8, picked from B*H), for the in-place
+    update, for the plan, and for calls long enough to run on the chunk kernels (T = 40)."""
+    import kda_ascendc_b200 as K
+    inp = O.make_inputs(B, T, H, seed0=13, h0_std=0.3)
+    d = _dev(inp)
+    args = [d[n] for n in ("q", "k", "v", "g", "beta")]
+    o_v, h_v = K.kda_recurrent_fwd(*args, initial_state=d["initial_state"], **_kw(d))
+    h0_k = d["initial_state"].transpose(-1, -2).contiguous()
+    o_k, h_k = K.kda_recurrent_fwd(*args, initial_state=h0_k, state_v_first=False, **_kw(d))
+    assert torch.equal(o_k, o_v) and torch.equal(h_k, h_v.transpose(-1, -2))
+    # no initial state, and the in-place update
+    o_v0, h_v0 = K.kda_recurrent_fwd(*args, initial_state=None, **_kw(d))
+    o_k0, h_k0 = K.kda_recurrent_fwd(*args, initial_state=None, state_v_first=False, **_kw(d))
+    assert torch.equal(o_k0, o_v0) and torch.equal(h_k0, h_v0.transpose(-1, -2))
+    st = h0_k.clone()
+    o_i, h_i = K.kda_recurrent_fwd(*args, initial_state=st, inplace_state=True, state_v_first=False, **_kw(d))
+    assert h_i is st and torch.equal(o_i, o_v) and torch.equal(st, h_k)
+    if T <= K.api.RECURRENT_MAX_TOKENS:
+        st2 = h0_k.clone()
+        plan = K.RecurrentPlan(*args, st2, state_v_first=False, **_kw(d))
+        assert torch.equal(plan.step(), o_v) and torch.equal(st2, h_k)
+
+
 def test_recurrent_plan_matches_stepwise_calls():
     import kda_ascendc_b200 as K
     B, H, n_tok = 3, 4, 6
