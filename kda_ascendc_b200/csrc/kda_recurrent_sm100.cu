@@ -174,6 +174,128 @@ __global__ void __launch_bounds__(REC_WARPS * 32) kda_recurrent_kernel(const Rec
   }
 }
 
+// K-first state h[K][V] with enough heads to fill the GPU: lanes along v.
+// A CTA owns all 128 k of a 32-wide slice of v (one full 128-byte line per k); thread (vq = tid % 8,
+// kg = tid / 8) keeps rows k = 8 kg .. 8 kg + 7 of columns v = 4 vq .. 4 vq + 3 of that slice in
+// registers (eight 16-byte accesses, four whole lines per warp instruction -- the access pattern of
+// the V-first kernel above on the transposed state).  The two dot products per token run over k:
+// serial over the thread's eight rows, two shuffles over the four k-groups of a warp, and a
+// 512-byte exchange through shared memory over the four warps (two CTA barriers per token).
+// Same arithmetic and rounding points as the kernel above; the fp32 sums run in another order.
+template <bool G_BF16>
+__global__ void __launch_bounds__(128) kda_recurrent_kfirst_kernel(const RecurrentParams p) {
+  __shared__ float4 red[2][4][8];   // [prediction | output][warp][v quad]
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int vq = tid & 7, kg = tid >> 3;
+  const int bh = blockIdx.x >> 2, slice = blockIdx.x & 3;
+  const int b = bh / p.H, h = bh % p.H;
+  const int v0 = slice * 32 + vq * 4;   // first state column of this thread
+  const int k0 = kg * 8;                // first state row of this thread
+
+  float4 s[8];
+  if (p.h0 != nullptr) {
+    const float* h0 = p.h0 + (static_cast<size_t>(bh) * D + k0) * D + v0;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) s[i] = *reinterpret_cast<const float4*>(h0 + i * D);
+  } else {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) s[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+
+  const float expA = expf(p.A_log[h]);
+  float bias[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) bias[i] = (p.dt_bias != nullptr) ? p.dt_bias[h * D + k0 + i] : 0.f;
+  const float lbr = p.lower_bound * RCP_LN2;
+
+  const int hq = h / p.group;   // grouped value heads share a q/k head
+  const __nv_bfloat16* qp = p.q + b * p.q_s[0] + hq * p.q_s[2];
+  const __nv_bfloat16* kp = p.k + b * p.k_s[0] + hq * p.k_s[2];
+  const __nv_bfloat16* vp = p.v + b * p.v_s[0] + h * p.v_s[2] + v0;
+  const uint8_t* gp = static_cast<const uint8_t*>(p.g) + (b * p.g_s[0] + h * p.g_s[2] + k0) * (G_BF16 ? 2 : 4);
+  const float* bp = p.beta + b * p.beta_s[0] + h * p.beta_s[2];
+  __nv_bfloat16* op = p.o + b * p.o_s[0] + h * p.o_s[2] + v0;
+
+  auto load4 = [](const __nv_bfloat16* src) {
+    const uint2 raw = *reinterpret_cast<const uint2*>(src);
+    return make_float4(bf16_lo_to_f32(raw.x), bf16_hi_to_f32(raw.x), bf16_lo_to_f32(raw.y), bf16_hi_to_f32(raw.y));
+  };
+  auto load8 = [](const __nv_bfloat16* src, float (&x)[8]) {
+    const uint4 raw = *reinterpret_cast<const uint4*>(src);
+    const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) { x[2 * i] = bf16_lo_to_f32(w[i]); x[2 * i + 1] = bf16_hi_to_f32(w[i]); }
+  };
+  // sum over the k-groups of this warp (lanes with the same vq), then over the warps
+  auto reduce_k = [&](float4 x, int which) {
+#pragma unroll
+    for (int m = 8; m <= 16; m <<= 1) {
+      x.x += __shfl_xor_sync(0xffffffffu, x.x, m); x.y += __shfl_xor_sync(0xffffffffu, x.y, m);
+      x.z += __shfl_xor_sync(0xffffffffu, x.z, m); x.w += __shfl_xor_sync(0xffffffffu, x.w, m);
+    }
+    if (lane < 8) red[which][warp][vq] = x;
+    __syncthreads();
+    const float4 a = red[which][0][vq], c = red[which][1][vq], d = red[which][2][vq], e = red[which][3][vq];
+    return make_float4((a.x + c.x) + (d.x + e.x), (a.y + c.y) + (d.y + e.y), (a.z + c.z) + (d.z + e.z), (a.w + c.w) + (d.w + e.w));
+  };
+
+  for (int t = 0; t < p.T; ++t) {
+    // l2 norms over all 128 k: every warp computes them (lane l: k = 4 l .. 4 l + 3), rounded to bf16 like the chunk path
+    const float4 qa = load4(qp + t * p.q_s[1] + lane * 4);
+    const float4 ka = load4(kp + t * p.k_s[1] + lane * 4);
+    const float rq = rsqrtf(warp_sum(qa.x * qa.x + qa.y * qa.y + qa.z * qa.z + qa.w * qa.w) + L2NORM_EPS);
+    const float rk = rsqrtf(warp_sum(ka.x * ka.x + ka.y * ka.y + ka.z * ka.z + ka.w * ka.w) + L2NORM_EPS);
+    float qn[8], kn[8], gr[8];
+    load8(qp + t * p.q_s[1] + k0, qn);
+    load8(kp + t * p.k_s[1] + k0, kn);
+    if (G_BF16) load8(reinterpret_cast<const __nv_bfloat16*>(gp + t * p.g_s[1] * 2), gr);
+    else {
+      const float4 g0 = *reinterpret_cast<const float4*>(gp + t * p.g_s[1] * 4);
+      const float4 g1 = *reinterpret_cast<const float4*>(gp + t * p.g_s[1] * 4 + 16);
+      gr[0] = g0.x; gr[1] = g0.y; gr[2] = g0.z; gr[3] = g0.w; gr[4] = g1.x; gr[5] = g1.y; gr[6] = g1.z; gr[7] = g1.w;
+    }
+    const float4 v4 = load4(vp + t * p.v_s[1]);
+    float beta = bp[t * p.beta_s[1]];
+    beta = 1.0f / (1.0f + __expf(-beta));
+
+    float4 part = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      qn[i] = bf16_round(qn[i] * rq);
+      kn[i] = bf16_round(kn[i] * rk);
+      // decay 2^(lb * sigmoid(e^A (g + bias)) / ln 2) of row k0 + i
+      const float z = expA * (gr[i] + bias[i]);
+      const float dc = ex2f(lbr / (1.0f + __expf(-z)));
+      s[i].x *= dc; s[i].y *= dc; s[i].z *= dc; s[i].w *= dc;
+      part.x = fmaf(s[i].x, kn[i], part.x); part.y = fmaf(s[i].y, kn[i], part.y);
+      part.z = fmaf(s[i].z, kn[i], part.z); part.w = fmaf(s[i].w, kn[i], part.w);
+    }
+    const float4 pred = reduce_k(part, 0);
+    const float4 vn = make_float4(beta * (v4.x - pred.x), beta * (v4.y - pred.y), beta * (v4.z - pred.z), beta * (v4.w - pred.w));
+    part = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      s[i].x = fmaf(vn.x, kn[i], s[i].x); s[i].y = fmaf(vn.y, kn[i], s[i].y);
+      s[i].z = fmaf(vn.z, kn[i], s[i].z); s[i].w = fmaf(vn.w, kn[i], s[i].w);
+      part.x = fmaf(s[i].x, qn[i], part.x); part.y = fmaf(s[i].y, qn[i], part.y);
+      part.z = fmaf(s[i].z, qn[i], part.z); part.w = fmaf(s[i].w, qn[i], part.w);
+    }
+    const float4 od = reduce_k(part, 1);
+    if (tid < 8) {
+      uint2 out;
+      out.x = pack_bf16(p.scale * od.x, p.scale * od.y);
+      out.y = pack_bf16(p.scale * od.z, p.scale * od.w);
+      *reinterpret_cast<uint2*>(op + t * p.o_s[1]) = out;
+    }
+  }
+
+  if (p.ht != nullptr) {
+    float* ht = p.ht + (static_cast<size_t>(bh) * D + k0) * D + v0;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) *reinterpret_cast<float4*>(ht + i * D) = s[i];
+  }
+}
+
 template <int ROWS>
 cudaError_t launch_rows(const RecurrentParams& p, bool g_bf16, cudaStream_t stream) {
   const int grid = p.B * p.H * (D / (ROWS * REC_WARPS));
@@ -187,6 +309,14 @@ cudaError_t launch_rows(const RecurrentParams& p, bool g_bf16, cudaStream_t stre
 // (sixteen CTAs per head) so that a handful of heads still spreads over many SMs
 cudaError_t launch_recurrent(const RecurrentParams& p, bool g_bf16, int sms, cudaStream_t stream) {
   const long long bh = static_cast<long long>(p.B) * p.H;
+  if (p.k_first && bh * 4 >= 2LL * sms) {
+    // four CTAs per head with the lanes along v; with fewer heads the calls are latency-bound and the
+    // row-per-warp kernel's strided state accesses cost nothing measurable
+    const int grid = static_cast<int>(bh) * 4;
+    if (g_bf16) kda_recurrent_kfirst_kernel<true><<<grid, 128, 0, stream>>>(p);
+    else kda_recurrent_kfirst_kernel<false><<<grid, 128, 0, stream>>>(p);
+    return cudaGetLastError();
+  }
   if (bh * 4 >= 2LL * sms) return launch_rows<8>(p, g_bf16, stream);
   if (bh * 8 >= 2LL * sms) return launch_rows<4>(p, g_bf16, stream);
   return launch_rows<2>(p, g_bf16, stream);
