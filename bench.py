@@ -353,17 +353,22 @@ def run_gpu_arm(steps, warmup, n_gpus, kernels_only=False):
     launches = steps * lib.kda_last_launch_count()
 
     # ---- per-kernel durations of the whole-sequence forward (events on the launching stream) ----
+    # The pairs are queued back to back and read after one synchronise: with the stream never empty the
+    # interval between two events is the kernel's device time, not the host's launch path (tensor-map
+    # encoding and the launch itself, about 6 us, would otherwise sit inside K1's interval).
     k1_ms, k2_ms = [], []
-    ev = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
-    for _ in range(steps):
-        ev[0].record()
+    ev = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(steps)]
+    assert lib.kda_fwd(ctypes.byref(args), stream) == 0, _lib.last_error()   # keeps the GPU busy while the first pair is queued
+    for e in ev:
+        e[0].record()
         assert lib.kda_fwd_k1(ctypes.byref(args), stream) == 0, _lib.last_error()
-        ev[1].record()
+        e[1].record()
         assert lib.kda_fwd_k2(ctypes.byref(args), stream) == 0, _lib.last_error()
-        ev[2].record()
-        torch.cuda.synchronize()
-        k1_ms.append(ev[0].elapsed_time(ev[1]))
-        k2_ms.append(ev[1].elapsed_time(ev[2]))
+        e[2].record()
+    torch.cuda.synchronize()
+    for e in ev:
+        k1_ms.append(e[0].elapsed_time(e[1]))
+        k2_ms.append(e[1].elapsed_time(e[2]))
     status = api.check_device_status(ws)
     assert status == 0, "device status %d" % status
     finite = bool(torch.isfinite(o.float()).all()) and bool(torch.isfinite(ht).all())
