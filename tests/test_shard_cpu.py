@@ -67,33 +67,34 @@ def _free_port():
         return s.getsockname()[1]
 
 
-def _rank_main(rank, world, port, ret):
+def _rank_main(rank, world, port, ret, T=64, H=2, cases=(("a2a", 1, None), ("gather", 1, None), ("a2a", 2, None),
+                                                         ("gather", 2, None))):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
     dist.init_process_group("gloo", rank=rank, world_size=world)
     try:
         torch.set_num_threads(1)
-        T = 64
-        inp = O.make_inputs(1, T, 2, seed0=9, regime="carry", h0_std=0.1)
+        inp = O.make_inputs(1, T, H, seed0=9, regime="carry", h0_std=0.1)
         L = T // world
         o_full, h_full = O.run_chunk_reference(inp)
         res = {}
-        for mode, sub in (("a2a", 1), ("gather", 1), ("a2a", 2), ("gather", 2)):
+        for mode, sub, two_level in cases:
             Ls = L // sub
             parts = [_segment_transforms(inp, rank * L + s * Ls, rank * L + (s + 1) * Ls) for s in range(sub)]
             # [sub * chains, 2, 128, 128], sub-segment major
             mq = torch.cat([torch.stack([M[0], Q[0]], dim=1) for _, M, Q in parts]).contiguous()
             entry, final = shard.exchange_and_fold(mq, inp["initial_state"], rank, world, mode=mode, sub=sub,
-                                                   walk=shard._walk_torch, want_final=True)
-            assert tuple(entry.shape) == (sub, 2, D, D)
-            outs = [O.run_chunk_reference(dict(seg, initial_state=entry[s].reshape(1, 2, D, D)))[0]
+                                                   two_level=two_level, walk=shard._walk_torch, want_final=True)
+            assert tuple(entry.shape) == (sub, H, D, D)
+            outs = [O.run_chunk_reference(dict(seg, initial_state=entry[s].reshape(1, H, D, D)))[0]
                     for s, (seg, _, _) in enumerate(parts)]
             o_loc = torch.cat(outs, 1)
             eo = (o_loc.float() - o_full[:, rank * L:(rank + 1) * L].float()).abs().max().item()
-            eh = (final.view(1, 2, D, D) - h_full).abs().max().item()
-            res[(mode, sub)] = (eo, eh)
-        # without the final state only the entry states come back
-        entry2, none = shard.exchange_and_fold(mq, inp["initial_state"], rank, world, mode="gather", sub=2,
-                                               walk=shard._walk_torch)
+            eh = (final.view(1, H, D, D) - h_full).abs().max().item()
+            res[(mode, sub, two_level)] = (eo, eh)
+        # without the final state only the entry states come back (same exchange, same walk: same bits)
+        mode, sub, two_level = cases[-1]
+        entry2, none = shard.exchange_and_fold(mq, inp["initial_state"], rank, world, mode=mode, sub=sub,
+                                               two_level=two_level, walk=shard._walk_torch)
         assert none is None and torch.equal(entry2, entry)
         ret[rank] = (res, o_full.float().abs().max().item(), h_full.abs().max().item())
     finally:
@@ -108,6 +109,23 @@ def test_sequence_split_over_two_gloo_ranks():
     assert sorted(ret.keys()) == [0, 1]
     for r in range(world):
         res, omax, hmax = ret[r]
+        for key, (eo, eh) in res.items():
+            assert eo <= 2.0 ** -8 * omax, (r, key, eo)
+            assert eh <= 2e-5 * max(1.0, hmax), (r, key, eh)
+
+
+def test_sequence_split_over_four_gloo_ranks_two_levels():
+    """Four ranks, four chains: the all-to-all with one chain per rank, and with two sub-segments per
+    rank the flat all-gather (eight segments), the two-level all-gather and the two-level all-to-all."""
+    world = 4
+    mgr = mp.Manager()
+    ret = mgr.dict()
+    cases = (("a2a", 1, None), ("gather", 2, None), ("gather", 2, True), ("a2a", 2, None))
+    mp.spawn(_rank_main, args=(world, _free_port(), ret, 128, 4, cases), nprocs=world, join=True)
+    assert sorted(ret.keys()) == list(range(world))
+    for r in range(world):
+        res, omax, hmax = ret[r]
+        assert len(res) == len(cases)
         for key, (eo, eh) in res.items():
             assert eo <= 2.0 ** -8 * omax, (r, key, eo)
             assert eh <= 2e-5 * max(1.0, hmax), (r, key, eh)
