@@ -402,15 +402,18 @@ def run_gpu_arm(steps, warmup, n_gpus, kernels_only=False):
         ms_heads = timed(fwd_heads, steps)
         launches_heads = steps * lib.kda_last_launch_count()
         hk1, hk2 = [], []
-        for _ in range(min(steps, 10)):
-            ev[0].record()
+        evh = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(min(steps, 10))]
+        fwd_heads()                       # keeps the GPU busy while the first pair is queued (as above)
+        for e in evh:
+            e[0].record()
             assert lib.kda_fwd_k1(ctypes.byref(args_h), stream) == 0, _lib.last_error()
-            ev[1].record()
+            e[1].record()
             assert lib.kda_fwd_k2(ctypes.byref(args_h), stream) == 0, _lib.last_error()
-            ev[2].record()
-            torch.cuda.synchronize()
-            hk1.append(ev[0].elapsed_time(ev[1]))
-            hk2.append(ev[1].elapsed_time(ev[2]))
+            e[2].record()
+        torch.cuda.synchronize()
+        for e in evh:
+            hk1.append(e[0].elapsed_time(e[1]))
+            hk2.append(e[1].elapsed_time(e[2]))
 
         L = T // world
         tsl = slice(rank * L, (rank + 1) * L)
@@ -442,7 +445,7 @@ def run_gpu_arm(steps, warmup, n_gpus, kernels_only=False):
                             heads_per_gpu=hl, k1_us=hk1m * 1e3, k2_us=hk2m * 1e3, collectives=0,
                             max_abs_vs_one_gpu=dict(o=e_h_o, ht=e_h_s)),
             seq_split=dict(ms_per_step=ms_seq / steps, tokens_per_s=B * T * steps / (ms_seq * 1e-3),
-                           tokens_per_gpu=L, exchange=plan.mode,
+                           tokens_per_gpu=L, exchange=plan.mode, exchange_transport=plan.exchange_kind,
                            timeline_us={n: v * 1e3 for n, v in zip(ph_names, ph_max)},
                            sub_segments_per_rank=plan.sub,
                            collectives="2 all-to-all (NCCL) per forward" if plan.mode == "a2a" else "1 all-gather (NCCL) per forward",
@@ -451,6 +454,7 @@ def run_gpu_arm(steps, warmup, n_gpus, kernels_only=False):
                     "fewer tokens per GPU shorten every kernel but add the transform pass and the exchange")
         ms_strong = min(ms_heads, ms_seq)
         launches_strong = launches_heads if best == "head_shard" else steps * 4
+        plan.close()
         del plan
 
     # ---- long-context sequence split (B=1 T=131072 H=16) over the ranks ----
@@ -481,9 +485,10 @@ def run_gpu_arm(steps, warmup, n_gpus, kernels_only=False):
         res = max_over_ranks([ms_sp, t_one, e_o, e_h] + [v for _, v in ph])
         seq_parallel = dict(workload="KDA fwd B=1 T=%d H=%d, %d contiguous segments of %d tokens" % (SP_T, SP_H, world, Ll),
                             ms=res[0], tokens_per_s=SP_T / (res[0] * 1e-3), one_gpu_ms=res[1],
-                            speedup_over_one_gpu=res[1] / res[0], exchange=plan.mode, sub_segments_per_rank=plan.sub,
+                            speedup_over_one_gpu=res[1] / res[0], exchange=plan.mode, exchange_transport=plan.exchange_kind, sub_segments_per_rank=plan.sub,
                             timeline_us={n: v * 1e3 for (n, _), v in zip(ph, res[4:])},
                             max_abs_vs_one_gpu=dict(o=res[2], ht=res[3]), o_bound=O_TOL, ht_bound=HT_TOL)
+        plan.close()
         del plan, dl, o1, h1, o2, h2
         torch.cuda.empty_cache()
 

@@ -169,6 +169,66 @@ typedef struct KdaFoldArgs {
 } KdaFoldArgs;
 int kda_state_fold_ex(const KdaFoldArgs* args, void* stream);
 
+/* The all-to-all exchange of the sequence split over peer memory (no reference counterpart: the
+ * reference analyses the route only, tools/probe_segment_affine.py:100-125).  The caller maps every
+ * rank's receive buffers and flag words into every process (CUDA IPC) and passes device pointers;
+ * the library issues plain loads and stores on them -- no multicast, no TMA on peer memory -- and
+ * every wait is bounded (status code 7 in *status when a flag does not arrive within a second).
+ * Flags are int32 epoch counters in the WAITING rank's memory, zero at start, raised to the run's
+ * epoch (1, 2, ...) by the rank that has stored the data.
+ *
+ * kda_peer_push: slice d (slice_floats fp32, a multiple of 4) of src goes to dst[d] +
+ * dst_offset_floats; once the slice is complete *flag[d] = epoch.  counter: `world` zeroed int32 in
+ * local memory, left zeroed.  One launch. */
+#define KDA_MAX_PEERS 16
+typedef struct KdaPeerPushArgs {
+  const float* src;
+  float* dst[KDA_MAX_PEERS];
+  int32_t* flag[KDA_MAX_PEERS];
+  int32_t* counter;
+  int64_t slice_floats, dst_offset_floats;
+  int32_t world, epoch;
+} KdaPeerPushArgs;
+int kda_peer_push(const KdaPeerPushArgs* args, void* stream);
+
+/* kda_state_fold_peer: kda_state_fold_ex on transforms that peers have stored into args->mq.  The
+ * walk starts when the n_wait flags at wait_flags have reached epoch; the state before segment j
+ * (j = n_seg: after the last) of chain c is written to s_in_seg[j] + c * 128 * 128 (typically
+ * rank j's entry-state buffer; NULL entries are skipped; args->s_in is ignored); when all of it
+ * has been stored, *signal[i] = epoch for i < n_signal.  counter: one zeroed int32, left zeroed. */
+typedef struct KdaFoldPeerArgs {
+  const int32_t* wait_flags;
+  int32_t n_wait, epoch;
+  float* s_in_seg[KDA_MAX_PEERS + 1];
+  int32_t* signal[KDA_MAX_PEERS];
+  int32_t n_signal;
+  int32_t* counter;
+} KdaFoldPeerArgs;
+int kda_state_fold_peer(const KdaFoldArgs* args, const KdaFoldPeerArgs* peer, void* stream);
+
+/* kda_peer_enable: lets kernels of the current device load from and store to memory of GPU
+ * peer_device that this process has mapped (cudaDeviceEnablePeerAccess; already enabled is fine).
+ * KDA_ERR_CUDA when the two GPUs have no peer path.  Call it once per peer before the first
+ * kda_peer_push / kda_state_fold_peer that is given pointers into that GPU's memory. */
+int kda_peer_enable(int32_t peer_device);
+
+/* CUDA IPC helpers for that set-up.  kda_ipc_export: the 64-byte handle of the device allocation
+ * that contains ptr and ptr's offset inside it (send both to the other processes).  kda_ipc_open:
+ * maps such a handle for kernels of the CURRENT device (call it with the importing GPU current)
+ * and returns base + offset; a handle is mapped once per process and device (further opens
+ * of it are counted). */
+int kda_ipc_export(const void* ptr, void* handle_out_64_bytes, int64_t* offset_out);
+int kda_ipc_open(const void* handle_64_bytes, int64_t offset, void** ptr_out);
+/* kda_ipc_close: gives back one kda_ipc_open of that handle on the current device; the mapping goes
+ * with the last one.  The exporting process may free the allocation only after every importer has
+ * closed it (or exited). */
+int kda_ipc_close(const void* handle_64_bytes);
+
+/* kda_flag_wait: a one-warp kernel that returns when the n (<= 32) flags have reached epoch, or
+ * writes status code 7 to *status (may be NULL) after the wait limit.  Orders the launches behind
+ * it on `stream` after the peers' stores. */
+int kda_flag_wait(const int32_t* flags, int32_t n, int32_t epoch, int32_t* status, void* stream);
+
 /* Token-by-token recurrence for decode steps and short sequences (T of one to a few dozen
  * tokens): reads the state from args->h0 (NULL = zeros), applies args->T tokens, writes the
  * outputs to args->o and the new state to args->ht (may be NULL; may be the same buffer as h0

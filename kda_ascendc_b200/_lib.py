@@ -17,7 +17,8 @@ FLAG_GATE, FLAG_L2NORM, FLAG_BETA_SIGMOID, FLAG_STATE_K_FIRST = 1, 2, 4, 8
 EXPORTS = (
     "kda_fwd_workspace_bytes", "kda_fwd", "kda_fwd_k1", "kda_fwd_k2", "kda_fwd_k2_state", "kda_recurrent_fwd",
     "kda_varlen_fill_tables", "kda_selftest_bounded_wait", "kda_fwd_static_scratch",
-    "kda_fwd_static_scratch_status", "kda_state_fold", "kda_state_fold_ex",
+    "kda_fwd_static_scratch_status", "kda_state_fold", "kda_state_fold_ex", "kda_state_fold_peer", "kda_peer_push",
+    "kda_flag_wait", "kda_peer_enable", "kda_ipc_export", "kda_ipc_open", "kda_ipc_close",
     "kda_fwd_status", "kda_fwd_k2_choice", "kda_last_launch_count", "kda_last_error", "kda_version",
 )
 
@@ -48,6 +49,25 @@ class KdaFoldArgs(ctypes.Structure):
     ]
 
 
+MAX_PEERS = 16
+
+
+class KdaPeerPushArgs(ctypes.Structure):
+    _fields_ = [
+        ("src", ctypes.c_void_p), ("dst", ctypes.c_void_p * MAX_PEERS), ("flag", ctypes.c_void_p * MAX_PEERS),
+        ("counter", ctypes.c_void_p), ("slice_floats", ctypes.c_int64), ("dst_offset_floats", ctypes.c_int64),
+        ("world", ctypes.c_int32), ("epoch", ctypes.c_int32),
+    ]
+
+
+class KdaFoldPeerArgs(ctypes.Structure):
+    _fields_ = [
+        ("wait_flags", ctypes.c_void_p), ("n_wait", ctypes.c_int32), ("epoch", ctypes.c_int32),
+        ("s_in_seg", ctypes.c_void_p * (MAX_PEERS + 1)), ("signal", ctypes.c_void_p * MAX_PEERS),
+        ("n_signal", ctypes.c_int32), ("counter", ctypes.c_void_p),
+    ]
+
+
 _lib = None
 
 
@@ -74,6 +94,20 @@ def load() -> ctypes.CDLL:
                                    ctypes.c_int32, ctypes.c_int32, ctypes.c_void_p, ctypes.c_void_p]
     lib.kda_state_fold_ex.restype = ctypes.c_int
     lib.kda_state_fold_ex.argtypes = [ctypes.POINTER(KdaFoldArgs), ctypes.c_void_p]
+    lib.kda_state_fold_peer.restype = ctypes.c_int
+    lib.kda_state_fold_peer.argtypes = [ctypes.POINTER(KdaFoldArgs), ctypes.POINTER(KdaFoldPeerArgs), ctypes.c_void_p]
+    lib.kda_peer_push.restype = ctypes.c_int
+    lib.kda_peer_push.argtypes = [ctypes.POINTER(KdaPeerPushArgs), ctypes.c_void_p]
+    lib.kda_peer_enable.restype = ctypes.c_int
+    lib.kda_peer_enable.argtypes = [ctypes.c_int32]
+    lib.kda_ipc_export.restype = ctypes.c_int
+    lib.kda_ipc_export.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.POINTER(ctypes.c_int64)]
+    lib.kda_ipc_open.restype = ctypes.c_int
+    lib.kda_ipc_open.argtypes = [ctypes.c_void_p, ctypes.c_int64, ctypes.POINTER(ctypes.c_void_p)]
+    lib.kda_ipc_close.restype = ctypes.c_int
+    lib.kda_ipc_close.argtypes = [ctypes.c_void_p]
+    lib.kda_flag_wait.restype = ctypes.c_int
+    lib.kda_flag_wait.argtypes = [ctypes.c_void_p, ctypes.c_int32, ctypes.c_int32, ctypes.c_void_p, ctypes.c_void_p]
     lib.kda_selftest_bounded_wait.restype = ctypes.c_int
     lib.kda_selftest_bounded_wait.argtypes = [ctypes.c_void_p, ctypes.c_void_p]
     lib.kda_varlen_fill_tables.restype = ctypes.c_int

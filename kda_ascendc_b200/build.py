@@ -15,7 +15,7 @@ from pathlib import Path
 PKG_DIR = Path(__file__).resolve().parent
 CSRC = PKG_DIR / "csrc"
 LIB_PATH = PKG_DIR / "libkda_b200.so"
-SOURCES = ["kda_c_api.cu", "kda_k1_sm100.cu", "kda_k2_sm100.cu", "kda_k2la_sm100.cu", "kda_k2m_sm100.cu", "kda_k2t_sm100.cu", "kda_recurrent_sm100.cu", "kda_fold_sm100.cu",
+SOURCES = ["kda_c_api.cu", "kda_k1_sm100.cu", "kda_k2_sm100.cu", "kda_k2la_sm100.cu", "kda_k2m_sm100.cu", "kda_k2t_sm100.cu", "kda_recurrent_sm100.cu", "kda_fold_sm100.cu", "kda_peer_sm100.cu",
            "kda_selftest.cu", "kda_static_scratch.cu"]
 HEADERS = ["kda_common.cuh", "kda_kernels.h", "../../include/kda_b200.h"]
 NVCC_FLAGS = [

@@ -3,6 +3,10 @@
 #include <cstddef>
 #include <cstdio>
 #include <cstring>
+#include <mutex>
+#include <vector>
+
+#include <cuda.h>
 
 #include "../../include/kda_b200.h"
 #include "kda_common.cuh"
@@ -390,11 +394,28 @@ int kda_recurrent_fwd(const KdaFwdArgs* a, void* stream) {
   return KDA_OK;
 }
 
-int kda_state_fold_ex(const KdaFoldArgs* f, void* stream) {
+static_assert(KDA_MAX_PEERS == kda::MAX_PEERS, "header and kernel limits differ");
+static_assert(sizeof(KdaPeerPushArgs) == 296 && offsetof(KdaPeerPushArgs, epoch) == 292 && sizeof(KdaFoldPeerArgs) == 296 &&
+                  offsetof(KdaFoldPeerArgs, counter) == 288,
+              "the ctypes mirrors of these structures pin their layout");
+
+static int fold_impl(const KdaFoldArgs* f, const KdaFoldPeerArgs* peer, void* stream) {
   g_launches = 0;
   if (f == nullptr) return fail(KDA_ERR_INVALID_ARG, "kda: fold args is NULL%s", "");
-  if (f->mq == nullptr || (f->s_in == nullptr && f->final_out == nullptr))
+  if (f->mq == nullptr || (peer == nullptr && f->s_in == nullptr && f->final_out == nullptr))
     return fail(KDA_ERR_INVALID_ARG, "kda: the fold needs mq and at least one of s_in / final_out%s", "");
+  if (peer != nullptr) {
+    if (peer->n_wait < 0 || peer->n_wait > KDA_MAX_PEERS || peer->n_signal < 0 || peer->n_signal > KDA_MAX_PEERS ||
+        f->n_seg > KDA_MAX_PEERS)
+      return fail(KDA_ERR_INVALID_ARG, "kda: the peer fold takes at most %s16 segments, flags and signals", "");
+    if ((peer->n_wait > 0 && peer->wait_flags == nullptr) || (peer->n_signal > 0 && peer->counter == nullptr) || peer->epoch <= 0)
+      return fail(KDA_ERR_INVALID_ARG, "kda: the peer fold needs wait_flags, counter and a positive epoch%s", "");
+    for (int i = 0; i <= f->n_seg && i <= KDA_MAX_PEERS; ++i)
+      if (peer->s_in_seg[i] != nullptr && reinterpret_cast<uintptr_t>(peer->s_in_seg[i]) % 16 != 0)
+        return fail(KDA_ERR_INVALID_ARG, "kda: s_in_seg entries must be 16-byte aligned%s", "");
+    for (int i = 0; i < peer->n_signal; ++i)
+      if (peer->signal[i] == nullptr) return fail(KDA_ERR_INVALID_ARG, "kda: signal[%s%lld] is NULL", "", i);
+  }
   if (f->n_chains <= 0 || f->n_seg < 0)
     return fail(KDA_ERR_INVALID_ARG, "kda: the fold needs n_chains > 0 and n_seg >= 0%s (got %lld, %lld)", "", f->n_chains, f->n_seg);
   const int64_t state = static_cast<int64_t>(kda::D) * kda::D;
@@ -422,8 +443,164 @@ int kda_state_fold_ex(const KdaFoldArgs* f, void* stream) {
   p.s_in = f->s_in; p.final_out = f->final_out; p.final_stride = final_stride;
   p.n_chains = f->n_chains; p.n_seg = f->n_seg; p.use_q = f->use_q ? 1 : 0;
   p.status = f->status;
+  if (peer != nullptr) {
+    p.s_in = nullptr;
+    p.wait_flags = peer->wait_flags; p.n_wait = peer->n_wait; p.epoch = peer->epoch;
+    p.s_in_seg_on = 1;
+    for (int i = 0; i <= f->n_seg; ++i) p.s_in_seg[i] = peer->s_in_seg[i];
+    p.n_signal = peer->n_signal;
+    for (int i = 0; i < peer->n_signal; ++i) p.signal[i] = peer->signal[i];
+    p.counter = peer->counter;
+  }
   cudaError_t e = kda::launch_state_fold(p, static_cast<cudaStream_t>(stream));
   if (e != cudaSuccess) return fail(KDA_ERR_CUDA, "kda: fold launch failed: %s", cudaGetErrorString(e));
+  ++g_launches;
+  return KDA_OK;
+}
+
+int kda_state_fold_ex(const KdaFoldArgs* f, void* stream) { return fold_impl(f, nullptr, stream); }
+
+int kda_state_fold_peer(const KdaFoldArgs* f, const KdaFoldPeerArgs* peer, void* stream) {
+  if (peer == nullptr) return fail(KDA_ERR_INVALID_ARG, "kda: peer args is NULL%s", "");
+  return fold_impl(f, peer, stream);
+}
+
+int kda_peer_push(const KdaPeerPushArgs* a, void* stream) {
+  g_launches = 0;
+  if (a == nullptr) return fail(KDA_ERR_INVALID_ARG, "kda: push args is NULL%s", "");
+  if (a->world < 1 || a->world > KDA_MAX_PEERS || a->epoch <= 0)
+    return fail(KDA_ERR_INVALID_ARG, "kda: the push needs 1..16 ranks and a positive epoch%s (world %lld)", "", a->world);
+  if (a->src == nullptr || a->counter == nullptr || a->slice_floats <= 0 || a->slice_floats % 4 != 0 ||
+      a->dst_offset_floats < 0 || a->dst_offset_floats % 4 != 0 || reinterpret_cast<uintptr_t>(a->src) % 16 != 0)
+    return fail(KDA_ERR_INVALID_ARG, "kda: the push needs src, counter and 16-byte multiples for slice and offset%s", "");
+  kda::PeerPushParams p;
+  memset(&p, 0, sizeof(p));
+  for (int d = 0; d < a->world; ++d) {
+    if (a->dst[d] == nullptr || a->flag[d] == nullptr || reinterpret_cast<uintptr_t>(a->dst[d]) % 16 != 0)
+      return fail(KDA_ERR_INVALID_ARG, "kda: dst[%s%lld] and its flag must be set, dst 16-byte aligned", "", d);
+    p.dst[d] = reinterpret_cast<float4*>(a->dst[d]);
+    p.flag[d] = a->flag[d];
+  }
+  p.src = reinterpret_cast<const float4*>(a->src);
+  p.dst_offset = a->dst_offset_floats / 4;
+  p.slice = a->slice_floats / 4;
+  p.counter = a->counter;
+  p.world = a->world; p.epoch = a->epoch;
+  cudaError_t e = kda::launch_peer_push(p, static_cast<cudaStream_t>(stream));
+  if (e != cudaSuccess) return fail(KDA_ERR_CUDA, "kda: push launch failed: %s", cudaGetErrorString(e));
+  ++g_launches;
+  return KDA_OK;
+}
+
+int kda_peer_enable(int32_t peer_device) {
+  int dev = 0, can = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return fail(KDA_ERR_CUDA, "kda: cudaGetDevice failed: %s", cudaGetErrorString(e));
+  if (peer_device == dev) return KDA_OK;
+  e = cudaDeviceCanAccessPeer(&can, dev, peer_device);
+  if (e != cudaSuccess || !can) {
+    cudaGetLastError();
+    return fail(KDA_ERR_CUDA, "kda: this GPU cannot map the memory of GPU %s%lld", "", peer_device);
+  }
+  e = cudaDeviceEnablePeerAccess(peer_device, 0);
+  if (e == cudaErrorPeerAccessAlreadyEnabled) {
+    cudaGetLastError();
+    e = cudaSuccess;
+  }
+  if (e != cudaSuccess) return fail(KDA_ERR_CUDA, "kda: enabling peer access failed: %s", cudaGetErrorString(e));
+  return KDA_OK;
+}
+
+// ---- CUDA IPC for the peer exchange -------------------------------------------------------------
+// The importing side opens a handle with ITS OWN device current, which is what maps the exporting
+// GPU's memory for kernels of the importing GPU (a mapping made with another device current is
+// not reachable from this one).  A handle is opened once per process and stays mapped.
+namespace {
+struct IpcOpened { cudaIpcMemHandle_t h; int dev; void* base; int refs; };
+std::mutex g_ipc_mu;
+std::vector<IpcOpened> g_ipc_opened;
+}  // namespace
+
+int kda_ipc_export(const void* ptr, void* handle_out, int64_t* offset_out) {
+  if (ptr == nullptr || handle_out == nullptr || offset_out == nullptr)
+    return fail(KDA_ERR_INVALID_ARG, "kda: ptr, handle_out and offset_out are required%s", "");
+  typedef CUresult (*RangeFn)(CUdeviceptr*, size_t*, CUdeviceptr);
+  static RangeFn range_fn = nullptr;
+  if (range_fn == nullptr) {
+    void* fp = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuMemGetAddressRange", &fp, cudaEnableDefault, &q) != cudaSuccess || q != cudaDriverEntryPointSuccess)
+      return fail(KDA_ERR_CUDA, "kda: cuMemGetAddressRange is not available from this driver%s", "");
+    range_fn = reinterpret_cast<RangeFn>(fp);
+  }
+  CUdeviceptr base = 0;
+  size_t size = 0;
+  if (range_fn(&base, &size, reinterpret_cast<CUdeviceptr>(ptr)) != CUDA_SUCCESS)
+    return fail(KDA_ERR_CUDA, "kda: the pointer does not belong to a device allocation%s", "");
+  cudaIpcMemHandle_t h;
+  cudaError_t e = cudaIpcGetMemHandle(&h, reinterpret_cast<void*>(base));
+  if (e != cudaSuccess) {
+    cudaGetLastError();
+    return fail(KDA_ERR_CUDA, "kda: cudaIpcGetMemHandle failed: %s", cudaGetErrorString(e));
+  }
+  memcpy(handle_out, &h, sizeof(h));
+  *offset_out = static_cast<int64_t>(reinterpret_cast<CUdeviceptr>(ptr) - base);
+  return KDA_OK;
+}
+
+int kda_ipc_open(const void* handle, int64_t offset, void** ptr_out) {
+  if (handle == nullptr || ptr_out == nullptr || offset < 0)
+    return fail(KDA_ERR_INVALID_ARG, "kda: handle and ptr_out are required%s", "");
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return fail(KDA_ERR_CUDA, "kda: cudaGetDevice failed: %s", cudaGetErrorString(e));
+  cudaIpcMemHandle_t h;
+  memcpy(&h, handle, sizeof(h));
+  std::lock_guard<std::mutex> lock(g_ipc_mu);
+  for (IpcOpened& o : g_ipc_opened)
+    if (o.dev == dev && memcmp(&o.h, &h, sizeof(h)) == 0) {
+      ++o.refs;
+      *ptr_out = static_cast<char*>(o.base) + offset;
+      return KDA_OK;
+    }
+  void* base = nullptr;
+  e = cudaIpcOpenMemHandle(&base, h, cudaIpcMemLazyEnablePeerAccess);
+  if (e != cudaSuccess) {
+    cudaGetLastError();
+    return fail(KDA_ERR_CUDA, "kda: cudaIpcOpenMemHandle failed: %s", cudaGetErrorString(e));
+  }
+  g_ipc_opened.push_back(IpcOpened{h, dev, base, 1});
+  *ptr_out = static_cast<char*>(base) + offset;
+  return KDA_OK;
+}
+
+int kda_ipc_close(const void* handle) {
+  if (handle == nullptr) return fail(KDA_ERR_INVALID_ARG, "kda: handle is required%s", "");
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return fail(KDA_ERR_CUDA, "kda: cudaGetDevice failed: %s", cudaGetErrorString(e));
+  std::lock_guard<std::mutex> lock(g_ipc_mu);
+  for (size_t i = 0; i < g_ipc_opened.size(); ++i) {
+    IpcOpened& o = g_ipc_opened[i];
+    if (o.dev != dev || memcmp(&o.h, handle, sizeof(o.h)) != 0) continue;
+    if (--o.refs > 0) return KDA_OK;
+    e = cudaIpcCloseMemHandle(o.base);
+    g_ipc_opened.erase(g_ipc_opened.begin() + static_cast<long>(i));
+    if (e != cudaSuccess) {
+      cudaGetLastError();
+      return fail(KDA_ERR_CUDA, "kda: cudaIpcCloseMemHandle failed: %s", cudaGetErrorString(e));
+    }
+    return KDA_OK;
+  }
+  return fail(KDA_ERR_INVALID_ARG, "kda: this handle is not open on the current device%s", "");
+}
+
+int kda_flag_wait(const int32_t* flags, int32_t n, int32_t epoch, int32_t* status, void* stream) {
+  g_launches = 0;
+  if (flags == nullptr || n < 1 || n > 32 || epoch <= 0)
+    return fail(KDA_ERR_INVALID_ARG, "kda: the flag wait needs 1..32 flags and a positive epoch%s (n %lld)", "", n);
+  cudaError_t e = kda::launch_flag_wait(flags, n, epoch, status, static_cast<cudaStream_t>(stream));
+  if (e != cudaSuccess) return fail(KDA_ERR_CUDA, "kda: flag wait launch failed: %s", cudaGetErrorString(e));
   ++g_launches;
   return KDA_OK;
 }

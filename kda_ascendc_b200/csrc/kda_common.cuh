@@ -52,6 +52,7 @@ constexpr int ST_OK = 0;
 constexpr int ST_K1_LOAD_TIMEOUT = 1;
 constexpr int ST_K2_FULL_TIMEOUT = 2;
 constexpr int ST_K2_EMPTY_TIMEOUT = 3;
+constexpr int ST_PEER_TIMEOUT = 7;   // a flag from another GPU did not arrive in time (sequence-split exchange)
 
 constexpr float RCP_LN2 = 1.44269504089f;  // literal of tests/test_torch_reference.py:87
 constexpr float L2NORM_EPS = 1e-6f;
@@ -134,6 +135,29 @@ __device__ __forceinline__ bool mbar_spin_bounded(uint32_t bar, uint32_t parity,
   for (int i = 0; i < 4096; ++i)
     if (mbar_test_wait(bar, parity)) return true;
   return mbar_wait_bounded(bar, parity, abort_flag);
+}
+
+// ---- flags between GPUs (peer memory) ------------------------------------------
+// A flag is an int32 epoch counter in the waiting GPU's own memory; a peer raises it with a
+// system-scope release store after its data stores, the owner polls it with system-scope acquire
+// loads.  Bounded like every other wait: false after WAIT_LIMIT_NS.
+__device__ __forceinline__ int ld_acquire_sys(const int* p) {
+  int v;
+  asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_release_sys(int* p, int v) {
+  asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ bool flag_wait_bounded(const int* flag, int epoch) {
+  if (ld_acquire_sys(flag) - epoch >= 0) return true;
+  const unsigned long long t0 = globaltimer_ns();
+  for (;;) {
+#pragma unroll 1
+    for (int i = 0; i < 64; ++i)
+      if (ld_acquire_sys(flag) - epoch >= 0) return true;
+    if (globaltimer_ns() - t0 > WAIT_LIMIT_NS) return false;
+  }
 }
 
 // ---- bulk (TMA, untiled) copies ---------------------------------------------

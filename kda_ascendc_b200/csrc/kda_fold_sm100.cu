@@ -16,6 +16,11 @@
 // parity bound is 2e-3 absolute, so there is no reduced-precision tensor-core path here.  ROWS is 4
 // while the CTAs (chains * 128 / ROWS, one per SM: the ring takes 128 KiB) fit one wave, else 16.
 // Every wait is bounded and reports through the status word.
+//
+// Exchange over peer memory (FoldParams::wait_flags / s_in_seg / signal): when the transforms are
+// stored into mq by the other GPUs of a sequence split, the walk first waits (bounded) for their
+// flags, writes the entry state of segment j straight into rank j's buffer, and the last CTA to
+// finish raises the flags that tell those ranks their entry states have arrived.
 #include "../../include/kda_b200.h"
 #include "kda_common.cuh"
 #include "kda_kernels.h"
@@ -72,8 +77,14 @@ kda_state_fold_kernel(const FoldParams p) {
     mbar_init(full0 + 8, 1);
     *sAbort = 0;
     fence_mbar_init();
-    if (n_seg > 0) issue(0);
-    if (n_seg > 1) issue(1);
+    // transforms stored by peers: wait for every source's flag before the first copy reads them
+    for (int i = 0; i < p.n_wait; ++i)
+      if (!flag_wait_bounded(p.wait_flags + i, p.epoch)) { *sAbort = 2; break; }
+    if (*sAbort == 0) {
+      if (p.n_wait > 0) fence_proxy_async();
+      if (n_seg > 0) issue(0);
+      if (n_seg > 1) issue(1);
+    }
   }
 
   float s[ROWS];
@@ -81,14 +92,24 @@ kda_state_fold_kernel(const FoldParams p) {
   for (int r = 0; r < ROWS; ++r)
     s[r] = (h0 != nullptr) ? h0[static_cast<size_t>(chain) * p.h0_stride + static_cast<size_t>(r0 + r) * D + t] : 0.f;
   __syncthreads();   // barriers initialised
+  if (*sAbort == 2) {   // a peer's flag never came: nothing has been issued, report and leave
+    if (t == 0 && status != nullptr) atomicExch(status, ST_PEER_TIMEOUT);
+    return;
+  }
+  // where the state before segment j (j = n_seg: after the last one) of this chain goes, or null
+  auto s_in_at = [&](int j) -> float* {
+    if (p.s_in_seg_on) return p.s_in_seg[j] != nullptr ? p.s_in_seg[j] + static_cast<size_t>(chain) * state_elems : nullptr;
+    return s_in != nullptr ? s_in + (static_cast<size_t>(j) * n_chains + chain) * state_elems : nullptr;
+  };
 
   int issued = n_seg < 2 ? n_seg : 2;
   for (int j = 0; j < n_seg; ++j) {
     const float* Q = m_ptr(j) + state_elems;
+    float* const sj = s_in_at(j);
     float acc[ROWS];
 #pragma unroll
     for (int r = 0; r < ROWS; ++r) {
-      if (s_in != nullptr) s_in[(static_cast<size_t>(j) * n_chains + chain) * state_elems + static_cast<size_t>(r0 + r) * D + t] = s[r];
+      if (sj != nullptr) sj[static_cast<size_t>(r0 + r) * D + t] = s[r];
       sS[j & 1][r][t] = s[r];
       acc[r] = p.use_q ? __ldg(Q + static_cast<size_t>(r0 + r) * D + t) : 0.f;
     }
@@ -130,10 +151,26 @@ kda_state_fold_kernel(const FoldParams p) {
     __syncthreads();
     return;
   }
+  float* const s_last = s_in_at(n_seg);
 #pragma unroll
   for (int r = 0; r < ROWS; ++r) {
-    if (s_in != nullptr) s_in[(static_cast<size_t>(n_seg) * n_chains + chain) * state_elems + static_cast<size_t>(r0 + r) * D + t] = s[r];
+    if (s_last != nullptr) s_last[static_cast<size_t>(r0 + r) * D + t] = s[r];
     if (p.final_out != nullptr) p.final_out[static_cast<size_t>(chain) * p.final_stride + static_cast<size_t>(r0 + r) * D + t] = s[r];
+  }
+  if (p.n_signal > 0) {
+    // every thread's stores to the peers are ordered before the flags: fence, count this CTA, and the
+    // last CTA of the grid raises them
+    __threadfence_system();
+    __syncthreads();
+    if (t == 0) {
+      const int done = atomicAdd(p.counter, 1);
+      __threadfence();
+      if (done == static_cast<int>(gridDim.x) - 1) {
+        *p.counter = 0;
+        __threadfence_system();
+        for (int i = 0; i < p.n_signal; ++i) st_release_sys(p.signal[i], p.epoch);
+      }
+    }
   }
 }
 

@@ -99,6 +99,8 @@ cudaError_t launch_k2n_pair(const K2Params& p, int vsplit, cudaStream_t stream);
 cudaError_t launch_k2t(const K2Params& p, long long n_records, cudaStream_t stream);
 
 // Walk of the per-segment affine state transforms of a sequence split (kda_fold_sm100.cu).
+constexpr int MAX_PEERS = 16;   // = KDA_MAX_PEERS of the public header
+
 struct FoldParams {
   const float* mq;             // M_j[c] at mq + j*seg_stride + c*chain_stride (floats), Q_j[c] 128*128 floats behind it
   long long seg_stride, chain_stride;
@@ -110,8 +112,32 @@ struct FoldParams {
   int n_chains, n_seg;
   int use_q;                   // 0: the walk is S <- S * M_j (composition of transition matrices)
   int* status;
+  // Exchange over peer memory (all zero for the plain fold).  The walk starts once the n_wait local
+  // flags have reached `epoch` (peers have stored the transforms into mq); the state before segment j
+  // goes to s_in_seg[j] + chain * 128 * 128 (a peer's buffer; a null entry is skipped) instead of s_in;
+  // after the last CTA has finished, *signal[i] = epoch for i < n_signal (system scope).
+  const int* wait_flags;
+  int n_wait, epoch;
+  int s_in_seg_on;
+  float* s_in_seg[MAX_PEERS + 1];
+  int* signal[MAX_PEERS];
+  int n_signal;
+  int* counter;                // local int, zero between launches
 };
 cudaError_t launch_state_fold(const FoldParams& p, cudaStream_t stream);
+
+// Peer-memory pieces of the sequence split's exchange (kda_peer_sm100.cu).
+struct PeerPushParams {
+  const float4* src;           // [world][slice] 16-byte units: slice d goes to rank d
+  float4* dst[MAX_PEERS];  // rank d's receive buffer (peer-mapped; the own one for d = rank)
+  long long dst_offset;        // 16-byte units into dst[d]: this rank's slot
+  long long slice;             // 16-byte units per destination
+  int* flag[MAX_PEERS];    // raised to `epoch` on rank d once the slice has been stored
+  int* counter;                // local int[world], zero between launches
+  int world, epoch;
+};
+cudaError_t launch_peer_push(const PeerPushParams& p, cudaStream_t stream);
+cudaError_t launch_flag_wait(const int* flags, int n, int epoch, int* status, cudaStream_t stream);
 
 // Token recurrence (decode / short sequences): no chunking, no workspace (kda_recurrent_sm100.cu).
 struct RecurrentParams {

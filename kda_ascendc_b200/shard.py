@@ -26,6 +26,7 @@ Two ways to spread one problem over the GPUs of a box:
 from __future__ import annotations
 
 import ctypes
+import os
 from typing import Optional, Sequence
 
 import torch
@@ -240,22 +241,212 @@ def exchange_and_fold(mq_local: torch.Tensor, h0: Optional[torch.Tensor], rank: 
         final = s_in[world] if want_final else None
     else:
         hp = chains // world
-        recv = buf("recv_mq", (world, hp, 2, D, D))            # [segment][my chains]
-        dist.all_to_all_single(recv, rank_mq.view(world, hp, 2, D, D), group=group)
-        s_in = buf("s_in", (world + 1, hp, D, D))
-        walk(recv, None if h0c is None else h0c[rank * hp:(rank + 1) * hp], world, s_in=s_in, status=status)
-        ent = buf("entry", (world, hp, D, D))                  # [owner of the chains][chains] = all chains in order
-        dist.all_to_all_single(ent, s_in[:world], group=group)
-        entry = ent.view(chains, D, D)
+        h0_own = None if h0c is None else h0c[rank * hp:(rank + 1) * hp]
+        peer = bufs.get("peer")
+        if peer is not None:                                   # stores and flags over peer memory, three launches
+            entry, last = peer.run(rank_mq.contiguous(), h0_own, status, want_final)
+        else:
+            recv = buf("recv_mq", (world, hp, 2, D, D))        # [segment][my chains]
+            dist.all_to_all_single(recv, rank_mq.view(world, hp, 2, D, D), group=group)
+            s_in = buf("s_in", (world + 1, hp, D, D))
+            walk(recv, h0_own, world, s_in=s_in, status=status)
+            ent = buf("entry", (world, hp, D, D))              # [owner of the chains][chains] = all chains in order
+            dist.all_to_all_single(ent, s_in[:world], group=group)
+            entry = ent.view(chains, D, D)
+            last = s_in[world].contiguous() if want_final else None
         if want_final:
             final = buf("final", (world, hp, D, D))
-            dist.all_gather_into_tensor(final.view(chains, D, D), s_in[world].contiguous(), group=group)
+            dist.all_gather_into_tensor(final.view(chains, D, D), last, group=group)
             final = final.view(chains, D, D)
     if sub == 1:
         return entry.view(1, chains, D, D), final
     sub_entry = buf("sub_entry", (sub, chains, D, D))          # entry states of this rank's sub-segments
     walk(mq5, entry, sub - 1, s_in=sub_entry, status=status)
     return sub_entry, final
+
+
+class _PeerExchange:
+    """The all-to-all exchange of a sequence split over peer memory: one process per GPU of ONE box.
+
+    Every rank owns one block -- a receive buffer for the transforms ``[world, hp, 2, 128, 128]`` (slot =
+    source rank), a buffer for the entry states of its own segment ``[world, hp, 128, 128]`` (slot =
+    the rank that owns and folds those chains) and two rows of int32 flags -- and maps the blocks of
+    all other ranks into its address space (CUDA IPC: ``kda_ipc_export`` / ``kda_ipc_open``, opened with
+    the importing GPU current; a block stays mapped in the peers until they exit, so a plan's block is
+    never returned to the driver while peers may still hold the mapping -- it goes back to torch's
+    caching allocator, which keeps the allocation).  A run is
+    three launches: ``kda_peer_push`` stores this rank's transforms into the owners' receive
+    buffers and raises their flags; ``kda_state_fold_peer`` waits for the flags of all sources, walks
+    this rank's chains and stores the state before segment j straight into rank j's entry buffer,
+    then raises the entry flags; ``kda_flag_wait`` holds the stream until every owner's entry states
+    have arrived.  Flags carry the run number, so nothing is reset between runs; every wait is
+    bounded and reports status code 7.  Buffers are reused safely: a rank starts run e + 1 only after
+    every owner has signalled the end of its walk of run e, and an owner starts its walk of run
+    e + 1 only after every rank has finished reading the entry states of run e.
+
+    ``_PeerExchange.create`` returns None (on every rank alike) when any rank could not set it up;
+    the caller then uses the NCCL collectives.
+    """
+
+    FLAG_WORDS = 64       # int32: [0, world) transforms from rank j; [world, 2 world) entry states from owner j; [32, 64) self-check
+
+    def __init__(self):
+        self.epoch = 0
+
+    @classmethod
+    def create(cls, chains: int, world: int, rank: int, group, device):
+        import torch.distributed as dist
+
+        self = cls()
+        lib = _lib.load()
+        ok, info = 1, None
+        try:
+            if chains % world or world > _lib.MAX_PEERS or 2 * world > 32:
+                raise ValueError("chain count or world size outside the peer exchange's range")
+            self.world, self.rank, self.hp, self.dev = world, rank, chains // world, device
+            n_recv, n_ent = chains * 2 * D * D, chains * D * D
+            self.block = torch.zeros(n_recv + n_ent + cls.FLAG_WORDS, dtype=torch.float32, device=device)
+            self.recv = self.block[:n_recv].view(world, self.hp, 2, D, D)
+            self.ent = self.block[n_recv:n_recv + n_ent].view(world, self.hp, D, D)
+            self.flag_off = n_recv + n_ent                      # in 4-byte words from the start of the block
+            self.flags = self.block[self.flag_off:].view(torch.int32)
+            self.counters = torch.zeros(world + 1, dtype=torch.int32, device=device)
+            self.final = torch.empty((self.hp, D, D), dtype=torch.float32, device=device)
+            torch.cuda.synchronize(device)
+            hbuf, off = ctypes.create_string_buffer(64), ctypes.c_int64(0)
+            with torch.cuda.device(device):
+                api._check(lib.kda_ipc_export(self.block.data_ptr(), hbuf, ctypes.byref(off)))
+            info = (bytes(hbuf.raw), int(off.value), int(device.index))
+        except Exception:  # noqa: BLE001 - any failure here means: use the collectives instead
+            ok = 0
+        infos = [None] * world
+        dist.all_gather_object(infos, (ok, info), group=group)
+        if all(i is not None and i[0] == 1 for i in infos):
+            try:
+                self.peer_ptr = []
+                self._opened = []
+                self._group = group
+                with torch.cuda.device(device):      # the importing GPU must be current when a handle is opened
+                    for r, (_, (handle, off, owner_dev)) in enumerate(infos):
+                        if r == rank:
+                            self.peer_ptr.append(self.block.data_ptr())
+                            continue
+                        api._check(lib.kda_peer_enable(owner_dev))
+                        ptr = ctypes.c_void_p(0)
+                        api._check(lib.kda_ipc_open(handle, off, ctypes.byref(ptr)))
+                        self._opened.append(handle)
+                        self.peer_ptr.append(int(ptr.value))
+                self._build_args()
+            except Exception:  # noqa: BLE001
+                ok = 0
+        else:
+            ok = 0
+        agreed = torch.tensor([ok], dtype=torch.int32, device=device)
+        dist.all_reduce(agreed, op=dist.ReduceOp.MIN, group=group)
+        if int(agreed.item()) == 0:
+            return None
+        # a dry run through the real kernels: every rank sends a pattern to every rank
+        try:
+            good = self._self_check()
+        except Exception:  # noqa: BLE001
+            good = 0
+        agreed = torch.tensor([good], dtype=torch.int32, device=device)
+        dist.all_reduce(agreed, op=dist.ReduceOp.MIN, group=group)
+        return self if int(agreed.item()) == 1 else None
+
+    def close(self):
+        """Collective: every rank unmaps the other ranks' blocks; afterwards the blocks may be freed.  Without it
+        the mappings live until the processes exit, and a block must not be returned to the driver
+        (``torch.cuda.empty_cache()``) while a peer still maps it."""
+        import torch.distributed as dist
+
+        if getattr(self, "_opened", None) is None:
+            return
+        torch.cuda.synchronize(self.dev)
+        dist.barrier(group=self._group)                     # nobody stores into a block any more
+        lib = _lib.load()
+        with torch.cuda.device(self.dev):
+            for handle in self._opened:
+                lib.kda_ipc_close(handle)
+        self._opened = None
+        dist.barrier(group=self._group)                     # every mapping is gone: the owners may free
+
+    def _build_args(self):
+        world, rank, hp = self.world, self.rank, self.hp
+        flag_addr = [ptr + 4 * self.flag_off for ptr in self.peer_ptr]          # start of rank r's flag words
+        push = _lib.KdaPeerPushArgs()
+        for d in range(world):
+            push.dst[d] = self.peer_ptr[d]                                       # rank d's receive buffer is the start of its block
+            push.flag[d] = flag_addr[d] + 4 * rank
+        push.counter = self.counters.data_ptr()
+        push.slice_floats = hp * 2 * D * D
+        push.dst_offset_floats = rank * hp * 2 * D * D
+        push.world = world
+        self._push = push
+        f = _lib.KdaFoldArgs()
+        f.mq = self.recv.data_ptr()
+        f.seg_stride, f.chain_stride = hp * 2 * D * D, 2 * D * D
+        f.n_chains, f.n_seg, f.use_q = hp, world, 1
+        self._fold = f
+        pa = _lib.KdaFoldPeerArgs()
+        pa.wait_flags, pa.n_wait = flag_addr[rank], world
+        ent_off = 4 * (world * hp * 2 * D * D)                                   # bytes from the start of a block to its entry buffer
+        for j in range(world):
+            pa.s_in_seg[j] = self.peer_ptr[j] + ent_off + 4 * rank * hp * D * D
+            pa.signal[j] = flag_addr[j] + 4 * (world + rank)
+        pa.n_signal = world
+        pa.counter = self.counters.data_ptr() + 4 * world
+        self._peer = pa
+        self._wait_flags = flag_addr[rank] + 4 * world
+
+    def _self_check(self) -> int:
+        lib = _lib.load()
+        world, rank = self.world, self.rank
+        self.epoch += 1
+        src = (torch.arange(world, device=self.dev, dtype=torch.float32).view(world, 1) + 1.0 + 100.0 * rank).repeat(1, 4).contiguous()
+        a = _lib.KdaPeerPushArgs.from_buffer_copy(self._push)
+        check_off = 4 * (self.flag_off + 32)                                     # the self-check words behind the flags
+        for d in range(world):
+            a.dst[d] = self.peer_ptr[d] + check_off
+        a.src, a.slice_floats, a.dst_offset_floats, a.epoch = src.data_ptr(), 4, 4 * rank, self.epoch
+        if world * 4 > 32:
+            return 0
+        with torch.cuda.device(self.dev):
+            stream = api._stream_handle()
+            api._check(lib.kda_peer_push(ctypes.byref(a), stream))
+            api._check(lib.kda_flag_wait(self._wait_flags - 4 * world, world, self.epoch, None, stream))
+            torch.cuda.synchronize(self.dev)
+        got = self.block[self.flag_off + 32:self.flag_off + 32 + 4 * world].view(world, 4)
+        want = (100.0 * torch.arange(world, device=self.dev, dtype=torch.float32).view(world, 1) + rank + 1.0).expand(world, 4)
+        return int(bool(torch.equal(got, want)))
+
+    def run(self, rank_mq: torch.Tensor, h0: Optional[torch.Tensor], status: Optional[torch.Tensor], want_final: bool):
+        """``rank_mq``: this rank's transforms ``[chains, 2, 128, 128]`` (contiguous); ``h0``: the state before the
+        first segment of this rank's OWN chains ``[hp, 128, 128]`` or None.  Returns the entry states of this
+        rank's segment for all chains ``[chains, 128, 128]`` (the plan's buffer) and, with ``want_final``, the
+        state after the last segment of the own chains ``[hp, 128, 128]``."""
+        lib = _lib.load()
+        if not rank_mq.is_contiguous() or rank_mq.dtype != torch.float32:
+            raise ValueError("rank_mq must be a contiguous fp32 tensor")
+        self.epoch += 1
+        push, f, pa = self._push, self._fold, self._peer
+        push.src, push.epoch = rank_mq.data_ptr(), self.epoch
+        if h0 is not None:
+            if h0.dtype != torch.float32 or h0.stride()[-2:] != (D, 1):
+                raise ValueError("h0 must be fp32 with dense 128 x 128 blocks")
+            f.h0, f.h0_stride = h0.data_ptr(), (h0.stride(0) if h0.shape[0] > 1 else D * D)
+        else:
+            f.h0, f.h0_stride = None, 0
+        st_ptr = None if status is None else status.data_ptr()
+        f.status = st_ptr
+        pa.epoch = self.epoch
+        pa.s_in_seg[self.world] = self.final.data_ptr() if want_final else None
+        with torch.cuda.device(self.dev):
+            stream = api._stream_handle()
+            api._check(lib.kda_peer_push(ctypes.byref(push), stream))
+            api._check(lib.kda_state_fold_peer(ctypes.byref(f), ctypes.byref(pa), stream))
+            api._check(lib.kda_flag_wait(self._wait_flags, self.world, self.epoch, st_ptr, stream))
+        return self.ent.view(self.world * self.hp, D, D), (self.final if want_final else None)
 
 
 def _sub_segments(x: torch.Tensor, sub: int) -> torch.Tensor:
@@ -327,7 +518,10 @@ class SeqParallelPlan:
     ``segments_per_rank``: a K2 pass is one serial chain per (batch, head), so a rank with few heads
     leaves most of its GPU idle; cutting the rank's tokens into 2 or 4 consecutive sub-segments
     (handled as batch entries of the same launches, no copy) runs that many chains side by side
-    for the same total work.  ``"auto"`` takes the largest of 4, 2 that keeps the chains of a pass at
+    for the same total work.  ``peer_exchange``: ``"auto"`` (default; the environment variable
+    ``KDA_B200_PEER_EXCHANGE=0`` turns it off), ``True`` (fail if it cannot be set up) or ``False``: the
+    all-to-all exchange as stores and flags over peer memory instead of two NCCL collectives.
+    ``segments_per_rank="auto"`` takes the largest of 4, 2 that keeps the chains of a pass at
     64 or fewer and the sub-segments at 2,048 tokens or more, else 1 (measured per rank on B200, 16
     heads x 16,384 tokens: K1 + transform pass + K2 = 1,060 us with one, 766 us with two, 605 us with
     four sub-segments).  The exchange stays that of one segment per rank: the rank composes its
@@ -335,7 +529,8 @@ class SeqParallelPlan:
     """
 
     def __init__(self, q, k, v, g, beta, *, scale=None, initial_state=None, lower_bound=-5.0, A_log=None,
-                 dt_bias=None, group=None, exchange="auto", final_state_on_all_ranks=False, segments_per_rank="auto"):
+                 dt_bias=None, group=None, exchange="auto", final_state_on_all_ranks=False, segments_per_rank="auto",
+                 peer_exchange="auto"):
         import torch.distributed as dist
 
         self.group = group
@@ -364,6 +559,24 @@ class SeqParallelPlan:
         self.want_final = bool(final_state_on_all_ranks)
         self.bufs: dict = {}
         self.out_shape = (B, L, H, D)
+        # The all-to-all runs over peer memory when the ranks can map each other's buffers (one box);
+        # every rank takes the same decision (the set-up is collective), else the NCCL collectives.
+        self.exchange_kind = "nccl"
+        want_peer = peer_exchange is True or (peer_exchange == "auto" and os.environ.get("KDA_B200_PEER_EXCHANGE", "1") != "0")
+        if self.world > 1 and self.mode == "a2a" and want_peer and q.is_cuda:
+            peer = _PeerExchange.create(self.chains, self.world, self.rank, group, q.device)
+            if peer is not None:
+                self.bufs["peer"] = peer
+                self.exchange_kind = "peer"
+            elif peer_exchange is True:
+                raise RuntimeError("the ranks could not map each other's memory: no peer exchange")
+
+    def close(self):
+        """Collective (call it on every rank, or on none): releases the peer mappings of the exchange, after
+        which the plan's buffers may be freed and the plan must not run again."""
+        peer = self.bufs.pop("peer", None)
+        if peer is not None:
+            peer.close()
 
     def run(self, timeline: Optional[list] = None):
         """One forward.  ``timeline``: a list that receives ``(phase, torch.cuda.Event)`` pairs

@@ -32,6 +32,35 @@ def test_library_exports_every_declared_symbol():
     assert set(_lib.EXPORTS) <= declared
 
 
+def test_peer_structs_and_argument_checks():
+    """The peer-exchange entry points: ctypes mirrors (sizes pinned by static_asserts in the library) and
+    the host-side argument checks (nothing is launched)."""
+    assert ctypes.sizeof(_lib.KdaPeerPushArgs) == 296 and _lib.KdaPeerPushArgs.epoch.offset == 292
+    assert ctypes.sizeof(_lib.KdaFoldPeerArgs) == 296 and _lib.KdaFoldPeerArgs.counter.offset == 288
+    lib = _lib.load()
+    a = _lib.KdaPeerPushArgs()
+    assert lib.kda_peer_push(None, None) == -1
+    a.world, a.epoch = 17, 1
+    assert lib.kda_peer_push(ctypes.byref(a), None) == -1 and "ranks" in _lib.last_error()
+    a.world, a.epoch = 2, 0
+    assert lib.kda_peer_push(ctypes.byref(a), None) == -1
+    a.epoch, a.src, a.counter, a.slice_floats = 1, 1024, 2048, 6
+    assert lib.kda_peer_push(ctypes.byref(a), None) == -1 and "16-byte" in _lib.last_error()
+    a.slice_floats = 8
+    assert lib.kda_peer_push(ctypes.byref(a), None) == -1 and "dst[0]" in _lib.last_error()
+    assert lib.kda_flag_wait(None, 1, 1, None, None) == -1
+    assert lib.kda_flag_wait(4096, 33, 1, None, None) == -1 and lib.kda_flag_wait(4096, 1, 0, None, None) == -1
+    f, pa = _lib.KdaFoldArgs(), _lib.KdaFoldPeerArgs()
+    f.mq, f.n_chains, f.n_seg, f.seg_stride, f.chain_stride, f.use_q = 4096, 1, 2, 32768, 32768, 1
+    assert lib.kda_state_fold_peer(ctypes.byref(f), None, None) == -1
+    pa.n_wait, pa.epoch = 2, 1
+    assert lib.kda_state_fold_peer(ctypes.byref(f), ctypes.byref(pa), None) == -1 and "wait_flags" in _lib.last_error()
+    pa.wait_flags, pa.n_signal, pa.counter = 4096, 1, 4096
+    assert lib.kda_state_fold_peer(ctypes.byref(f), ctypes.byref(pa), None) == -1 and "signal[0]" in _lib.last_error()
+    f.n_seg = 17
+    assert lib.kda_state_fold_peer(ctypes.byref(f), ctypes.byref(pa), None) == -1 and "16 segments" in _lib.last_error()
+
+
 def test_struct_layout_matches_header():
     # 13 pointers, 4 int32, 6 x 3 int64, 2 floats, uint32, 3 int32, 2 pointers, int32 + padding
     assert ctypes.sizeof(_lib.KdaFwdArgs) == 13 * 8 + 4 * 4 + 18 * 8 + 6 * 4 + 2 * 8 + 8

@@ -29,6 +29,7 @@ def _rank_main(rank, world, port, ret):
         dev = torch.device("cuda", rank)
         T = 1024
         seq = {}
+        transports, same_exchange = set(), True
         for regime, exchange, sub in (("carry", "a2a", 1), ("carry", "gather", 1), ("carry", "gather", 2), ("carry", "a2a", 4),
                                       ("baseline", "a2a", 1), ("baseline", "auto", "auto")):
             inp = O.make_inputs(1, T, 4, seed0=21, regime=regime, h0_std=0.1 if regime == "carry" else 0.02)
@@ -54,13 +55,28 @@ def _rank_main(rank, world, port, ret):
             e_or = (o2.float().cpu() - o_r[:, sl].float()).abs().max().item()
             e_hr = (h2.cpu() - h_r).abs().max().item()
             seq[(regime, exchange, sub)] = (e_o, e_h, e_or, e_hr, omax, hmax)
+            if plan.mode == "a2a":
+                # The exchange over peer memory (stores + flags, when the ranks could map each other) moves the same
+                # numbers as the NCCL all-to-all: with it switched off, three more runs must give the same bits.
+                transports.add(plan.exchange_kind)
+                plan_n = shard.SeqParallelPlan(d["q"][:, sl], d["k"][:, sl], d["v"][:, sl], d["g"][:, sl], d["beta"][:, sl],
+                                               initial_state=d["initial_state"], exchange=exchange,
+                                               final_state_on_all_ranks=True, segments_per_rank=sub, peer_exchange=False, **kw)
+                assert plan_n.exchange_kind == "nccl"
+                for _ in range(3):
+                    o2b, h2b = plan.run()
+                    o2n, h2n = plan_n.run()
+                    same_exchange = same_exchange and bool(torch.equal(o2b, o2n) and torch.equal(h2b, h2n))
+                assert K.api.check_device_status(plan.seg.ws) == 0
+                plan_n.close()
+            plan.close()
         e_seq = seq
         # head shards: rank r owns a contiguous block of heads, nothing is exchanged
         o3, h3, (lo, hi) = shard.forward_head_shard(d["q"], d["k"], d["v"], d["g"], d["beta"], rank=rank, world=world,
                                                     initial_state=d["initial_state"], output_final_state=True, **kw)
         same = bool(torch.equal(o3, o1[:, :, lo:hi]) and torch.equal(h3, h1[:, lo:hi]))
         torch.cuda.synchronize()
-        ret[rank] = (e_seq, same)
+        ret[rank] = (e_seq, same, sorted(transports), same_exchange)
     finally:
         dist.destroy_process_group()
 
@@ -74,7 +90,14 @@ def test_two_ranks_sequence_split_and_head_shards():
     ret = mp.Manager().dict()
     mp.spawn(_rank_main, args=(world, _free_port(), ret), nprocs=world, join=True)
     for r in range(world):
-        e_seq, same = ret[r]
+        e_seq, same, transports, same_exchange = ret[r]
+        assert same_exchange, (r, transports)
+        # on one NVLink box the peer exchange comes up; where the ranks cannot map each other the plan falls
+        # back to the NCCL collectives on every rank alike (then the comparison above is NCCL against NCCL)
+        assert set(transports) <= {"peer", "nccl"} and len(transports) == 1, (r, transports)
+        if transports != ["peer"]:
+            import warnings
+            warnings.warn("the peer exchange did not come up on this box: %r" % (transports,))
         for (regime, exchange, sub), (e_o, e_h, e_or, e_hr, omax, hmax) in e_seq.items():
             if regime == "baseline":   # benchmark distribution: the absolute bounds of the one-pass path
                 assert e_or <= 1e-3 and e_hr <= 2e-3, (r, regime, exchange, sub, e_or, e_hr)
