@@ -13,8 +13,8 @@
 // memory.  M_j (64 KiB) arrives by bulk (TMA) copies into a two-deep ring, so the copy of M_{j+1}
 // runs under the products with M_j and the walk costs about one L2-to-shared copy per segment
 // instead of 128 dependent global reads.  Plain fp32 FMAs: the entry states feed a recurrence whose
-// parity bound is 2e-3 absolute, so there is no reduced-precision tensor-core path here.  ROWS is 4
-// while the CTAs (chains * 128 / ROWS, one per SM: the ring takes 128 KiB) fit one wave, else 16.
+// parity bound is 2e-3 absolute, so there is no reduced-precision tensor-core path here.  ROWS is the
+// smallest of 4, 8, 16 with which the CTAs (chains * 128 / ROWS, one per SM: the ring takes 128 KiB) fit one wave.
 // Every wait is bounded and reports through the status word.
 //
 // Exchange over peer memory (FoldParams::wait_flags / s_in_seg / signal): when the transforms are
@@ -194,8 +194,10 @@ cudaError_t launch_state_fold(const FoldParams& p, cudaStream_t stream) {
   if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   // Measured on B200 (8 segments): the walk is bound by the L2-to-shared copies of M_j (every CTA of a
   // chain pulls all 64 KiB of it), so few rows per CTA only pay while the CTAs fit one wave:
-  // 4 chains 23 us with 4 rows per CTA against 35 us with 16; 32 chains 100 us against 65 us.
+  // 4 chains 23 us with 4 rows per CTA against 35 us with 16; 32 chains 100 us against 65 us; in between
+  // 8 rows per CTA (8 chains x 4 segments 19.9 us against 24.1 us with 16 rows, x 8 segments 28.5 against 38.9).
   if (p.n_chains * (D / 4) <= sms) return launch_fold_t<4>(p, stream);
+  if (p.n_chains * (D / 8) <= sms) return launch_fold_t<8>(p, stream);
   return launch_fold_t<16>(p, stream);
 }
 
