@@ -71,6 +71,20 @@ NCU_TRAFFIC = dict(shape=(1, 8192, 32), record_bytes=26112, source="profiles/kda
                    bytes={"kda_k1": 643.47e6, "kda_k2": 489.44e6})
 
 
+def merge_exchange_marks(names, values):
+    """The peer exchange marks the end of its push and of its walk inside the `exchange_fold` phase of a plan's
+    timeline: fold the three intervals back into one phase (so that the timeline reads the same for both
+    transports) and return the parts separately (ms; None for the NCCL exchange)."""
+    if "exchange_push" not in names:
+        return list(names), list(values), None
+    parts = dict(zip(names, values))
+    total = parts["exchange_push"] + parts["exchange_walk"] + parts["exchange_fold"]
+    out_n = [n for n in names if n not in ("exchange_push", "exchange_walk")]
+    out_v = [total if n == "exchange_fold" else parts[n] for n in out_n]
+    return out_n, out_v, dict(push=parts["exchange_push"] * 1e3, walk_incl_waiting_for_peers=parts["exchange_walk"] * 1e3,
+                              entry_states_arrive=parts["exchange_fold"] * 1e3)
+
+
 def workload_text(n_gpus):
     if n_gpus == 1:
         return "KDA fwd B=1 T=8192 H=32 K=V=128 BT=16 bf16 (headline benchmark shape) on one GPU"
@@ -431,6 +445,7 @@ def run_gpu_arm(steps, warmup, n_gpus, kernels_only=False):
                 phases.setdefault(n1, []).append(e0_.elapsed_time(e1_))
         ph_names = list(phases)
         ph_max = max_over_ranks([statistics.mean(phases[n]) for n in ph_names])
+        ph_names, ph_max, exchange_parts = merge_exchange_marks(ph_names, ph_max)
         # what the two splits return against the whole-sequence forward of this very run
         e_h_o = (o_h.float() - o_whole[:, :, lo:hi].float()).abs().max().item()
         e_h_s = (ht_h - ht_whole[:, lo:hi]).abs().max().item()
@@ -446,7 +461,7 @@ def run_gpu_arm(steps, warmup, n_gpus, kernels_only=False):
                             max_abs_vs_one_gpu=dict(o=e_h_o, ht=e_h_s)),
             seq_split=dict(ms_per_step=ms_seq / steps, tokens_per_s=B * T * steps / (ms_seq * 1e-3),
                            tokens_per_gpu=L, exchange=plan.mode, exchange_transport=plan.exchange_kind,
-                           timeline_us={n: v * 1e3 for n, v in zip(ph_names, ph_max)},
+                           timeline_us={n: v * 1e3 for n, v in zip(ph_names, ph_max)}, exchange_parts_us=exchange_parts,
                            sub_segments_per_rank=plan.sub,
                            collectives="2 all-to-all (NCCL) per forward" if plan.mode == "a2a" else "1 all-gather (NCCL) per forward",
                            max_abs_vs_one_gpu=dict(o=e_s_o, ht=e_s_s)),
@@ -483,10 +498,11 @@ def run_gpu_arm(steps, warmup, n_gpus, kernels_only=False):
         e_o = (o2.float() - o1[:, tsl].float()).abs().max().item()
         e_h = (h2 - h1).abs().max().item() if h2 is not None else 0.0
         res = max_over_ranks([ms_sp, t_one, e_o, e_h] + [v for _, v in ph])
+        sp_names, sp_vals, sp_parts = merge_exchange_marks([n for n, _ in ph], res[4:])
         seq_parallel = dict(workload="KDA fwd B=1 T=%d H=%d, %d contiguous segments of %d tokens" % (SP_T, SP_H, world, Ll),
                             ms=res[0], tokens_per_s=SP_T / (res[0] * 1e-3), one_gpu_ms=res[1],
                             speedup_over_one_gpu=res[1] / res[0], exchange=plan.mode, exchange_transport=plan.exchange_kind, sub_segments_per_rank=plan.sub,
-                            timeline_us={n: v * 1e3 for (n, _), v in zip(ph, res[4:])},
+                            timeline_us={n: v * 1e3 for n, v in zip(sp_names, sp_vals)}, exchange_parts_us=sp_parts,
                             max_abs_vs_one_gpu=dict(o=res[2], ht=res[3]), o_bound=O_TOL, ht_bound=HT_TOL)
         plan.close()
         del plan, dl, o1, h1, o2, h2

@@ -158,11 +158,11 @@ kda_state_fold_kernel(const FoldParams p) {
     if (p.final_out != nullptr) p.final_out[static_cast<size_t>(chain) * p.final_stride + static_cast<size_t>(r0 + r) * D + t] = s[r];
   }
   if (p.n_signal > 0) {
-    // every thread's stores to the peers are ordered before the flags: fence, count this CTA, and the
-    // last CTA of the grid raises them
-    __threadfence_system();
+    // the stores to the peers are ordered before the flags: CTA barrier, device-scope fence and count per
+    // CTA; the CTA that counts last has observed them all and raises the flags behind one system-scope fence
     __syncthreads();
     if (t == 0) {
+      __threadfence();
       const int done = atomicAdd(p.counter, 1);
       __threadfence();
       if (done == static_cast<int>(gridDim.x) - 1) {

@@ -135,6 +135,7 @@ struct PeerPushParams {
   int* flag[MAX_PEERS];    // raised to `epoch` on rank d once the slice has been stored
   int* counter;                // local int[world], zero between launches
   int world, epoch;
+  int ctas_per_dst;            // set by the launcher
 };
 cudaError_t launch_peer_push(const PeerPushParams& p, cudaStream_t stream);
 cudaError_t launch_flag_wait(const int* flags, int n, int epoch, int* status, cudaStream_t stream);

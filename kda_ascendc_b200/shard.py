@@ -174,7 +174,8 @@ def exchange_mode(chains: int, world: int, requested: str = "auto") -> str:
 
 def exchange_and_fold(mq_local: torch.Tensor, h0: Optional[torch.Tensor], rank: int, world: int, *, group=None,
                       mode: str = "a2a", sub: int = 1, two_level: Optional[bool] = None, walk=None,
-                      bufs: Optional[dict] = None, want_final: bool = False, status: Optional[torch.Tensor] = None):
+                      bufs: Optional[dict] = None, want_final: bool = False, status: Optional[torch.Tensor] = None,
+                      mark=None):
     """From this rank's transforms to the entry states of its segment(s).
 
     ``mq_local``: ``[sub * chains, 2, 128, 128]`` -- ``sub`` consecutive sub-segments of this rank
@@ -244,7 +245,7 @@ def exchange_and_fold(mq_local: torch.Tensor, h0: Optional[torch.Tensor], rank: 
         h0_own = None if h0c is None else h0c[rank * hp:(rank + 1) * hp]
         peer = bufs.get("peer")
         if peer is not None:                                   # stores and flags over peer memory, three launches
-            entry, last = peer.run(rank_mq.contiguous(), h0_own, status, want_final)
+            entry, last = peer.run(rank_mq.contiguous(), h0_own, status, want_final, mark=mark)
         else:
             recv = buf("recv_mq", (world, hp, 2, D, D))        # [segment][my chains]
             dist.all_to_all_single(recv, rank_mq.view(world, hp, 2, D, D), group=group)
@@ -420,7 +421,8 @@ class _PeerExchange:
         want = (100.0 * torch.arange(world, device=self.dev, dtype=torch.float32).view(world, 1) + rank + 1.0).expand(world, 4)
         return int(bool(torch.equal(got, want)))
 
-    def run(self, rank_mq: torch.Tensor, h0: Optional[torch.Tensor], status: Optional[torch.Tensor], want_final: bool):
+    def run(self, rank_mq: torch.Tensor, h0: Optional[torch.Tensor], status: Optional[torch.Tensor], want_final: bool,
+            mark=None):
         """``rank_mq``: this rank's transforms ``[chains, 2, 128, 128]`` (contiguous); ``h0``: the state before the
         first segment of this rank's OWN chains ``[hp, 128, 128]`` or None.  Returns the entry states of this
         rank's segment for all chains ``[chains, 128, 128]`` (the plan's buffer) and, with ``want_final``, the
@@ -444,7 +446,11 @@ class _PeerExchange:
         with torch.cuda.device(self.dev):
             stream = api._stream_handle()
             api._check(lib.kda_peer_push(ctypes.byref(push), stream))
+            if mark is not None:
+                mark("exchange_push")
             api._check(lib.kda_state_fold_peer(ctypes.byref(f), ctypes.byref(pa), stream))
+            if mark is not None:
+                mark("exchange_walk")
             api._check(lib.kda_flag_wait(self._wait_flags, self.world, self.epoch, st_ptr, stream))
         return self.ent.view(self.world * self.hp, D, D), (self.final if want_final else None)
 
@@ -599,7 +605,8 @@ class SeqParallelPlan:
         mq = seg.transforms()
         mark("transforms")
         entry, final = exchange_and_fold(mq, self.h0, self.rank, self.world, group=self.group, mode=self.mode,
-                                         sub=self.sub, bufs=self.bufs, want_final=self.want_final, status=seg.ws)
+                                         sub=self.sub, bufs=self.bufs, want_final=self.want_final, status=seg.ws,
+                                         mark=mark if timeline is not None else None)
         mark("exchange_fold")
         o, ht = seg.outputs(entry.reshape(seg.B, seg.H, D, D))
         mark("k2")
