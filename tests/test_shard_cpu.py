@@ -131,6 +131,45 @@ def test_sequence_split_over_four_gloo_ranks_two_levels():
             assert eh <= 2e-5 * max(1.0, hmax), (r, key, eh)
 
 
+@pytest.mark.parametrize("world,hp", [(2, 3), (4, 8), (8, 4), (8, 2)])
+def test_peer_exchange_argument_blocks(world, hp):
+    """The pointer arithmetic of the peer exchange for up to eight ranks, on CPU tensors (nothing is launched):
+    every rank's push targets slot [rank] of each owner's receive buffer and flag row, its walk writes slot
+    [rank] of each segment owner's entry buffer and entry-flag row, all inside the owners' blocks."""
+    chains = world * hp
+    n_recv, n_ent = chains * 2 * D * D, chains * D * D
+    ranks = []
+    for r in range(world):
+        pe = shard._PeerExchange()
+        pe.world, pe.rank, pe.hp, pe.dev = world, r, hp, torch.device("cpu")
+        pe.block = torch.zeros(n_recv + n_ent + shard._PeerExchange.FLAG_WORDS, dtype=torch.float32)
+        pe.recv = pe.block[:n_recv].view(world, hp, 2, D, D)
+        pe.ent = pe.block[n_recv:n_recv + n_ent].view(world, hp, D, D)
+        pe.flag_off = n_recv + n_ent
+        pe.flags = pe.block[pe.flag_off:].view(torch.int32)
+        pe.counters = torch.zeros(world + 1, dtype=torch.int32)
+        pe.final = torch.empty((hp, D, D), dtype=torch.float32)
+        ranks.append(pe)
+    for pe in ranks:
+        pe.peer_ptr = [q.block.data_ptr() for q in ranks]
+        pe._build_args()
+    assert 2 * world <= 32 and 32 + 4 * world <= shard._PeerExchange.FLAG_WORDS      # flag rows and self-check words fit
+    for pe in ranks:
+        r = pe.rank
+        assert pe._push.world == world and pe._push.slice_floats == hp * 2 * D * D
+        assert pe._push.dst_offset_floats == r * hp * 2 * D * D
+        assert pe._fold.mq == pe.recv.data_ptr() and pe._fold.n_chains == hp and pe._fold.n_seg == world
+        assert pe._peer.wait_flags == pe.flags.data_ptr() and pe._peer.n_wait == world and pe._peer.n_signal == world
+        assert pe._wait_flags == pe.flags[world:].data_ptr()
+        for d, q in enumerate(ranks):
+            assert pe._push.dst[d] == q.recv.data_ptr()
+            assert pe._push.dst[d] + 4 * pe._push.dst_offset_floats == q.recv[r].data_ptr()       # slot [source rank]
+            assert pe._push.flag[d] == q.flags[r:].data_ptr()
+            assert pe._peer.s_in_seg[d] == q.ent[r].data_ptr()                                   # slot [owner of the chains]
+            assert pe._peer.signal[d] == q.flags[world + r:].data_ptr()
+        assert pe._peer.s_in_seg[world] is None
+
+
 def test_exchange_mode_choice():
     assert shard.exchange_mode(32, 8) == "a2a" and shard.exchange_mode(16, 8) == "a2a"
     assert shard.exchange_mode(5, 4) == "gather" and shard.exchange_mode(32, 8, "gather") == "gather"
