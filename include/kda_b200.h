@@ -43,6 +43,7 @@ extern "C" {
 #define KDA_ERR_INVALID_ARG (-1)
 #define KDA_ERR_CUDA (-2)
 #define KDA_ERR_DEVICE_STATUS (-3)
+#define KDA_ERR_UNSUPPORTED (-4)   /* the call is valid but this entry point has no kernel for it */
 
 #define KDA_G_FP32 0
 #define KDA_G_BF16 1
@@ -190,6 +191,14 @@ typedef struct KdaPeerPushArgs {
   int32_t world, epoch;
 } KdaPeerPushArgs;
 int kda_peer_push(const KdaPeerPushArgs* args, void* stream);
+
+/* kda_fwd_k2_state_push: kda_fwd_k2_state(args, 2, stream) and kda_peer_push in ONE launch -- the
+ * transform-pair pass writes the (M, Q) tiles of chain c straight into rank (c / hp)'s buffer,
+ * push->dst[c / hp] + dst_offset_floats + (c % hp) * 2 * 128 * 128 with hp = slice_floats / (2 * 128 * 128)
+ * = chains / world, and raises push->flag[d] when destination d is complete; args->ht and push->src are
+ * not used.  Only the 8-row pair form does this: KDA_ERR_UNSUPPORTED when the problem has more chains
+ * than that form takes (the caller then runs the two calls separately). */
+int kda_fwd_k2_state_push(const KdaFwdArgs* args, const KdaPeerPushArgs* push, void* stream);
 
 /* kda_state_fold_peer: kda_state_fold_ex on transforms that peers have stored into args->mq.  The
  * walk starts when the n_wait flags at wait_flags have reached epoch; the state before segment j

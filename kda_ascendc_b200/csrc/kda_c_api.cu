@@ -214,7 +214,7 @@ int do_k1(const KdaFwdArgs* a, cudaStream_t st) {
   return KDA_OK;
 }
 
-int do_k2(const KdaFwdArgs* a, bool state_only, int zero_u, cudaStream_t st) {
+int do_k2(const KdaFwdArgs* a, bool state_only, int zero_u, cudaStream_t st, const KdaPeerPushArgs* push = nullptr) {
   kda::K2Params p;
   memset(&p, 0, sizeof(p));
   p.rec = rec_ptr(a);
@@ -245,7 +245,22 @@ int do_k2(const KdaFwdArgs* a, bool state_only, int zero_u, cudaStream_t st) {
     const long long bh = static_cast<long long>(a->n_seqs > 0 ? a->n_seqs : a->B) * a->H;
     if (2 * bh > 0x3fffffffLL) return fail(KDA_ERR_INVALID_ARG, "kda: too many chains%s", "");
     cudaError_t pe;
-    if (a->k2_variant == 0 && a->k2_vsplit == 0 && 2 * bh * 4 <= sms) {
+    if (push != nullptr) {
+      // the tiles go straight into the owners' receive buffers: only the 8-row pair form does that
+      if (!(variant == 1 || variant == 5))
+        return fail(KDA_ERR_UNSUPPORTED, "kda: the fused push needs the 8-row pair form%s (too many chains: %lld)", "", bh);
+      const long long hp = push->slice_floats / (2LL * kda::D * kda::D);
+      if (hp <= 0 || hp * push->world != bh || push->slice_floats % (2LL * kda::D * kda::D) != 0)
+        return fail(KDA_ERR_INVALID_ARG, "kda: slice_floats must be chains / world whole (M, Q) pairs%s (chains %lld)", "", bh);
+      p.push_on = 1;
+      p.push_hp = static_cast<int>(hp);
+      p.push_epoch = push->epoch;
+      p.push_dst_offset = push->dst_offset_floats;
+      p.push_counter = push->counter;
+      for (int d = 0; d < push->world; ++d) { p.push_dst[d] = push->dst[d]; p.push_flag[d] = push->flag[d]; }
+      p.pair_mode = 0;
+      pe = kda::launch_k2n_pair(p, vsplit, st);
+    } else if (a->k2_variant == 0 && a->k2_vsplit == 0 && 2 * bh * 4 <= sms) {
       p.n_chains = static_cast<int>(2 * bh);
       pe = kda::launch_k2n(p, 2 * bh * 16 <= sms ? 16 : 2 * bh * 8 <= sms ? 8 : 4, 1, true, st);
     } else if (variant == 1 || variant == 5) {
@@ -463,6 +478,27 @@ int kda_state_fold_ex(const KdaFoldArgs* f, void* stream) { return fold_impl(f, 
 int kda_state_fold_peer(const KdaFoldArgs* f, const KdaFoldPeerArgs* peer, void* stream) {
   if (peer == nullptr) return fail(KDA_ERR_INVALID_ARG, "kda: peer args is NULL%s", "");
   return fold_impl(f, peer, stream);
+}
+
+static int check_push_targets(const KdaPeerPushArgs* a) {
+  if (a == nullptr) return fail(KDA_ERR_INVALID_ARG, "kda: push args is NULL%s", "");
+  if (a->world < 1 || a->world > KDA_MAX_PEERS || a->epoch <= 0)
+    return fail(KDA_ERR_INVALID_ARG, "kda: the push needs 1..16 ranks and a positive epoch%s (world %lld)", "", a->world);
+  if (a->counter == nullptr || a->slice_floats <= 0 || a->slice_floats % 4 != 0 || a->dst_offset_floats < 0 ||
+      a->dst_offset_floats % 4 != 0)
+    return fail(KDA_ERR_INVALID_ARG, "kda: the push needs a counter and 16-byte multiples for slice and offset%s", "");
+  for (int d = 0; d < a->world; ++d)
+    if (a->dst[d] == nullptr || a->flag[d] == nullptr || reinterpret_cast<uintptr_t>(a->dst[d]) % 16 != 0)
+      return fail(KDA_ERR_INVALID_ARG, "kda: dst[%s%lld] and its flag must be set, dst 16-byte aligned", "", d);
+  return KDA_OK;
+}
+
+int kda_fwd_k2_state_push(const KdaFwdArgs* a, const KdaPeerPushArgs* push, void* stream) {
+  g_launches = 0;
+  if (int rc = check_common(a)) return rc;
+  if (int rc = check_k2(a, true)) return rc;
+  if (int rc = check_push_targets(push)) return rc;
+  return do_k2(a, true, 2, static_cast<cudaStream_t>(stream), push);
 }
 
 int kda_peer_push(const KdaPeerPushArgs* a, void* stream) {

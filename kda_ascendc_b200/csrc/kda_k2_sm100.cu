@@ -352,8 +352,10 @@ __global__ void __launch_bounds__((CW + 1) * 32, 1) kda_k2_kernel(const K2Params
       }
     }
 
-    if (!failed && p.ht != nullptr) {
-      float* ht = p.ht + static_cast<size_t>(PAIR ? 2 * bh : chain) * D * D;
+    if (!failed && (p.ht != nullptr || (PAIR && p.push_on))) {
+      float* ht = (PAIR && p.push_on)
+                      ? p.push_dst[bh / p.push_hp] + p.push_dst_offset + static_cast<size_t>(2 * (bh % p.push_hp)) * D * D
+                      : p.ht + static_cast<size_t>(PAIR ? 2 * bh : chain) * D * D;
 #pragma unroll
       for (int m = 0; m < 8; ++m)
 #pragma unroll
@@ -367,6 +369,19 @@ __global__ void __launch_bounds__((CW + 1) * 32, 1) kda_k2_kernel(const K2Params
   }
 
   __syncthreads();
+  if (PAIR && p.push_on && tid == 0 && *sAbort == 0) {
+    // the tiles went into another rank's receive buffer: the CTA barrier has put every warp's stores before
+    // this count; the CTA that counts last for a destination raises its flag behind one system-scope fence
+    const int owner = bh / p.push_hp;
+    __threadfence();
+    const int done = atomicAdd(p.push_counter + owner, 1);
+    __threadfence();
+    if (done == p.push_ctas_per_dst - 1) {
+      p.push_counter[owner] = 0;
+      __threadfence_system();
+      st_release_sys(p.push_flag[owner], p.push_epoch);
+    }
+  }
   if (*sAbort != 0 && tid == 0) {
     // give copies that are still in flight a bounded chance to land before the CTA's
     // shared memory is released
@@ -407,8 +422,10 @@ cudaError_t launch_k2n(const K2Params& p, int vsplit, int ntile, bool state_only
   return cudaErrorInvalidValue;
 }
 
-cudaError_t launch_k2n_pair(const K2Params& p, int vsplit, cudaStream_t stream) {
+cudaError_t launch_k2n_pair(const K2Params& p0, int vsplit, cudaStream_t stream) {
   // the transform-pair pass: two recurrences over the same eight rows per warp, 16 / vsplit consumer warps per CTA
+  K2Params p = p0;
+  p.push_ctas_per_dst = p.push_hp * vsplit;   // vsplit CTAs share a chain
   switch (vsplit) {
     case 4: return launch_k2_t<4, 2, true, true>(p, stream);
     case 8: return launch_k2_t<2, 2, true, true>(p, stream);

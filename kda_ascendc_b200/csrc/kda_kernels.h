@@ -51,6 +51,8 @@ struct K1Params {
   FastDiv div_g;   // divides by H / Hq
 };
 
+constexpr int MAX_PEERS = 16;   // = KDA_MAX_PEERS of the public header
+
 struct K2Params {
   const uint8_t* rec;
   const float* h0;   // [B,H,128,128] or null
@@ -72,6 +74,15 @@ struct K2Params {
   int n_seqs;
   // a launch may cover a sub-range of the (batch, head) chains: first chain and count (0 = all)
   int chain0, n_chains;
+  // Transform-pair pass of a sequence split over peer memory (the 8-row pair form only): the (M, Q) tiles
+  // of chain c go straight into the receive buffer of the rank that owns the chain,
+  // push_dst[c / push_hp] + push_dst_offset + (c % push_hp) * 2 * 128 * 128, instead of ht, and the CTA that
+  // completes a destination raises its flag (as kda_peer_push_kernel does).
+  int push_on, push_hp, push_epoch, push_ctas_per_dst;
+  long long push_dst_offset;
+  float* push_dst[MAX_PEERS];
+  int* push_flag[MAX_PEERS];
+  int* push_counter;
 };
 
 cudaError_t launch_k1(const K1Params& p, bool g_bf16, bool fast_exp, cudaStream_t stream);
@@ -99,8 +110,6 @@ cudaError_t launch_k2n_pair(const K2Params& p, int vsplit, cudaStream_t stream);
 cudaError_t launch_k2t(const K2Params& p, long long n_records, cudaStream_t stream);
 
 // Walk of the per-segment affine state transforms of a sequence split (kda_fold_sm100.cu).
-constexpr int MAX_PEERS = 16;   // = KDA_MAX_PEERS of the public header
-
 struct FoldParams {
   const float* mq;             // M_j[c] at mq + j*seg_stride + c*chain_stride (floats), Q_j[c] 128*128 floats behind it
   long long seg_stride, chain_stride;

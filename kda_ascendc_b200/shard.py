@@ -175,7 +175,7 @@ def exchange_mode(chains: int, world: int, requested: str = "auto") -> str:
 def exchange_and_fold(mq_local: torch.Tensor, h0: Optional[torch.Tensor], rank: int, world: int, *, group=None,
                       mode: str = "a2a", sub: int = 1, two_level: Optional[bool] = None, walk=None,
                       bufs: Optional[dict] = None, want_final: bool = False, status: Optional[torch.Tensor] = None,
-                      mark=None):
+                      mark=None, pushed: bool = False):
     """From this rank's transforms to the entry states of its segment(s).
 
     ``mq_local``: ``[sub * chains, 2, 128, 128]`` -- ``sub`` consecutive sub-segments of this rank
@@ -245,7 +245,8 @@ def exchange_and_fold(mq_local: torch.Tensor, h0: Optional[torch.Tensor], rank: 
         h0_own = None if h0c is None else h0c[rank * hp:(rank + 1) * hp]
         peer = bufs.get("peer")
         if peer is not None:                                   # stores and flags over peer memory, three launches
-            entry, last = peer.run(rank_mq.contiguous(), h0_own, status, want_final, mark=mark)
+            entry, last = peer.run(None if pushed else rank_mq.contiguous(), h0_own, status, want_final, mark=mark,
+                                   pushed=pushed)
         else:
             recv = buf("recv_mq", (world, hp, 2, D, D))        # [segment][my chains]
             dist.all_to_all_single(recv, rank_mq.view(world, hp, 2, D, D), group=group)
@@ -421,18 +422,26 @@ class _PeerExchange:
         want = (100.0 * torch.arange(world, device=self.dev, dtype=torch.float32).view(world, 1) + rank + 1.0).expand(world, 4)
         return int(bool(torch.equal(got, want)))
 
-    def run(self, rank_mq: torch.Tensor, h0: Optional[torch.Tensor], status: Optional[torch.Tensor], want_final: bool,
-            mark=None):
+    def begin(self):
+        """Starts a run whose push is done by the transform-pair pass itself (``kda_fwd_k2_state_push``): returns the
+        push block with the new run number; :meth:`run` must follow with ``pushed=True``."""
+        self.epoch += 1
+        self._push.src, self._push.epoch = None, self.epoch
+        return self._push
+
+    def run(self, rank_mq: Optional[torch.Tensor], h0: Optional[torch.Tensor], status: Optional[torch.Tensor], want_final: bool,
+            mark=None, pushed: bool = False):
         """``rank_mq``: this rank's transforms ``[chains, 2, 128, 128]`` (contiguous); ``h0``: the state before the
         first segment of this rank's OWN chains ``[hp, 128, 128]`` or None.  Returns the entry states of this
         rank's segment for all chains ``[chains, 128, 128]`` (the plan's buffer) and, with ``want_final``, the
         state after the last segment of the own chains ``[hp, 128, 128]``."""
         lib = _lib.load()
-        if not rank_mq.is_contiguous() or rank_mq.dtype != torch.float32:
-            raise ValueError("rank_mq must be a contiguous fp32 tensor")
-        self.epoch += 1
         push, f, pa = self._push, self._fold, self._peer
-        push.src, push.epoch = rank_mq.data_ptr(), self.epoch
+        if not pushed:
+            if not rank_mq.is_contiguous() or rank_mq.dtype != torch.float32:
+                raise ValueError("rank_mq must be a contiguous fp32 tensor")
+            self.epoch += 1
+            push.src, push.epoch = rank_mq.data_ptr(), self.epoch
         if h0 is not None:
             if h0.dtype != torch.float32 or h0.stride()[-2:] != (D, 1):
                 raise ValueError("h0 must be fp32 with dense 128 x 128 blocks")
@@ -445,7 +454,8 @@ class _PeerExchange:
         pa.s_in_seg[self.world] = self.final.data_ptr() if want_final else None
         with torch.cuda.device(self.dev):
             stream = api._stream_handle()
-            api._check(lib.kda_peer_push(ctypes.byref(push), stream))
+            if not pushed:
+                api._check(lib.kda_peer_push(ctypes.byref(push), stream))
             if mark is not None:
                 mark("exchange_push")
             api._check(lib.kda_state_fold_peer(ctypes.byref(f), ctypes.byref(pa), stream))
@@ -499,6 +509,14 @@ class _Segment:
             api._check(self.lib.kda_fwd_k2_state(ctypes.byref(self.args_mq), 2,
                                                  api._stream_handle() if stream is None else stream))
         return self.mq
+
+    def transforms_push(self, push, stream=None) -> int:
+        """The transform pass with its tiles stored straight into the owners' receive buffers
+        (``kda_fwd_k2_state_push``); returns the library's code (``ERR_UNSUPPORTED``: no such kernel for this
+        problem, nothing was launched)."""
+        with torch.cuda.device(self.dev):
+            return self.lib.kda_fwd_k2_state_push(ctypes.byref(self.args_mq), ctypes.byref(push),
+                                                  api._stream_handle() if stream is None else stream)
 
     def outputs(self, S_in, stream=None):
         """Ordinary K2 pass from the true entry state: (o, state after the segment)."""
@@ -568,6 +586,7 @@ class SeqParallelPlan:
         # The all-to-all runs over peer memory when the ranks can map each other's buffers (one box);
         # every rank takes the same decision (the set-up is collective), else the NCCL collectives.
         self.exchange_kind = "nccl"
+        self._fused_push = os.environ.get("KDA_B200_FUSED_PUSH", "1") != "0"
         want_peer = peer_exchange is True or (peer_exchange == "auto" and os.environ.get("KDA_B200_PEER_EXCHANGE", "1") != "0")
         if self.world > 1 and self.mode == "a2a" and want_peer and q.is_cuda:
             peer = _PeerExchange.create(self.chains, self.world, self.rank, group, q.device)
@@ -602,11 +621,23 @@ class SeqParallelPlan:
             o, ht = seg.outputs(self.h0)
             mark("k2")
             return o, ht
-        mq = seg.transforms()
+        # One segment per rank over peer memory: the transform pass stores its tiles straight into the owners'
+        # receive buffers (no copy kernel), where the library has a kernel for that (the 8-row pair form).
+        peer = self.bufs.get("peer")
+        pushed = False
+        if peer is not None and self.sub == 1 and self._fused_push:
+            rc = seg.transforms_push(peer.begin())
+            if rc == _lib.ERR_UNSUPPORTED:          # the same answer on every rank: same shapes
+                self._fused_push = False
+                peer.epoch -= 1
+            else:
+                api._check(rc)
+                pushed = True
+        mq = seg.mq if pushed else seg.transforms()
         mark("transforms")
         entry, final = exchange_and_fold(mq, self.h0, self.rank, self.world, group=self.group, mode=self.mode,
                                          sub=self.sub, bufs=self.bufs, want_final=self.want_final, status=seg.ws,
-                                         mark=mark if timeline is not None else None)
+                                         mark=mark if timeline is not None else None, pushed=pushed)
         mark("exchange_fold")
         o, ht = seg.outputs(entry.reshape(seg.B, seg.H, D, D))
         mark("k2")

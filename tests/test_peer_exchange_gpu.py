@@ -81,6 +81,43 @@ def test_push_walk_and_flags_between_two_emulated_ranks(cuda_device):
             assert pe.counters.tolist() == [0] * (world + 1)                                  # left zeroed for the next run
 
 
+def test_transform_pass_that_pushes_its_own_tiles(cuda_device):
+    """kda_fwd_k2_state_push: the transform-pair pass stores (M, Q) straight into the owners' receive buffers
+    and raises their flags -- the same bits as the plain pass followed by kda_peer_push."""
+    from kda_ascendc_b200 import _lib, api, shard
+    from oracle import kda_oracle as O
+
+    dev = cuda_device
+    world, hp, L = 2, 2, 64
+    H = world * hp
+    inp = O.make_inputs(1, world * L, H, seed0=4, regime="carry", h0_std=0.1)
+    d = {k: (v.to(dev) if torch.is_tensor(v) else v) for k, v in inp.items()}
+    ranks = _rank_objects(world, hp, dev)
+    segs = []
+    for r in range(world):
+        sl = slice(r * L, (r + 1) * L)
+        seg = shard._Segment(d["q"][:, sl], d["k"][:, sl], d["v"][:, sl], d["g"][:, sl], d["beta"][:, sl], d["scale"],
+                             d["lower_bound"], d["A_log"], d["dt_bias"])
+        seg.k1()
+        segs.append(seg)
+    for epoch in (1, 2):
+        for pe, seg in zip(ranks, segs):
+            pe.recv.fill_(float("nan"))
+        for pe, seg in zip(ranks, segs):
+            push = pe.begin()
+            assert push.epoch == epoch
+            assert seg.transforms_push(push) == 0, _lib.last_error()
+        torch.cuda.synchronize()
+        for r, seg in enumerate(segs):
+            mq = seg.transforms().clone()                   # the plain pass: [chains, 2, 128, 128]
+            torch.cuda.synchronize()
+            for dst, pe in enumerate(ranks):
+                assert torch.equal(pe.recv[r], mq[dst * hp:(dst + 1) * hp])
+        for pe in ranks:
+            assert pe.flags[:world].tolist() == [epoch] * world and pe.counters.tolist() == [0] * (world + 1)
+            assert api.check_device_status(segs[0].ws) == 0
+
+
 def test_a_flag_that_never_comes_ends_in_a_status_code(cuda_device):
     import kda_ascendc_b200 as K
     from kda_ascendc_b200 import _lib, api
