@@ -215,6 +215,12 @@ typedef struct KdaFoldPeerArgs {
 } KdaFoldPeerArgs;
 int kda_state_fold_peer(const KdaFoldArgs* args, const KdaFoldPeerArgs* peer, void* stream);
 
+/* kda_fwd_k2_after_flags: kda_fwd_k2 whose entry state args->h0 is stored by other GPUs -- the kernel itself
+ * waits (bounded, status code 7) until the n flags have reached epoch before it reads h0, while it
+ * already loads the first records: kda_flag_wait + kda_fwd_k2 in one launch.  The 8-row and 16-row
+ * forms do this; KDA_ERR_UNSUPPORTED for problems that run in the tensor-memory form. */
+int kda_fwd_k2_after_flags(const KdaFwdArgs* args, const int32_t* flags, int32_t n, int32_t epoch, void* stream);
+
 /* kda_peer_enable: lets kernels of the current device load from and store to memory of GPU
  * peer_device that this process has mapped (cudaDeviceEnablePeerAccess; already enabled is fine).
  * KDA_ERR_CUDA when the two GPUs have no peer path.  Call it once per peer before the first

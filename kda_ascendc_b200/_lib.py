@@ -17,7 +17,7 @@ FLAG_GATE, FLAG_L2NORM, FLAG_BETA_SIGMOID, FLAG_STATE_K_FIRST = 1, 2, 4, 8
 EXPORTS = (
     "kda_fwd_workspace_bytes", "kda_fwd", "kda_fwd_k1", "kda_fwd_k2", "kda_fwd_k2_state", "kda_recurrent_fwd",
     "kda_varlen_fill_tables", "kda_selftest_bounded_wait", "kda_fwd_static_scratch",
-    "kda_fwd_static_scratch_status", "kda_state_fold", "kda_state_fold_ex", "kda_state_fold_peer", "kda_peer_push", "kda_fwd_k2_state_push",
+    "kda_fwd_static_scratch_status", "kda_state_fold", "kda_state_fold_ex", "kda_state_fold_peer", "kda_peer_push", "kda_fwd_k2_state_push", "kda_fwd_k2_after_flags",
     "kda_flag_wait", "kda_peer_enable", "kda_ipc_export", "kda_ipc_open", "kda_ipc_close",
     "kda_fwd_status", "kda_fwd_k2_choice", "kda_last_launch_count", "kda_last_error", "kda_version",
 )
@@ -99,6 +99,8 @@ def load() -> ctypes.CDLL:
     lib.kda_state_fold_peer.argtypes = [ctypes.POINTER(KdaFoldArgs), ctypes.POINTER(KdaFoldPeerArgs), ctypes.c_void_p]
     lib.kda_fwd_k2_state_push.restype = ctypes.c_int
     lib.kda_fwd_k2_state_push.argtypes = [ctypes.POINTER(KdaFwdArgs), ctypes.POINTER(KdaPeerPushArgs), ctypes.c_void_p]
+    lib.kda_fwd_k2_after_flags.restype = ctypes.c_int
+    lib.kda_fwd_k2_after_flags.argtypes = [ctypes.POINTER(KdaFwdArgs), ctypes.c_void_p, ctypes.c_int32, ctypes.c_int32, ctypes.c_void_p]
     lib.kda_peer_push.restype = ctypes.c_int
     lib.kda_peer_push.argtypes = [ctypes.POINTER(KdaPeerPushArgs), ctypes.c_void_p]
     lib.kda_peer_enable.restype = ctypes.c_int

@@ -214,7 +214,10 @@ int do_k1(const KdaFwdArgs* a, cudaStream_t st) {
   return KDA_OK;
 }
 
-int do_k2(const KdaFwdArgs* a, bool state_only, int zero_u, cudaStream_t st, const KdaPeerPushArgs* push = nullptr) {
+struct H0Flags { const int32_t* flags; int n, epoch; };
+
+int do_k2(const KdaFwdArgs* a, bool state_only, int zero_u, cudaStream_t st, const KdaPeerPushArgs* push = nullptr,
+          const H0Flags* h0f = nullptr) {
   kda::K2Params p;
   memset(&p, 0, sizeof(p));
   p.rec = rec_ptr(a);
@@ -274,6 +277,13 @@ int do_k2(const KdaFwdArgs* a, bool state_only, int zero_u, cudaStream_t st, con
     if (pe != cudaSuccess) return fail(KDA_ERR_CUDA, "kda: K2 (transform pair) launch failed: %s", cudaGetErrorString(pe));
     ++g_launches;
     return KDA_OK;
+  }
+  if (h0f != nullptr) {
+    // the entry state is stored by other GPUs: the kernels that can wait for it themselves are the 8-row and
+    // the 16-row form
+    if (!(variant == 1 || variant == 3))
+      return fail(KDA_ERR_UNSUPPORTED, "kda: this K2 form cannot wait for the entry state%s (variant %lld)", "", variant);
+    p.h0_flags = h0f->flags; p.h0_n_flags = h0f->n; p.h0_epoch = h0f->epoch;
   }
   cudaError_t e;
   if (variant == 4) {
@@ -499,6 +509,16 @@ int kda_fwd_k2_state_push(const KdaFwdArgs* a, const KdaPeerPushArgs* push, void
   if (int rc = check_k2(a, true)) return rc;
   if (int rc = check_push_targets(push)) return rc;
   return do_k2(a, true, 2, static_cast<cudaStream_t>(stream), push);
+}
+
+int kda_fwd_k2_after_flags(const KdaFwdArgs* a, const int32_t* flags, int32_t n, int32_t epoch, void* stream) {
+  g_launches = 0;
+  if (int rc = check_common(a)) return rc;
+  if (int rc = check_k2(a, false)) return rc;
+  if (flags == nullptr || n < 1 || n > KDA_MAX_PEERS || epoch <= 0 || a->h0 == nullptr)
+    return fail(KDA_ERR_INVALID_ARG, "kda: the call needs h0, 1..16 flags and a positive epoch%s (n %lld)", "", n);
+  const H0Flags h0f{flags, n, epoch};
+  return do_k2(a, false, 0, static_cast<cudaStream_t>(stream), nullptr, &h0f);
 }
 
 int kda_peer_push(const KdaPeerPushArgs* a, void* stream) {

@@ -132,6 +132,7 @@ __global__ void __launch_bounds__((CW + 1) * 32, 1) kda_k2_kernel(const K2Params
     const int v0 = vs * VCOLS + warp * (RT * 8);   // first state row of this warp
     // hT[m][nv][e]: k = 16m + gq (+8 for e >= 2), v = v0 + 8nv + 2tq + (e & 1)   (PAIR: v = v0 + 2tq + (e & 1))
     float hT[8][NVT][4];
+    bool h0_ok = true;
     if (PAIR) {
 #pragma unroll
       for (int m = 0; m < 8; ++m)
@@ -149,6 +150,12 @@ __global__ void __launch_bounds__((CW + 1) * 32, 1) kda_k2_kernel(const K2Params
           for (int e = 0; e < 4; ++e)
             hT[m][nv][e] = (plane == 0 && (v0 + nv * 8 + tq * 2 + (e & 1)) == (m * 16 + gq + (e >> 1) * 8)) ? 1.f : 0.f;
     } else if (p.h0 != nullptr) {
+      if (p.h0_n_flags > 0) {   // the entry state comes from other GPUs: wait for their flags (the producer warp is already loading records)
+        int ok = 1;
+        if (lane == 0)
+          for (int i = 0; i < p.h0_n_flags; ++i) ok &= flag_wait_bounded(p.h0_flags + i, p.h0_epoch) ? 1 : 0;
+        h0_ok = __shfl_sync(0xffffffffu, ok, 0) != 0;
+      }
       const float* h0 = p.h0 + static_cast<size_t>(bh) * D * D;
 #pragma unroll
       for (int m = 0; m < 8; ++m)
@@ -185,7 +192,10 @@ __global__ void __launch_bounds__((CW + 1) * 32, 1) kda_k2_kernel(const K2Params
     float oa[NVT][4];                // output tile of the previous step, stored one step late
 
     bool failed = false;
-    if (!__all_sync(0xffffffffu, mbar_wait_bounded(full0, 0, sAbort))) {
+    if (!h0_ok) {
+      if (*sAbort == 0) { *sAbort = 1; atomicExch(p.status, ST_PEER_TIMEOUT); }
+      failed = true;
+    } else if (!__all_sync(0xffffffffu, mbar_wait_bounded(full0, 0, sAbort))) {
       if (*sAbort == 0) { *sAbort = 1; atomicExch(p.status, ST_K2_FULL_TIMEOUT); }
       failed = true;
     } else {

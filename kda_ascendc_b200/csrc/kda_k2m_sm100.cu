@@ -108,6 +108,7 @@ __global__ void __launch_bounds__((CW + 1) * 32, MINB) kda_k2m_kernel(const K2Pa
     const int vrow0 = (vs * CW + warp) * 16;
     // hs[nt][e]: v = vrow0 + gq (+8 for e >= 2), k = 8nt + 2tq + (e & 1)
     float hs[16][4];
+    bool h0_ok = true;
     if (pair) {
 #pragma unroll
       for (int nt = 0; nt < 16; ++nt)
@@ -115,6 +116,12 @@ __global__ void __launch_bounds__((CW + 1) * 32, MINB) kda_k2m_kernel(const K2Pa
         for (int e = 0; e < 4; ++e)
           hs[nt][e] = (plane == 0 && (vrow0 + gq + (e >> 1) * 8) == (nt * 8 + tq * 2 + (e & 1))) ? 1.f : 0.f;
     } else if (p.h0 != nullptr) {
+      if (p.h0_n_flags > 0) {   // the entry state comes from other GPUs: wait for their flags (the producer warp is already loading records)
+        int ok = 1;
+        if (lane == 0)
+          for (int i = 0; i < p.h0_n_flags; ++i) ok &= flag_wait_bounded(p.h0_flags + i, p.h0_epoch) ? 1 : 0;
+        h0_ok = __shfl_sync(0xffffffffu, ok, 0) != 0;
+      }
       const float* h0 = p.h0 + static_cast<size_t>(bh) * D * D;
 #pragma unroll
       for (int nt = 0; nt < 16; ++nt) {
@@ -171,7 +178,10 @@ __global__ void __launch_bounds__((CW + 1) * 32, MINB) kda_k2m_kernel(const K2Pa
     };
 
     bool failed = false;
-    if (!__all_sync(0xffffffffu, mbar_wait_bounded(full0, 0, sAbort))) {
+    if (!h0_ok) {
+      if (*sAbort == 0) { *sAbort = 1; atomicExch(p.status, ST_PEER_TIMEOUT); }
+      failed = true;
+    } else if (!__all_sync(0xffffffffu, mbar_wait_bounded(full0, 0, sAbort))) {
       if (*sAbort == 0) { *sAbort = 1; atomicExch(p.status, ST_K2_FULL_TIMEOUT); }
       failed = true;
     } else {

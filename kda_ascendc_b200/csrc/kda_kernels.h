@@ -83,6 +83,11 @@ struct K2Params {
   float* push_dst[MAX_PEERS];
   int* push_flag[MAX_PEERS];
   int* push_counter;
+  // Final pass of a sequence split over peer memory (the 8-row and 16-row forms): h0 is stored by other
+  // GPUs; the consumer warps read it once the h0_n_flags local flags have reached h0_epoch (bounded wait,
+  // status code 7), while the producer warp already streams the first records in.
+  const int* h0_flags;
+  int h0_n_flags, h0_epoch;
 };
 
 cudaError_t launch_k1(const K1Params& p, bool g_bf16, bool fast_exp, cudaStream_t stream);

@@ -175,7 +175,7 @@ def exchange_mode(chains: int, world: int, requested: str = "auto") -> str:
 def exchange_and_fold(mq_local: torch.Tensor, h0: Optional[torch.Tensor], rank: int, world: int, *, group=None,
                       mode: str = "a2a", sub: int = 1, two_level: Optional[bool] = None, walk=None,
                       bufs: Optional[dict] = None, want_final: bool = False, status: Optional[torch.Tensor] = None,
-                      mark=None, pushed: bool = False):
+                      mark=None, pushed: bool = False, defer_wait: bool = False):
     """From this rank's transforms to the entry states of its segment(s).
 
     ``mq_local``: ``[sub * chains, 2, 128, 128]`` -- ``sub`` consecutive sub-segments of this rank
@@ -246,7 +246,7 @@ def exchange_and_fold(mq_local: torch.Tensor, h0: Optional[torch.Tensor], rank: 
         peer = bufs.get("peer")
         if peer is not None:                                   # stores and flags over peer memory, three launches
             entry, last = peer.run(None if pushed else rank_mq.contiguous(), h0_own, status, want_final, mark=mark,
-                                   pushed=pushed)
+                                   pushed=pushed, defer_wait=defer_wait and sub == 1)
         else:
             recv = buf("recv_mq", (world, hp, 2, D, D))        # [segment][my chains]
             dist.all_to_all_single(recv, rank_mq.view(world, hp, 2, D, D), group=group)
@@ -294,6 +294,7 @@ class _PeerExchange:
 
     def __init__(self):
         self.epoch = 0
+        self.pending = None     # (flags, n, epoch) of entry states whose arrival nothing has waited for yet
 
     @classmethod
     def create(cls, chains: int, world: int, rank: int, group, device):
@@ -430,7 +431,7 @@ class _PeerExchange:
         return self._push
 
     def run(self, rank_mq: Optional[torch.Tensor], h0: Optional[torch.Tensor], status: Optional[torch.Tensor], want_final: bool,
-            mark=None, pushed: bool = False):
+            mark=None, pushed: bool = False, defer_wait: bool = False):
         """``rank_mq``: this rank's transforms ``[chains, 2, 128, 128]`` (contiguous); ``h0``: the state before the
         first segment of this rank's OWN chains ``[hp, 128, 128]`` or None.  Returns the entry states of this
         rank's segment for all chains ``[chains, 128, 128]`` (the plan's buffer) and, with ``want_final``, the
@@ -461,7 +462,11 @@ class _PeerExchange:
             api._check(lib.kda_state_fold_peer(ctypes.byref(f), ctypes.byref(pa), stream))
             if mark is not None:
                 mark("exchange_walk")
-            api._check(lib.kda_flag_wait(self._wait_flags, self.world, self.epoch, st_ptr, stream))
+            if defer_wait:      # the consumer of the entry states waits itself (kda_fwd_k2_after_flags)
+                self.pending = (self._wait_flags, self.world, self.epoch)
+            else:
+                self.pending = None
+                api._check(lib.kda_flag_wait(self._wait_flags, self.world, self.epoch, st_ptr, stream))
         return self.ent.view(self.world * self.hp, D, D), (self.final if want_final else None)
 
 
@@ -518,14 +523,26 @@ class _Segment:
             return self.lib.kda_fwd_k2_state_push(ctypes.byref(self.args_mq), ctypes.byref(push),
                                                   api._stream_handle() if stream is None else stream)
 
-    def outputs(self, S_in, stream=None):
-        """Ordinary K2 pass from the true entry state: (o, state after the segment)."""
+    def outputs(self, S_in, stream=None, after_flags=None):
+        """Ordinary K2 pass from the true entry state: (o, state after the segment).  ``after_flags = (flags, n,
+        epoch)``: the entry state is being stored by other GPUs and the kernel waits for those flags itself
+        (``kda_fwd_k2_after_flags``); returns ``(None, None)`` when the library has no such kernel for this
+        problem (nothing was launched)."""
         if S_in is not None and not (S_in.is_contiguous() and S_in.dtype == torch.float32):
+            if after_flags is not None:
+                raise ValueError("an entry state that is still arriving cannot be copied")
             S_in = S_in.contiguous().float()
         self._s_in = S_in   # keep the entry state alive until the launch has been ordered
         self.args.h0 = None if S_in is None else ctypes.c_void_p(S_in.data_ptr())
         with torch.cuda.device(self.dev):
-            api._check(self.lib.kda_fwd_k2(ctypes.byref(self.args), api._stream_handle() if stream is None else stream))
+            st = api._stream_handle() if stream is None else stream
+            if after_flags is not None:
+                rc = self.lib.kda_fwd_k2_after_flags(ctypes.byref(self.args), after_flags[0], after_flags[1], after_flags[2], st)
+                if rc == _lib.ERR_UNSUPPORTED:
+                    return None, None
+                api._check(rc)
+            else:
+                api._check(self.lib.kda_fwd_k2(ctypes.byref(self.args), st))
         return self.o, self.ht
 
 
@@ -587,6 +604,7 @@ class SeqParallelPlan:
         # every rank takes the same decision (the set-up is collective), else the NCCL collectives.
         self.exchange_kind = "nccl"
         self._fused_push = os.environ.get("KDA_B200_FUSED_PUSH", "1") != "0"
+        self._k2_waits = self._fused_push
         want_peer = peer_exchange is True or (peer_exchange == "auto" and os.environ.get("KDA_B200_PEER_EXCHANGE", "1") != "0")
         if self.world > 1 and self.mode == "a2a" and want_peer and q.is_cuda:
             peer = _PeerExchange.create(self.chains, self.world, self.rank, group, q.device)
@@ -637,9 +655,21 @@ class SeqParallelPlan:
         mark("transforms")
         entry, final = exchange_and_fold(mq, self.h0, self.rank, self.world, group=self.group, mode=self.mode,
                                          sub=self.sub, bufs=self.bufs, want_final=self.want_final, status=seg.ws,
-                                         mark=mark if timeline is not None else None, pushed=pushed)
+                                         mark=mark if timeline is not None else None, pushed=pushed,
+                                         defer_wait=self._k2_waits)
         mark("exchange_fold")
-        o, ht = seg.outputs(entry.reshape(seg.B, seg.H, D, D))
+        pending = peer.pending if peer is not None else None
+        if pending is not None:
+            # the final pass waits for the entry states itself, behind its first record loads
+            peer.pending = None
+            o, ht = seg.outputs(entry.reshape(seg.B, seg.H, D, D), after_flags=pending)
+            if o is None:                            # no kernel of that kind for this problem: wait, then the plain pass
+                self._k2_waits = False
+                with torch.cuda.device(seg.dev):
+                    api._check(seg.lib.kda_flag_wait(pending[0], pending[1], pending[2], seg.ws.data_ptr(), api._stream_handle()))
+                o, ht = seg.outputs(entry.reshape(seg.B, seg.H, D, D))
+        else:
+            o, ht = seg.outputs(entry.reshape(seg.B, seg.H, D, D))
         mark("k2")
         o = o.view(self.out_shape)
         if self.want_final:

@@ -118,6 +118,38 @@ def test_transform_pass_that_pushes_its_own_tiles(cuda_device):
             assert api.check_device_status(segs[0].ws) == 0
 
 
+@pytest.mark.parametrize("H,T", [(4, 256), (40, 64)])
+def test_final_pass_that_waits_for_its_entry_state(cuda_device, H, T):
+    """kda_fwd_k2_after_flags (the 8-row form for 4 chains, the 16-row form for 40): with the flags already raised
+    the pass equals the plain one bit for bit; with flags nothing raises it gives up after the wait limit with
+    status code 7 and the context stays usable."""
+    from kda_ascendc_b200 import api, shard
+    from oracle import kda_oracle as O
+
+    dev = cuda_device
+    inp = O.make_inputs(1, T, H, seed0=6, regime="carry", h0_std=0.3)
+    d = {k: (v.to(dev) if torch.is_tensor(v) else v) for k, v in inp.items()}
+    seg = shard._Segment(d["q"], d["k"], d["v"], d["g"], d["beta"], d["scale"], d["lower_bound"], d["A_log"], d["dt_bias"])
+    seg.k1()
+    S = d["initial_state"].contiguous()
+    o_p, h_p = (x.clone() for x in seg.outputs(S))
+    flags = torch.full((4,), 3, dtype=torch.int32, device=dev)
+    o_w, h_w = seg.outputs(S, after_flags=(flags.data_ptr(), 4, 3))
+    assert o_w is not None, "the library should have a waiting kernel for this shape"
+    torch.cuda.synchronize()
+    assert torch.equal(o_w, o_p) and torch.equal(h_w, h_p) and api.check_device_status(seg.ws) == 0
+    t0 = time.perf_counter()
+    seg.outputs(S, after_flags=(flags.data_ptr(), 4, 4))          # epoch 4 never comes
+    torch.cuda.synchronize()
+    assert 0.5 < time.perf_counter() - t0 < 20.0
+    with pytest.raises(RuntimeError, match="bounded device-side wait"):
+        api.check_device_status(seg.ws)
+    seg.ws[:4].zero_()
+    o_a, h_a = seg.outputs(S)
+    torch.cuda.synchronize()
+    assert torch.equal(o_a, o_p) and torch.equal(h_a, h_p)
+
+
 def test_a_flag_that_never_comes_ends_in_a_status_code(cuda_device):
     import kda_ascendc_b200 as K
     from kda_ascendc_b200 import _lib, api
