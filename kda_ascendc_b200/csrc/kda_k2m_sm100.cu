@@ -116,7 +116,7 @@ __global__ void __launch_bounds__((CW + 1) * 32, MINB) kda_k2m_kernel(const K2Pa
         for (int e = 0; e < 4; ++e)
           hs[nt][e] = (plane == 0 && (vrow0 + gq + (e >> 1) * 8) == (nt * 8 + tq * 2 + (e & 1))) ? 1.f : 0.f;
     } else if (p.h0 != nullptr) {
-      if (p.h0_n_flags > 0) {   // the entry state comes from other GPUs: wait for their flags (the producer warp is already loading records)
+      if (!STATE_ONLY && p.h0_n_flags > 0) {   // the entry state comes from other GPUs: wait for their flags (the producer warp is already loading records)
         int ok = 1;
         if (lane == 0)
           for (int i = 0; i < p.h0_n_flags; ++i) ok &= flag_wait_bounded(p.h0_flags + i, p.h0_epoch) ? 1 : 0;
